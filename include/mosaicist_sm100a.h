@@ -1,0 +1,106 @@
+/* libmosaicist_sm100a — C ABI of the B200 (sm_100a) block-scaled grouped-GEMM / MoE
+ * hot path.
+ *
+ * The reference project has no native interface for this path: its kernels are Pallas /
+ * CuTeDSL programs called from Python capture modules (experiments/loop/*.py).  Each
+ * entry point below therefore cites the reference *function* whose arithmetic and
+ * argument meaning it replaces.
+ *
+ * Conventions
+ *   - every function returns 0 (MSC_OK) or a negative MSC_ERR_* code and never throws or
+ *     exits; msc_last_error() gives a thread-local one-line message for the last failure;
+ *   - the caller owns every buffer; all pointers are DEVICE pointers unless a comment
+ *     says "host"; the library allocates nothing on the device unless a comment says so;
+ *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous and there is
+ *     no hidden synchronisation;
+ *   - device-side waits are bounded: a kernel that gives up records a code in the
+ *     library's status word (msc_status_word_read) and leaves the context usable.
+ */
+#ifndef MOSAICIST_SM100A_H
+#define MOSAICIST_SM100A_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSC_OK 0
+#define MSC_ERR_BAD_ARG (-1)
+#define MSC_ERR_UNSUPPORTED (-2)
+#define MSC_ERR_SMEM (-3)
+#define MSC_ERR_CUDA (-4)
+#define MSC_ERR_TIMEOUT (-5)
+
+/* Epilogue selection for the grouped GEMMs. */
+#define MSC_EPI_PLAIN 0       /* out = bf16(alpha[g] * acc)                               */
+#define MSC_EPI_ROW_SCALE 1   /* out = bf16(alpha[g] * row_scale[row] * acc)  (routing weight) */
+
+/* Tuning knobs; zero-initialise for library defaults.  The fields mirror the KNOBS the
+ * reference's candidate modules expose (experiments/loop/cand_pallas_gemm.py:24-38:
+ * block_k / stages / persistent ...), restated for a persistent one-CTA-per-SM kernel. */
+typedef struct msc_gemm_cfg {
+  int tile_n;    /* CTA tile width: 128 or 256; 0 = default                             */
+  int stages;    /* operand ring depth; 0 = as many as shared memory holds              */
+  int raster;    /* 0: n-tile fastest inside a group, 1: m-tile fastest                 */
+  int max_ctas;  /* persistent grid size; 0 = one CTA per SM                            */
+  int epilogue;  /* MSC_EPI_*                                                            */
+  int reserved[3];
+} msc_gemm_cfg;
+
+int msc_version(void);
+const char* msc_last_error(void);
+
+/* Path of the PTX text of this library's kernels (written next to the .so at build time),
+ * so a capture module can drop it where the reference's collect_artifacts looks
+ * (src/mosaicist/capture.py:81-116).  Host string, owned by the library. */
+const char* msc_ptx_path(void);
+
+/* Reads and clears the device status word of the current device (0 = no kernel gave up).
+ * Synchronises the device.  `out` is a host pointer. */
+int msc_status_word_read(int* out);
+
+/* NVFP4 masked grouped GEMM:
+ *   out[g, r, :] = bf16( alpha[g] * sum_k (a_q*a_sf)[g, r, k] * (b_q*b_sf)[g, :, k] ),  r < masked_m[g]
+ * Replaces masked_grouped_gemm / masked_grouped_gemm_w1p
+ * (experiments/flashinfer-megamoe-sm100a/masked_gemm.py:104, masked_gemm_ws.py:359) and the
+ * FlashInfer call it stands in for (experiments/loop/ref_flashinfer_gemm.py:25-31).
+ *   a_q  (l, m, k/2) bytes, two e2m1 per byte, element 2i in the low nibble, K-minor
+ *   a_sf (l, m/128, k/64, 32, 16) e4m3, the tiling of nvfp4.py:121-131
+ *   b_q  (l, n, k/2), b_sf (l, n/128, k/64, 32, 16)
+ *   alpha (l) fp32 or NULL (= 1); masked_m (l) int32 or NULL (= m)
+ *   out  (l, m, n) bf16; rows >= masked_m[g] are not written
+ * Requires m % 128 == 0, n % tile_n == 0, k % 64 == 0. */
+int msc_grouped_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const void* b_sf,
+                           const float* alpha, const int32_t* masked_m, void* out,
+                           int l, int m, int n, int k, const msc_gemm_cfg* cfg, void* stream);
+
+/* Same arithmetic over a row-concatenated ("ragged") activation tensor: group g owns rows
+ * [group_offsets[g], group_offsets[g] + group_rows[g]) of a_q / out; offsets must be
+ * multiples of 128 (the scale tiling is per 128 rows).  row_scale (rows_total) fp32 is read
+ * when cfg->epilogue == MSC_EPI_ROW_SCALE.  The reference has no ragged form; this is the
+ * layout BASELINE config 3 and the MoE layer use, with per-group semantics as above.
+ *   a_q (rows_total, k/2), a_sf (ceil(rows_total/128), k/64, 32, 16), out (rows_total, n) */
+int msc_grouped_gemm_nvfp4_ragged(const void* a_q, const void* a_sf, const void* b_q,
+                                  const void* b_sf, const float* alpha,
+                                  const int32_t* group_offsets, const int32_t* group_rows,
+                                  const float* row_scale, void* out, int l, int rows_total,
+                                  int n, int k, const msc_gemm_cfg* cfg, void* stream);
+
+/* MXFP8 grouped GEMM (e4m3 values, one ue8m0 scale per 32 K-elements), ragged rows as
+ * above.  The nearest reference arithmetic is the Hopper analog's block-scaled FP8 GEMM
+ * (experiments/flashinfer-megamoe-sm90a/quant.py:47-75) with the scale format and block
+ * size BASELINE config 3 prescribes.
+ *   a_q (rows_total, k) e4m3, a_sf (ceil(rows_total/128), k/128, 32, 16) ue8m0 (same
+ *   128-row tiling, 4 scale columns per chunk), b_q (l, n, k), b_sf (l, n/128, k/128, 32, 16)
+ * Requires k % 128 == 0. */
+int msc_grouped_gemm_mxfp8_ragged(const void* a_q, const void* a_sf, const void* b_q,
+                                  const void* b_sf, const float* alpha,
+                                  const int32_t* group_offsets, const int32_t* group_rows,
+                                  const float* row_scale, void* out, int l, int rows_total,
+                                  int n, int k, const msc_gemm_cfg* cfg, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOSAICIST_SM100A_H */

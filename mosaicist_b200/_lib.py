@@ -1,0 +1,71 @@
+"""ctypes binding of libmosaicist_sm100a.so.
+
+The library is the product: if it cannot be loaded every operator raises — there is no
+CPU or PyTorch fallback behind these calls.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import pathlib
+
+PKG = pathlib.Path(__file__).resolve().parent
+LIB_PATH = PKG / "libmosaicist_sm100a.so"
+
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_SMEM, ERR_CUDA, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5
+EPI_PLAIN, EPI_ROW_SCALE = 0, 1
+
+
+class MscError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{message} (libmosaicist_sm100a status {code})")
+        self.code = code
+
+
+class GemmCfg(ctypes.Structure):
+    _fields_ = [("tile_n", ctypes.c_int), ("stages", ctypes.c_int), ("raster", ctypes.c_int),
+                ("max_ctas", ctypes.c_int), ("epilogue", ctypes.c_int),
+                ("reserved", ctypes.c_int * 3)]
+
+
+_P, _I = ctypes.c_void_p, ctypes.c_int
+_CFG = ctypes.POINTER(GemmCfg)
+
+#: every symbol include/mosaicist_sm100a.h declares: name -> (restype, argtypes)
+SIGNATURES = {
+    "msc_version": (_I, []),
+    "msc_last_error": (ctypes.c_char_p, []),
+    "msc_ptx_path": (ctypes.c_char_p, []),
+    "msc_status_word_read": (_I, [ctypes.POINTER(ctypes.c_int)]),
+    "msc_grouped_gemm_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),
+    "msc_grouped_gemm_nvfp4_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),
+    "msc_grouped_gemm_mxfp8_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """The loaded library, with argument types set.  Raises if it is missing."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise MscError(ERR_CUDA, f"{LIB_PATH} is missing: run `python -m mosaicist_b200.build`")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise MscError(code, load().msc_last_error().decode() or "libmosaicist_sm100a call failed")
+
+
+def status_word() -> int:
+    """Reads and clears the device status word (synchronises the device)."""
+    out = ctypes.c_int(0)
+    check(load().msc_status_word_read(ctypes.byref(out)))
+    return out.value

@@ -1,0 +1,66 @@
+"""Builds libmosaicist_sm100a.so (and the PTX text beside it) in-tree with nvcc.
+
+    python -m mosaicist_b200.build [--force]
+
+The library is compiled for sm_100a only.  nvcc cross-compiles without a GPU, so this
+runs on a CPU-only machine; the resulting .so is what the GPU machine loads.
+"""
+
+from __future__ import annotations
+
+import pathlib
+import shutil
+import subprocess
+import sys
+
+PKG = pathlib.Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIB = PKG / "libmosaicist_sm100a.so"
+PTX = PKG / "libmosaicist_sm100a.ptx"
+PTXAS_LOG = PKG / "libmosaicist_sm100a.ptxas.log"
+
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math"]
+
+
+def sources() -> list[pathlib.Path]:
+    return sorted(CSRC.glob("*.cu"))
+
+
+def _stale() -> bool:
+    if not LIB.exists() or not PTX.exists():
+        return True
+    built = LIB.stat().st_mtime
+    deps = list(CSRC.glob("*")) + [PKG.parent / "include" / "mosaicist_sm100a.h"]
+    return any(p.stat().st_mtime > built for p in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
+    """Compile every .cu under csrc/ into one shared library; returns its path."""
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not force and not _stale():
+        return LIB
+    if not pathlib.Path(nvcc).exists():
+        if LIB.exists():
+            return LIB  # prebuilt library on a machine without the toolkit
+        raise RuntimeError("nvcc not found and no prebuilt libmosaicist_sm100a.so")
+    srcs = [str(s) for s in sources()]
+    cmd = [nvcc, *ARCH, *COMMON, "-Xptxas", "-v", "-shared", "-Xcompiler", "-fPIC",
+           "-cudart", "static", "-o", str(LIB), *srcs, "-ldl"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    PTXAS_LOG.write_text(res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stderr[-4000:])
+    if verbose:
+        print(res.stderr)
+    # PTX text of the GEMM kernels: what a capture module hands to the PTX fingerprinter
+    cmd = [nvcc, *ARCH, *COMMON, "-ptx", "-o", str(PTX), str(CSRC / "gemm_blockscaled.cu")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc -ptx failed:\n" + res.stderr[-4000:])
+    return LIB
+
+
+if __name__ == "__main__":
+    path = build(force="--force" in sys.argv, verbose=True)
+    print("built", path)

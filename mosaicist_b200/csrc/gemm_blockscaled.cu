@@ -1,0 +1,456 @@
+// Block-scaled grouped GEMM for sm_100a: NVFP4 (e2m1 x e2m1, ue4m3 scale per 16) and
+// MXFP8 (e4m3 x e4m3, ue8m0 scale per 32), fp32 accumulation in TMEM, bf16 output.
+//
+// One persistent CTA per SM, 192 threads, three roles:
+//   warps 0-3  epilogue: tcgen05.ld their TMEM lane quadrant, scale, round to bf16, store
+//   warp 4     MMA issuer: one thread stages scale factors into TMEM (tcgen05.cp) and
+//              issues tcgen05.mma for each K step of the tile
+//   warp 5     producer: one thread issues TMA loads for the operand ring
+// The accumulator is double-buffered in TMEM (when two fit) so the epilogue of tile i
+// overlaps the main loop of tile i+1.
+//
+// Both operand kinds move the same bytes: a K stage is 128 bytes of K per row (256 e2m1 or
+// 128 e4m3 elements), loaded as a [128 or TILE_N rows] x 128 B box with the 128-byte swizzle,
+// and consumed by four MMAs that each advance 32 bytes along K.  What differs is the scale
+// bookkeeping: NVFP4 uses one 512-byte scale chunk (32 x 16 B: 128 rows x 4 scales) per MMA,
+// MXFP8 one chunk per stage with the MMA picking its byte through the descriptor's
+// scale-factor id.
+//
+// Arithmetic follows masked_grouped_gemm_reference
+// (experiments/flashinfer-megamoe-sm100a/nvfp4.py:68-78): products of e2m1/e4m3 values and
+// their block scales accumulate in fp32, alpha is applied in fp32, one rounding to bf16.
+#include "host_common.h"
+#include "ptx.cuh"
+
+#include <cuda_bf16.h>
+
+namespace msc {
+
+enum : int { KIND_NVFP4 = 0, KIND_MXFP8 = 1 };
+
+struct GemmParams {
+  const uint8_t* sfa;        // [row_tiles][sf_chunks][512]
+  const uint8_t* sfb;        // [l][n/128][sf_chunks][512]
+  const float* alpha;        // [l] or null
+  const float* row_scale;    // [rows_total] or null
+  const int* group_rows;     // [l] or null (= m_stride)
+  const int* group_offsets;  // [l] or null (= g * m_stride)
+  __nv_bfloat16* out;        // [rows_total][n]
+  int* status;
+  int l, m_stride, n;
+  int k_stages;              // ceil(k_bytes / 128)
+  int sf_chunks;             // scale chunks along K per 128-row tile
+  int raster;
+};
+
+template <int TILE_N, int STAGES>
+struct Smem {
+  static constexpr int kHeader = 1024;
+  static constexpr int kA = 128 * 128;
+  static constexpr int kB = TILE_N * 128;
+  static constexpr int kSub = TILE_N / 128;
+  static constexpr int kSfa = 4 * 512;
+  static constexpr int kSfb = 4 * 512 * kSub;
+  static constexpr int kOffA = kHeader;
+  static constexpr int kOffB = kOffA + STAGES * kA;
+  static constexpr int kOffSfa = kOffB + STAGES * kB;
+  static constexpr int kOffSfb = kOffSfa + STAGES * kSfa;
+  static constexpr int kTotal = kOffSfb + STAGES * kSfb;
+  static constexpr int kAlloc = kTotal + 1024;  // slack to realign the base to 1024 B
+};
+
+// Walks the flattened (group, m-tile, n-tile) space in increasing tile id.
+struct TileCursor {
+  int g = 0, base = 0, mtiles = 0, rows = 0, off = 0;
+  bool primed = false;
+  __device__ __forceinline__ bool seek(const GemmParams& p, int ntiles, int t, int& mt, int& nt) {
+    while (true) {
+      if (!primed) {
+        if (g >= p.l) return false;
+        rows = p.group_rows ? __ldg(p.group_rows + g) : p.m_stride;
+        if (rows < 0) rows = 0;
+        if (p.m_stride > 0 && rows > p.m_stride) rows = p.m_stride;
+        off = p.group_offsets ? __ldg(p.group_offsets + g) : g * p.m_stride;
+        mtiles = (rows + 127) >> 7;
+        primed = true;
+      }
+      const int tiles = mtiles * ntiles;
+      if (t < base + tiles) break;
+      base += tiles;
+      ++g;
+      primed = false;
+    }
+    const int u = t - base;
+    if (p.raster == 0) {
+      mt = u / ntiles;
+      nt = u - mt * ntiles;
+    } else {
+      nt = u / mtiles;
+      mt = u - nt * mtiles;
+    }
+    return true;
+  }
+};
+
+template <int KIND, int TILE_N, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                        const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  using L = Smem<TILE_N, STAGES>;
+  constexpr int kSub = L::kSub;
+  constexpr int kAccBufs = (TILE_N == 128) ? 2 : 1;
+  constexpr int kSfaCols = 16;             // 4 MMAs x 4 columns (NVFP4); MXFP8 uses 4
+  constexpr int kSfbCols = 16 * kSub;
+  constexpr int kSlotCols = kSfaCols + kSfbCols;
+  constexpr int kSfCol0 = kAccBufs * TILE_N;
+  constexpr int kSfSlots = (512 - kSfCol0) / kSlotCols >= 4 ? 4 : (512 - kSfCol0) / kSlotCols;
+  static_assert(kSfSlots >= 1, "no TMEM left for scale factors");
+  constexpr int kChunksPerStage = (KIND == KIND_NVFP4) ? 4 : 1;
+  constexpr uint32_t kIdescBase =
+      (KIND == KIND_NVFP4)
+          ? ((1u << 7) | (1u << 10) | (uint32_t(TILE_N >> 3) << 17) | (8u << 24))
+          : ((uint32_t(TILE_N >> 3) << 17) | (1u << 23) | (8u << 24));
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - raw);
+
+  // header: barriers, TMEM base pointer, abort flag
+  const uint32_t bar_full = sbase;                        // STAGES x 8
+  const uint32_t bar_empty = sbase + 8 * STAGES;          // STAGES x 8
+  const uint32_t bar_acc_full = sbase + 16 * STAGES;      // 2 x 8
+  const uint32_t bar_acc_empty = bar_acc_full + 16;       // 2 x 8
+  const uint32_t bar_drain = bar_acc_empty + 16;          // 1 x 8
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + 512);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(sgen + 516);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int ntiles = p.n / TILE_N;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 4);
+    }
+    mbar_init(bar_drain, 1);
+    *abort_flag = 0u;
+    fence_barrier_init();
+  }
+  if (warp == 5 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 5) {
+    // ------------------------------ producer ------------------------------------
+    if (lane == 0) {
+      TileCursor cur;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok; t += gridDim.x) {
+        int mt, nt;
+        if (!cur.seek(p, ntiles, t, mt, nt)) break;
+        const int row0 = cur.off + mt * 128;
+        const int brow0 = cur.g * p.n + nt * TILE_N;
+        const uint8_t* sfa_src = p.sfa + (size_t)(row0 >> 7) * p.sf_chunks * 512;
+        const uint8_t* sfb_src =
+            p.sfb + ((size_t)cur.g * (p.n >> 7) + (size_t)nt * kSub) * p.sf_chunks * 512;
+        for (int kb = 0; kb < p.k_stages; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 1)) {
+            ok = false;
+            break;
+          }
+          const int c0 = kb * kChunksPerStage;
+          const int nch = min(kChunksPerStage, p.sf_chunks - c0);
+          const uint32_t full = bar_full + 8 * s;
+          mbar_arrive_expect_tx(full, L::kA + L::kB + (1 + kSub) * nch * 512);
+          tma_load_2d(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
+          tma_load_2d(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, brow0);
+          bulk_load_1d(sbase + L::kOffSfa + s * L::kSfa, sfa_src + (size_t)c0 * 512, nch * 512,
+                       full);
+#pragma unroll
+          for (int sub = 0; sub < kSub; ++sub)
+            bulk_load_1d(sbase + L::kOffSfb + s * L::kSfb + sub * 2048,
+                         sfb_src + ((size_t)sub * p.sf_chunks + c0) * 512, nch * 512, full);
+        }
+      }
+      if (*abort_flag) {
+        // wait (bounded) for the loads still in flight so none lands after the CTA exits
+        for (int j = max(0, it - STAGES); j < it; ++j)
+          mbar_wait_drain(bar_full + 8 * (j % STAGES), (j / STAGES) & 1);
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------ MMA issuer ----------------------------------
+    if (lane == 0) {
+      TileCursor cur;
+      int it = 0, tl = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok; t += gridDim.x, ++tl) {
+        int mt, nt;
+        if (!cur.seek(p, ntiles, t, mt, nt)) break;
+        const int buf = tl % kAccBufs;
+        const uint32_t aph = (tl / kAccBufs) & 1;
+        if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status, 2)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t acc = tmem_base + buf * TILE_N;
+        for (int kb = 0; kb < p.k_stages; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait_bounded(bar_full + 8 * s, ph, abort_flag, p.status, 3)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const int c0 = kb * kChunksPerStage;
+          const int nch = min(kChunksPerStage, p.sf_chunks - c0);
+          const uint32_t sfa_t = tmem_base + kSfCol0 + (it % kSfSlots) * kSlotCols;
+          const uint32_t sfb_t = sfa_t + kSfaCols;
+          const uint32_t sfa_s = sbase + L::kOffSfa + s * L::kSfa;
+          const uint32_t sfb_s = sbase + L::kOffSfb + s * L::kSfb;
+          for (int c = 0; c < nch; ++c) {
+            tc_cp_32x128b_warpx4(sfa_t + 4 * c, scale_desc(sfa_s + c * 512));
+#pragma unroll
+            for (int sub = 0; sub < kSub; ++sub)
+              tc_cp_32x128b_warpx4(sfb_t + 4 * kSub * c + 4 * sub,
+                                   scale_desc(sfb_s + sub * 2048 + c * 512));
+          }
+          const uint64_t adesc = operand_desc_sw128(sbase + L::kOffA + s * L::kA);
+          const uint64_t bdesc = operand_desc_sw128(sbase + L::kOffB + s * L::kB);
+          const int nmma = (KIND == KIND_NVFP4) ? nch : 4;
+          for (int j = 0; j < nmma; ++j) {
+            const uint32_t accumulate = (kb | j) ? 1u : 0u;
+            if (KIND == KIND_NVFP4) {
+              tc_mma_nvfp4(acc, adesc + 2 * j, bdesc + 2 * j, kIdescBase, sfa_t + 4 * j,
+                           sfb_t + 4 * kSub * j, accumulate);
+            } else {
+              const uint32_t idesc = kIdescBase | (uint32_t(j) << 29) | (uint32_t(j) << 4);
+              tc_mma_mxf8(acc, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, accumulate);
+            }
+          }
+          tc_commit(bar_empty + 8 * s);  // frees the smem stage once these MMAs have read it
+        }
+        if (ok) tc_commit(bar_acc_full + 8 * buf);
+      }
+      if (*abort_flag) {
+        tc_commit(bar_drain);
+        mbar_wait_drain(bar_drain, 0);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------------
+    TileCursor cur;
+    int tl = 0;
+    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    for (int t = blockIdx.x;; t += gridDim.x, ++tl) {
+      int mt, nt;
+      if (!cur.seek(p, ntiles, t, mt, nt)) break;
+      const int buf = tl % kAccBufs;
+      const uint32_t aph = (tl / kAccBufs) & 1;
+      bool ok = mbar_wait_bounded(bar_acc_full + 8 * buf, aph, abort_flag, p.status, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row_local = mt * 128 + warp * 32 + lane;
+      const bool valid = row_local < cur.rows;
+      const size_t out_row = (size_t)cur.off + row_local;
+      float scale = p.alpha ? __ldg(p.alpha + cur.g) : 1.0f;
+      if (p.row_scale && valid) scale *= __ldg(p.row_scale + out_row);
+      __nv_bfloat16* dst = p.out + out_row * p.n + (size_t)nt * TILE_N;
+#pragma unroll 1
+      for (int c = 0; c < TILE_N / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_base + buf * TILE_N + c * 32, v);
+        tmem_ld_wait();
+        if (valid) {
+          uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float lo = __uint_as_float(v[q * 8 + 2 * e]) * scale;
+              const float hi = __uint_as_float(v[q * 8 + 2 * e + 1]) * scale;
+              __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
+              w[e] = *reinterpret_cast<uint32_t*>(&pr);
+            }
+            d4[q] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------- host side -------------------------------------------
+
+template <int KIND, int TILE_N, int STAGES>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                  cudaStream_t stream) {
+  using L = Smem<TILE_N, STAGES>;
+  auto kern = gemm_blockscaled_kernel<KIND, TILE_N, STAGES>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  MSC_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+    configured[dev & 63] = true;
+  }
+  kern<<<grid, 192, L::kAlloc, stream>>>(ta, tb, p);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+template <int KIND, int TILE_N>
+static int pick_stages(int stages, const CUtensorMap& ta, const CUtensorMap& tb,
+                       const GemmParams& p, int grid, cudaStream_t stream) {
+  constexpr int kMax = (TILE_N == 128) ? 6 : 4;
+  if (stages <= 0 || stages > kMax) stages = kMax;
+  switch (stages) {
+    case 2: return launch<KIND, TILE_N, 2>(ta, tb, p, grid, stream);
+    case 3: return launch<KIND, TILE_N, 3>(ta, tb, p, grid, stream);
+    case 4: return launch<KIND, TILE_N, 4>(ta, tb, p, grid, stream);
+    case 5:
+      if constexpr (TILE_N == 128) return launch<KIND, TILE_N, 5>(ta, tb, p, grid, stream);
+      break;
+    case 6:
+      if constexpr (TILE_N == 128) return launch<KIND, TILE_N, 6>(ta, tb, p, grid, stream);
+      break;
+    default: break;
+  }
+  return fail(MSC_ERR_UNSUPPORTED, "stages=%d is not built for tile_n=%d", stages, TILE_N);
+}
+
+// Shared body of the three entry points.  k_bytes: bytes of K per row; chunk_elems: K
+// elements one 512-byte scale chunk covers.
+static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void* b_q,
+                        const void* b_sf, const float* alpha, const int32_t* group_offsets,
+                        const int32_t* group_rows, const float* row_scale, void* out, int l,
+                        long long rows_total, int m_stride, int n, int k,
+                        const msc_gemm_cfg* cfg_in, void* stream_v) {
+  msc_gemm_cfg cfg = {};
+  if (cfg_in) cfg = *cfg_in;
+  if (!a_q || !a_sf || !b_q || !b_sf || !out) return fail(MSC_ERR_BAD_ARG, "NULL operand pointer");
+  if (l <= 0 || rows_total <= 0 || n <= 0 || k <= 0)
+    return fail(MSC_ERR_BAD_ARG, "l, rows, n, k must be positive");
+  const int tile_n = cfg.tile_n ? cfg.tile_n : 128;
+  if (tile_n != 128 && tile_n != 256)
+    return fail(MSC_ERR_UNSUPPORTED, "tile_n must be 128 or 256, got %d", tile_n);
+  if (n % tile_n) return fail(MSC_ERR_BAD_ARG, "n=%d must be a multiple of tile_n=%d", n, tile_n);
+  const int chunk_elems = (kind == KIND_NVFP4) ? 64 : 128;
+  if (k % chunk_elems)
+    return fail(MSC_ERR_BAD_ARG, "k=%d must be a multiple of %d", k, chunk_elems);
+  if (cfg.epilogue != MSC_EPI_PLAIN && cfg.epilogue != MSC_EPI_ROW_SCALE)
+    return fail(MSC_ERR_UNSUPPORTED, "unknown epilogue %d", cfg.epilogue);
+  if (cfg.epilogue == MSC_EPI_ROW_SCALE && !row_scale)
+    return fail(MSC_ERR_BAD_ARG, "MSC_EPI_ROW_SCALE needs row_scale");
+  if (reinterpret_cast<uintptr_t>(a_sf) % 16 || reinterpret_cast<uintptr_t>(b_sf) % 16 ||
+      reinterpret_cast<uintptr_t>(out) % 16)
+    return fail(MSC_ERR_BAD_ARG, "scale and output pointers must be 16-byte aligned");
+  const long long k_bytes = (kind == KIND_NVFP4) ? k / 2 : k;
+
+  int* status = status_word();
+  if (!status) return fail(MSC_ERR_CUDA, "status word unavailable on this device");
+
+  CUtensorMap ta, tb;
+  int rc = make_tmap_bytes_2d(&ta, a_q, (uint64_t)rows_total, (uint64_t)k_bytes, 128);
+  if (rc) return rc;
+  rc = make_tmap_bytes_2d(&tb, b_q, (uint64_t)l * n, (uint64_t)k_bytes, (uint32_t)tile_n);
+  if (rc) return rc;
+
+  GemmParams p;
+  p.sfa = static_cast<const uint8_t*>(a_sf);
+  p.sfb = static_cast<const uint8_t*>(b_sf);
+  p.alpha = alpha;
+  p.row_scale = (cfg.epilogue == MSC_EPI_ROW_SCALE) ? row_scale : nullptr;
+  p.group_rows = group_rows;
+  p.group_offsets = group_offsets;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.status = status;
+  p.l = l;
+  p.m_stride = m_stride;
+  p.n = n;
+  p.k_stages = (int)((k_bytes + 127) / 128);
+  p.sf_chunks = k / chunk_elems;
+  p.raster = cfg.raster ? 1 : 0;
+
+  const long long max_tiles = ((rows_total + 127) / 128 + l) * (long long)(n / tile_n);
+  int grid = cfg.max_ctas > 0 ? cfg.max_ctas : num_sms();
+  if (grid <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
+  if (grid > max_tiles) grid = (int)max_tiles;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  if (kind == KIND_NVFP4) {
+    if (tile_n == 128) return pick_stages<KIND_NVFP4, 128>(cfg.stages, ta, tb, p, grid, stream);
+    return pick_stages<KIND_NVFP4, 256>(cfg.stages, ta, tb, p, grid, stream);
+  }
+  if (tile_n == 128) return pick_stages<KIND_MXFP8, 128>(cfg.stages, ta, tb, p, grid, stream);
+  return pick_stages<KIND_MXFP8, 256>(cfg.stages, ta, tb, p, grid, stream);
+}
+
+}  // namespace msc
+
+extern "C" {
+
+int msc_grouped_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const void* b_sf,
+                           const float* alpha, const int32_t* masked_m, void* out, int l, int m,
+                           int n, int k, const msc_gemm_cfg* cfg, void* stream) {
+  if (m <= 0 || m % 128) return msc::fail(MSC_ERR_BAD_ARG, "m=%d must be a positive multiple of 128", m);
+  if (cfg && cfg->epilogue != MSC_EPI_PLAIN)
+    return msc::fail(MSC_ERR_UNSUPPORTED, "the masked form takes MSC_EPI_PLAIN only");
+  return msc::grouped_gemm(msc::KIND_NVFP4, a_q, a_sf, b_q, b_sf, alpha, nullptr, masked_m, nullptr,
+                           out, l, (long long)l * m, m, n, k, cfg, stream);
+}
+
+int msc_grouped_gemm_nvfp4_ragged(const void* a_q, const void* a_sf, const void* b_q,
+                                  const void* b_sf, const float* alpha,
+                                  const int32_t* group_offsets, const int32_t* group_rows,
+                                  const float* row_scale, void* out, int l, int rows_total, int n,
+                                  int k, const msc_gemm_cfg* cfg, void* stream) {
+  if (!group_offsets || !group_rows)
+    return msc::fail(MSC_ERR_BAD_ARG, "group_offsets and group_rows are required");
+  return msc::grouped_gemm(msc::KIND_NVFP4, a_q, a_sf, b_q, b_sf, alpha, group_offsets, group_rows,
+                           row_scale, out, l, rows_total, 0, n, k, cfg, stream);
+}
+
+int msc_grouped_gemm_mxfp8_ragged(const void* a_q, const void* a_sf, const void* b_q,
+                                  const void* b_sf, const float* alpha,
+                                  const int32_t* group_offsets, const int32_t* group_rows,
+                                  const float* row_scale, void* out, int l, int rows_total, int n,
+                                  int k, const msc_gemm_cfg* cfg, void* stream) {
+  if (!group_offsets || !group_rows)
+    return msc::fail(MSC_ERR_BAD_ARG, "group_offsets and group_rows are required");
+  return msc::grouped_gemm(msc::KIND_MXFP8, a_q, a_sf, b_q, b_sf, alpha, group_offsets, group_rows,
+                           row_scale, out, l, rows_total, 0, n, k, cfg, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,114 @@
+// Error reporting, status word and tensor-map plumbing behind the C ABI.
+#include "host_common.h"
+
+#include <dlfcn.h>
+#include <string.h>
+
+#include <mutex>
+#include <string>
+
+namespace msc {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// One status word per device that loads the library.  Kernels receive its address as an
+// argument; a bounded wait that gives up stores (0x100 | wait id) here.
+__device__ int g_status_word;
+
+int* status_word() {
+  static std::mutex mu;
+  static int* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    cached[dev] = static_cast<int*>(p);
+  }
+  return cached[dev];
+}
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  if (!fn) fail(MSC_ERR_CUDA, "cuTensorMapEncodeTiled could not be resolved from the driver");
+  return fn;
+}
+
+int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                       uint32_t box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return MSC_ERR_CUDA;
+  if (reinterpret_cast<uintptr_t>(base) % 16 || row_bytes % 16)
+    return fail(MSC_ERR_BAD_ARG, "operand base and row pitch must be 16-byte aligned");
+  if (box_rows == 0 || box_rows > 256) return fail(MSC_ERR_BAD_ARG, "box rows out of range");
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {128u, box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MSC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return MSC_OK;
+}
+
+int num_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+  return cached[dev];
+}
+
+}  // namespace msc
+
+extern "C" {
+
+int msc_version(void) { return 1; }
+
+const char* msc_last_error(void) { return msc::g_err; }
+
+const char* msc_ptx_path(void) {
+  static std::string path;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    Dl_info info;
+    if (dladdr(reinterpret_cast<void*>(&msc_version), &info) && info.dli_fname) {
+      std::string so(info.dli_fname);
+      size_t dot = so.rfind(".so");
+      path = (dot == std::string::npos ? so : so.substr(0, dot)) + ".ptx";
+    }
+  });
+  return path.c_str();
+}
+
+int msc_status_word_read(int* out) {
+  if (!out) return msc::fail(MSC_ERR_BAD_ARG, "out is NULL");
+  int* w = msc::status_word();
+  if (!w) return msc::fail(MSC_ERR_CUDA, "status word unavailable on this device");
+  MSC_CUDA_OK(cudaDeviceSynchronize());
+  MSC_CUDA_OK(cudaMemcpy(out, w, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*out != 0) MSC_CUDA_OK(cudaMemset(w, 0, sizeof(int)));
+  return MSC_OK;
+}
+
+}  // extern "C"

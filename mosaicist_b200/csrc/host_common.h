@@ -1,0 +1,42 @@
+// Host-side helpers shared by the C-ABI translation units: error reporting, the device
+// status word, driver entry points for tensor-map encoding.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/mosaicist_sm100a.h"
+
+namespace msc {
+
+// Sets the thread-local message msc_last_error() returns and hands `code` back.
+int fail(int code, const char* fmt, ...);
+
+// Device pointer of the current device's status word (lazily resolved, one per device).
+int* status_word();
+
+// cuTensorMapEncodeTiled, resolved through the runtime so libcuda is not a link-time
+// dependency.  Returns nullptr (and sets the error message) if it cannot be resolved.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn();
+
+// 2-D byte tensor [rows][row_bytes] with a [box_rows][128 B] box and 128-byte swizzle.
+int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                       uint32_t box_rows);
+
+int num_sms();
+
+#define MSC_CUDA_OK(expr)                                                              \
+  do {                                                                                 \
+    cudaError_t e__ = (expr);                                                          \
+    if (e__ != cudaSuccess)                                                            \
+      return ::msc::fail(MSC_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__));      \
+  } while (0)
+
+}  // namespace msc

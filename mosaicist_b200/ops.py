@@ -1,0 +1,132 @@
+"""Host-side operators over torch CUDA tensors, named after the reference functions they
+replace (experiments/flashinfer-megamoe-sm100a/*.py).  torch supplies device memory and
+the stream; all arithmetic happens in libmosaicist_sm100a.so.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+
+@dataclass(frozen=True)
+class GemmConfig:
+    """Knobs of the persistent block-scaled GEMM.  The reference's GemmConfig
+    (masked_gemm.py:52-76) tunes block_k / stages of a one-tile-per-CTA kernel; here K
+    staging is fixed at 128 bytes per row and the knobs are the tile width, the ring
+    depth, the tile order and the persistent grid size.  Zero means library default."""
+    tile_n: int = 0
+    stages: int = 0
+    raster: int = 0
+    max_ctas: int = 0
+
+    def c(self, epilogue: int = _lib.EPI_PLAIN) -> _lib.GemmCfg:
+        return _lib.GemmCfg(self.tile_n, self.stages, self.raster, self.max_ctas, epilogue)
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtypes, shape=None):
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if t.dtype not in dtypes:
+        raise ValueError(f"{name} has dtype {t.dtype}, expected one of {dtypes}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
+_BYTES = (torch.uint8, torch.int8, torch.float8_e4m3fn, torch.float8_e8m0fnu)
+if hasattr(torch, "float4_e2m1fn_x2"):
+    _BYTES = _BYTES + (torch.float4_e2m1fn_x2,)
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def masked_grouped_gemm(a_q, a_sf, b_q, b_sf, alpha=None, masked_m=None,
+                        config: GemmConfig = GemmConfig(), out=None) -> torch.Tensor:
+    """out[l, m, n] = bf16(alpha[l] * dequant(A)[l] @ dequant(B)[l].T), rows >= masked_m[l]
+    left untouched.  Same operands as masked_grouped_gemm (masked_gemm.py:104-123):
+    a_q (l, m, k/2) packed e2m1, a_sf (l, m/128, k/64, 32, 16) e4m3 in the MMA tiling,
+    b_q (l, n, k/2), b_sf (l, n/128, k/64, 32, 16), alpha (l,) f32, masked_m (l,) i32."""
+    _need(a_q, "a_q", _BYTES)
+    _need(b_q, "b_q", _BYTES)
+    l, m, kh = a_q.shape
+    n = b_q.shape[1]
+    k = kh * 2
+    _need(b_q, "b_q", _BYTES, (l, n, kh))
+    _need(a_sf, "a_sf", _BYTES, (l, m // 128, k // 64, 32, 16))
+    _need(b_sf, "b_sf", _BYTES, (l, n // 128, k // 64, 32, 16))
+    if alpha is not None:
+        _need(alpha, "alpha", (torch.float32,), (l,))
+    if masked_m is not None:
+        _need(masked_m, "masked_m", (torch.int32,), (l,))
+    if out is None:
+        out = torch.empty((l, m, n), dtype=torch.bfloat16, device=a_q.device)
+    else:
+        _need(out, "out", (torch.bfloat16,), (l, m, n))
+    cfg = config.c()
+    _lib.check(_lib.load().msc_grouped_gemm_nvfp4(
+        _ptr(a_q), _ptr(a_sf), _ptr(b_q), _ptr(b_sf), _ptr(alpha), _ptr(masked_m), _ptr(out),
+        l, m, n, k, cfg, _stream()))
+    return out
+
+
+def _ragged(fn_name, k, a_q, a_sf, b_q, b_sf, alpha, group_offsets, group_rows, row_scale,
+            config, out):
+    rows_total = a_q.shape[0]
+    l, n = b_q.shape[0], b_q.shape[1]
+    _need(group_offsets, "group_offsets", (torch.int32,), (l,))
+    _need(group_rows, "group_rows", (torch.int32,), (l,))
+    if alpha is not None:
+        _need(alpha, "alpha", (torch.float32,), (l,))
+    if row_scale is not None:
+        _need(row_scale, "row_scale", (torch.float32,), (rows_total,))
+    if out is None:
+        out = torch.empty((rows_total, n), dtype=torch.bfloat16, device=a_q.device)
+    else:
+        _need(out, "out", (torch.bfloat16,), (rows_total, n))
+    cfg = config.c(_lib.EPI_ROW_SCALE if row_scale is not None else _lib.EPI_PLAIN)
+    _lib.check(getattr(_lib.load(), fn_name)(
+        _ptr(a_q), _ptr(a_sf), _ptr(b_q), _ptr(b_sf), _ptr(alpha), _ptr(group_offsets),
+        _ptr(group_rows), _ptr(row_scale), _ptr(out), l, rows_total, n, k, cfg, _stream()))
+    return out
+
+
+def ragged_grouped_gemm_nvfp4(a_q, a_sf, b_q, b_sf, group_offsets, group_rows, alpha=None,
+                              row_scale=None, config: GemmConfig = GemmConfig(), out=None):
+    """NVFP4 grouped GEMM over row-concatenated groups: group g owns rows
+    [group_offsets[g], +group_rows[g]) of a_q (rows_total, k/2) and out (rows_total, n);
+    offsets are multiples of 128.  Per-group arithmetic as masked_grouped_gemm."""
+    _need(a_q, "a_q", _BYTES)
+    rows_total, kh = a_q.shape
+    k = kh * 2
+    l, n = b_q.shape[0], b_q.shape[1]
+    _need(b_q, "b_q", _BYTES, (l, n, kh))
+    _need(a_sf, "a_sf", _BYTES, ((rows_total + 127) // 128, k // 64, 32, 16))
+    _need(b_sf, "b_sf", _BYTES, (l, n // 128, k // 64, 32, 16))
+    return _ragged("msc_grouped_gemm_nvfp4_ragged", k, a_q, a_sf, b_q, b_sf, alpha,
+                   group_offsets, group_rows, row_scale, config, out)
+
+
+def ragged_grouped_gemm_mxfp8(a_q, a_sf, b_q, b_sf, group_offsets, group_rows, alpha=None,
+                              row_scale=None, config: GemmConfig = GemmConfig(), out=None):
+    """MXFP8 grouped GEMM (e4m3 values, ue8m0 scale per 32) over row-concatenated groups.
+    a_q (rows_total, k) e4m3, a_sf (ceil(rows_total/128), k/128, 32, 16) ue8m0, b_q (l, n, k),
+    b_sf (l, n/128, k/128, 32, 16)."""
+    _need(a_q, "a_q", _BYTES)
+    rows_total, k = a_q.shape
+    l, n = b_q.shape[0], b_q.shape[1]
+    _need(b_q, "b_q", _BYTES, (l, n, k))
+    _need(a_sf, "a_sf", _BYTES, ((rows_total + 127) // 128, k // 128, 32, 16))
+    _need(b_sf, "b_sf", _BYTES, (l, n // 128, k // 128, 32, 16))
+    return _ragged("msc_grouped_gemm_mxfp8_ragged", k, a_q, a_sf, b_q, b_sf, alpha,
+                   group_offsets, group_rows, row_scale, config, out)
