@@ -7,10 +7,12 @@ CPU or PyTorch fallback behind these calls.
 from __future__ import annotations
 
 import ctypes
+import os
 import pathlib
 
 PKG = pathlib.Path(__file__).resolve().parent
-LIB_PATH = PKG / "libmosaicist_sm100a.so"
+#: MSC_LIB_PATH selects another build of the same library (e.g. one compiled with -DMSC_DEBUG)
+LIB_PATH = pathlib.Path(os.environ.get("MSC_LIB_PATH") or PKG / "libmosaicist_sm100a.so")
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_SMEM, ERR_CUDA, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5
 EPI_PLAIN, EPI_ROW_SCALE = 0, 1

@@ -41,7 +41,32 @@ struct GemmParams {
   int k_stages;              // ceil(k_bytes / 128)
   int sf_chunks;             // scale chunks along K per 128-row tile
   int raster;
+#ifdef MSC_DEBUG
+  unsigned long long* trace;  // [cta][8 tiles][3 roles][2] clock64 stamps, then [cta][2] at the end
+  int debug_flags;            // 1: skip global stores, 2: skip scale loads/copies, 4: skip MMAs
+#endif
 };
+
+#ifdef MSC_DEBUG
+static unsigned long long* g_trace = nullptr;
+static int g_debug_flags = 0;
+#define MSC_STAMP(role, tl, which)                                                        \
+  do {                                                                                    \
+    if (p.trace && (tl) < 8 && (threadIdx.x & 31) == 0)                                                            \
+      p.trace[(((size_t)blockIdx.x * 8 + (tl)) * 3 + (role)) * 2 + (which)] = clock64();  \
+  } while (0)
+#define MSC_FLAG(bit) (p.debug_flags & (bit))
+// fine stamps: [cta][32] after the per-CTA begin/end pairs; taken for tile 1, K stage 4
+#define MSC_FINE(slot)                                                                     \
+  do {                                                                                     \
+    if (p.trace && tl == 1 && kb == 4)                                                     \
+      p.trace[(size_t)gridDim.x * 50 + (size_t)blockIdx.x * 32 + (slot)] = clock64();      \
+  } while (0)
+#else
+#define MSC_FINE(slot) do {} while (0)
+#define MSC_STAMP(role, tl, which) do {} while (0)
+#define MSC_FLAG(bit) false
+#endif
 
 template <int TILE_N, int STAGES>
 struct Smem {
@@ -154,107 +179,177 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+#ifdef MSC_DEBUG
+  if (p.trace && threadIdx.x == 0) {
+    p.trace[(size_t)gridDim.x * 48 + blockIdx.x * 2] = clock64();
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    p.trace[(size_t)gridDim.x * 50 + (size_t)blockIdx.x * 32 + 30] = gt;
+  }
+#endif
 
+  // The producer and MMA warps run their loops with all 32 lanes converged and issue each
+  // asynchronous instruction from one elected lane: operands then stay warp-uniform, which
+  // is what keeps the issue cost of TMA / tcgen05 instructions low.
   if (warp == 5) {
     // ------------------------------ producer ------------------------------------
-    if (lane == 0) {
-      TileCursor cur;
-      int it = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; ok; t += gridDim.x) {
-        int mt, nt;
-        if (!cur.seek(p, ntiles, t, mt, nt)) break;
-        const int row0 = cur.off + mt * 128;
-        const int brow0 = cur.g * p.n + nt * TILE_N;
-        const uint8_t* sfa_src = p.sfa + (size_t)(row0 >> 7) * p.sf_chunks * 512;
-        const uint8_t* sfb_src =
-            p.sfb + ((size_t)cur.g * (p.n >> 7) + (size_t)nt * kSub) * p.sf_chunks * 512;
-        for (int kb = 0; kb < p.k_stages; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 1)) {
-            ok = false;
-            break;
-          }
-          const int c0 = kb * kChunksPerStage;
-          const int nch = min(kChunksPerStage, p.sf_chunks - c0);
-          const uint32_t full = bar_full + 8 * s;
-          mbar_arrive_expect_tx(full, L::kA + L::kB + (1 + kSub) * nch * 512);
-          tma_load_2d(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
-          tma_load_2d(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, brow0);
-          bulk_load_1d(sbase + L::kOffSfa + s * L::kSfa, sfa_src + (size_t)c0 * 512, nch * 512,
-                       full);
+    TileCursor cur;
+    int it = 0, tl = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok; t += gridDim.x, ++tl) {
+      int mt, nt;
+      if (!cur.seek(p, ntiles, t, mt, nt)) break;
+      const int row0 = cur.off + mt * 128;
+      const int brow0 = cur.g * p.n + nt * TILE_N;
+      const uint8_t* sfa_src = p.sfa + (size_t)(row0 >> 7) * p.sf_chunks * 512;
+      const uint8_t* sfb_src =
+          p.sfb + ((size_t)cur.g * (p.n >> 7) + (size_t)nt * kSub) * p.sf_chunks * 512;
+      MSC_STAMP(0, tl, 0);
+      for (int kb = 0; kb < p.k_stages; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (lane == 0) MSC_FINE(0);
+        ok = warp_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 1);
+        if (!ok) break;
+        if (lane == 0) MSC_FINE(1);
+        const int c0 = kb * kChunksPerStage;
+        const int nch = min(kChunksPerStage, p.sf_chunks - c0);
+        const uint32_t full = bar_full + 8 * s;
+        if (elect_one()) {
+          if (MSC_FLAG(8)) {
+            mbar_arrive(full);
+          } else {
+            mbar_arrive_expect_tx(full, L::kA + L::kB + (1 + kSub) * nch * 512);
+            tma_load_2d(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
+            tma_load_2d(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, brow0);
+            bulk_load_1d(sbase + L::kOffSfa + s * L::kSfa, sfa_src + (size_t)c0 * 512, nch * 512,
+                         full);
 #pragma unroll
-          for (int sub = 0; sub < kSub; ++sub)
-            bulk_load_1d(sbase + L::kOffSfb + s * L::kSfb + sub * 2048,
-                         sfb_src + ((size_t)sub * p.sf_chunks + c0) * 512, nch * 512, full);
+            for (int sub = 0; sub < kSub; ++sub)
+              bulk_load_1d(sbase + L::kOffSfb + s * L::kSfb + sub * 2048,
+                           sfb_src + ((size_t)sub * p.sf_chunks + c0) * 512, nch * 512, full);
+          }
+          MSC_FINE(2);
         }
+        __syncwarp();
+        if (lane == 0) MSC_FINE(3);
       }
-      if (*abort_flag) {
-        // wait (bounded) for the loads still in flight so none lands after the CTA exits
-        for (int j = max(0, it - STAGES); j < it; ++j)
-          mbar_wait_drain(bar_full + 8 * (j % STAGES), (j / STAGES) & 1);
-      }
+      MSC_STAMP(0, tl, 1);
+    }
+    if (*abort_flag && lane == 0) {
+      // wait (bounded) for the loads still in flight so none lands after the CTA exits
+      for (int j = max(0, it - STAGES); j < it; ++j)
+        mbar_wait_drain(bar_full + 8 * (j % STAGES), (j / STAGES) & 1);
     }
   } else if (warp == 4) {
     // ------------------------------ MMA issuer ----------------------------------
-    if (lane == 0) {
-      TileCursor cur;
-      int it = 0, tl = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; ok; t += gridDim.x, ++tl) {
-        int mt, nt;
-        if (!cur.seek(p, ntiles, t, mt, nt)) break;
-        const int buf = tl % kAccBufs;
-        const uint32_t aph = (tl / kAccBufs) & 1;
-        if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status, 2)) {
-          ok = false;
-          break;
+    // Per K stage the elected lane issues the scale copies, the MMAs and one commit as a
+    // straight-line block; everything that can be is hoisted out of it (stage index and
+    // parity are stepped, not divided; the next stage's barrier is probed one stage ahead)
+    // because the tensor pipe idles whenever this warp is not feeding it.
+    TileCursor cur;
+    int tl = 0;
+    uint32_t s = 0, ph = 0, slot = 0;
+    bool ok = true;
+    bool ready = mbar_test(bar_full, 0);
+    const uint64_t adesc0 = operand_desc_sw128(sbase + L::kOffA);
+    const uint64_t bdesc0 = operand_desc_sw128(sbase + L::kOffB);
+    const uint64_t sfa_d0 = scale_desc(sbase + L::kOffSfa);
+    const uint64_t sfb_d0 = scale_desc(sbase + L::kOffSfb);
+    for (int t = blockIdx.x; ok; t += gridDim.x, ++tl) {
+      int mt, nt;
+      if (!cur.seek(p, ntiles, t, mt, nt)) break;
+      const int buf = tl % kAccBufs;
+      const uint32_t aph = (tl / kAccBufs) & 1;
+      ok = warp_wait(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status, 2);
+      if (!ok) break;
+      MSC_STAMP(1, tl, 0);
+      const uint32_t acc = tmem_base + buf * TILE_N;
+      for (int kb = 0; kb < p.k_stages; ++kb) {
+        if (lane == 0) MSC_FINE(8);
+        if (!__all_sync(0xffffffffu, ready)) {
+          ok = warp_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3);
+          if (!ok) break;
         }
+        if (lane == 0) MSC_FINE(9);
+        const uint32_t s_next = (s + 1 == STAGES) ? 0u : s + 1;
+        const uint32_t ph_next = (s + 1 == STAGES) ? ph ^ 1u : ph;
+        ready = mbar_test(bar_full + 8 * s_next, ph_next);
         tc_fence_after_sync();
-        const uint32_t acc = tmem_base + buf * TILE_N;
-        for (int kb = 0; kb < p.k_stages; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait_bounded(bar_full + 8 * s, ph, abort_flag, p.status, 3)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const int c0 = kb * kChunksPerStage;
-          const int nch = min(kChunksPerStage, p.sf_chunks - c0);
-          const uint32_t sfa_t = tmem_base + kSfCol0 + (it % kSfSlots) * kSlotCols;
-          const uint32_t sfb_t = sfa_t + kSfaCols;
-          const uint32_t sfa_s = sbase + L::kOffSfa + s * L::kSfa;
-          const uint32_t sfb_s = sbase + L::kOffSfb + s * L::kSfb;
-          for (int c = 0; c < nch; ++c) {
-            tc_cp_32x128b_warpx4(sfa_t + 4 * c, scale_desc(sfa_s + c * 512));
+#ifdef MSC_DEBUG
+        if (p.trace && tl == 1 && kb < 12 && lane == 0)  // arrival cadence of tile 1's stages
+          p.trace[((size_t)blockIdx.x * 8 + 6) * 6 + kb] = clock64();
+#endif
+        const int c0 = kb * kChunksPerStage;
+        const int nch = min(kChunksPerStage, p.sf_chunks - c0);
+        const uint32_t sfa_t = tmem_base + kSfCol0 + slot * kSlotCols;
+        const uint32_t sfb_t = sfa_t + kSfaCols;
+        // descriptor low words count 16-byte units
+        const uint64_t sfa_d = sfa_d0 + s * (L::kSfa >> 4);
+        const uint64_t sfb_d = sfb_d0 + s * (L::kSfb >> 4);
+        const uint64_t adesc = adesc0 + s * (L::kA >> 4);
+        const uint64_t bdesc = bdesc0 + s * (L::kB >> 4);
+        if (lane == 0) MSC_FINE(10);
+        if (elect_one()) {
+          MSC_FINE(11);
+          if (nch == kChunksPerStage && !MSC_FLAG(2 | 4)) {
+            // full stage: +32 per 512-byte scale chunk, +128 per 2048-byte sub-tile block,
+            // +2 per 32 bytes of K inside the swizzled operand tile
 #pragma unroll
-            for (int sub = 0; sub < kSub; ++sub)
-              tc_cp_32x128b_warpx4(sfb_t + 4 * kSub * c + 4 * sub,
-                                   scale_desc(sfb_s + sub * 2048 + c * 512));
-          }
-          const uint64_t adesc = operand_desc_sw128(sbase + L::kOffA + s * L::kA);
-          const uint64_t bdesc = operand_desc_sw128(sbase + L::kOffB + s * L::kB);
-          const int nmma = (KIND == KIND_NVFP4) ? nch : 4;
-          for (int j = 0; j < nmma; ++j) {
-            const uint32_t accumulate = (kb | j) ? 1u : 0u;
-            if (KIND == KIND_NVFP4) {
-              tc_mma_nvfp4(acc, adesc + 2 * j, bdesc + 2 * j, kIdescBase, sfa_t + 4 * j,
-                           sfb_t + 4 * kSub * j, accumulate);
-            } else {
-              const uint32_t idesc = kIdescBase | (uint32_t(j) << 29) | (uint32_t(j) << 4);
-              tc_mma_mxf8(acc, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, accumulate);
+            for (int c = 0; c < kChunksPerStage; ++c) {
+              tc_cp_32x128b_warpx4(sfa_t + 4 * c, sfa_d + 32 * c);
+#pragma unroll
+              for (int sub = 0; sub < kSub; ++sub)
+                tc_cp_32x128b_warpx4(sfb_t + 4 * kSub * c + 4 * sub, sfb_d + 128 * sub + 32 * c);
+            }
+            MSC_FINE(12);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t accumulate = (j > 0 || kb > 0) ? 1u : 0u;
+              if (KIND == KIND_NVFP4) {
+                tc_mma_nvfp4(acc, adesc + 2 * j, bdesc + 2 * j, kIdescBase, sfa_t + 4 * j,
+                             sfb_t + 4 * kSub * j, accumulate);
+              } else {
+                const uint32_t idesc = kIdescBase | (uint32_t(j) << 29) | (uint32_t(j) << 4);
+                tc_mma_mxf8(acc, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, accumulate);
+              }
+            }
+          } else {
+            // last, partial K stage of an NVFP4 problem (or a debug run that skips work)
+            for (int c = 0; c < nch && !MSC_FLAG(2); ++c) {
+              tc_cp_32x128b_warpx4(sfa_t + 4 * c, sfa_d + 32 * c);
+              for (int sub = 0; sub < kSub; ++sub)
+                tc_cp_32x128b_warpx4(sfb_t + 4 * kSub * c + 4 * sub, sfb_d + 128 * sub + 32 * c);
+            }
+            MSC_FINE(12);
+            const int nmma = (KIND == KIND_NVFP4) ? nch : 4;
+            for (int j = 0; j < nmma && !MSC_FLAG(4); ++j) {
+              const uint32_t accumulate = (j > 0 || kb > 0) ? 1u : 0u;
+              if (KIND == KIND_NVFP4) {
+                tc_mma_nvfp4(acc, adesc + 2 * j, bdesc + 2 * j, kIdescBase, sfa_t + 4 * j,
+                             sfb_t + 4 * kSub * j, accumulate);
+              } else {
+                const uint32_t idesc = kIdescBase | (uint32_t(j) << 29) | (uint32_t(j) << 4);
+                tc_mma_mxf8(acc, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, accumulate);
+              }
             }
           }
+          MSC_FINE(13);
           tc_commit(bar_empty + 8 * s);  // frees the smem stage once these MMAs have read it
+          MSC_FINE(14);
         }
-        if (ok) tc_commit(bar_acc_full + 8 * buf);
+        if (lane == 0) MSC_FINE(15);
+        s = s_next;
+        ph = ph_next;
+        slot = (slot + 1 == kSfSlots) ? 0u : slot + 1;
       }
-      if (*abort_flag) {
-        tc_commit(bar_drain);
-        mbar_wait_drain(bar_drain, 0);
-      }
+      if (ok && elect_one()) tc_commit(bar_acc_full + 8 * buf);
+      MSC_STAMP(1, tl, 1);
+    }
+    __syncwarp();
+    if (*abort_flag && lane == 0) {
+      tc_commit(bar_drain);
+      mbar_wait_drain(bar_drain, 0);
     }
   } else {
     // ------------------------------ epilogue ------------------------------------
@@ -266,10 +361,13 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!cur.seek(p, ntiles, t, mt, nt)) break;
       const int buf = tl % kAccBufs;
       const uint32_t aph = (tl / kAccBufs) & 1;
-      bool ok = mbar_wait_bounded(bar_acc_full + 8 * buf, aph, abort_flag, p.status, 4);
+      // one lane per warp waits; the others park on the warp vote instead of polling
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait_bounded(bar_acc_full + 8 * buf, aph, abort_flag, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (warp == 0) MSC_STAMP(2, tl, 0);
       const int row_local = mt * 128 + warp * 32 + lane;
       const bool valid = row_local < cur.rows;
       const size_t out_row = (size_t)cur.off + row_local;
@@ -281,7 +379,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + lane_base + buf * TILE_N + c * 32, v);
         tmem_ld_wait();
-        if (valid) {
+        if (valid && !MSC_FLAG(1)) {
           uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -300,11 +398,20 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+      if (warp == 0) MSC_STAMP(2, tl, 1);
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
+#ifdef MSC_DEBUG
+  if (p.trace && threadIdx.x == 0) {
+    p.trace[(size_t)gridDim.x * 48 + blockIdx.x * 2 + 1] = clock64();
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    p.trace[(size_t)gridDim.x * 50 + (size_t)blockIdx.x * 32 + 31] = gt;
+  }
+#endif
   if (warp == 0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
@@ -402,6 +509,10 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   p.k_stages = (int)((k_bytes + 127) / 128);
   p.sf_chunks = k / chunk_elems;
   p.raster = cfg.raster ? 1 : 0;
+#ifdef MSC_DEBUG
+  p.trace = g_trace;
+  p.debug_flags = g_debug_flags;
+#endif
 
   const long long max_tiles = ((rows_total + 127) / 128 + l) * (long long)(n / tile_n);
   int grid = cfg.max_ctas > 0 ? cfg.max_ctas : num_sms();
@@ -420,6 +531,15 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
 }  // namespace msc
 
 extern "C" {
+
+#ifdef MSC_DEBUG
+// Debug builds only: device buffer for per-tile clock stamps and pipeline-stage skip flags.
+int msc_debug_config(void* trace, int flags) {
+  msc::g_trace = static_cast<unsigned long long*>(trace);
+  msc::g_debug_flags = flags;
+  return MSC_OK;
+}
+#endif
 
 int msc_grouped_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const void* b_sf,
                            const float* alpha, const int32_t* masked_m, void* out, int l, int m,

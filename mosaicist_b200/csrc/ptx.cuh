@@ -38,12 +38,32 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One potentially-blocking probe: the hardware suspends the thread until the phase
+// completes or about `hint_ns` nanoseconds pass, so a waiting thread does not spin on
+// shared memory while TMA writes and the tensor pipe reads use it.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity,
+                                              uint32_t hint_ns = 20000u) {
   uint32_t ok;
   asm volatile(
       "{\n"
       " .reg .pred p;\n"
-      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+// Non-blocking probe of a phase.  Issued one iteration ahead of its use so the barrier's
+// read latency overlaps other work.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
       " selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
@@ -70,6 +90,27 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
       return false;
     }
   }
+}
+
+// The same wait made by all 32 lanes of a converged warp, with a warp-uniform result.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity,
+                                          volatile uint32_t* abort_flag, int* status, int code) {
+  const bool ok = mbar_wait_bounded(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n"
+      " .reg .b32 rx;\n"
+      " .reg .pred px;\n"
+      " elect.sync rx|px, 0xffffffff;\n"
+      " @px mov.s32 %0, 1;\n"
+      "}\n"
+      : "+r"(pred));
+  return pred != 0;
 }
 
 // Exit-path drain: waits for a phase regardless of the abort flag, with a short budget.
