@@ -100,6 +100,40 @@ int msc_grouped_gemm_mxfp8_ragged(const void* a_q, const void* a_sf, const void*
                                   const float* row_scale, void* out, int l, int rows_total,
                                   int n, int k, const msc_gemm_cfg* cfg, void* stream);
 
+/* NVFP4 quantisation of activations: q = e2m1, one e4m3 scale per 16 K-elements,
+ *   sf = e4m3(clip(amax/6 * gs, 0, 448)),  q = e2m1_rne(clip(x / (f32(sf)/gs), -6, 6)).
+ * Replaces quantize_nvfp4 (experiments/flashinfer-megamoe-sm100a/nvfp4.py:39-57) and its
+ * kernel quantize_nvfp4_pallas (quantize_kernels.py:119-159).
+ *   x (l, m, k) bf16 (x_dtype 0) or fp32 (x_dtype 1); global_scale (l) fp32;
+ *   masked_m (l) int32 or NULL: rows >= masked_m[g] are skipped;
+ *   q (l, m, k/2) bytes; sf either row-major (l, m, k/16) (sf_layout 0, what the reference
+ *   kernel writes) or already in the MMA tiling (l, m/128, k/64, 32, 16) (sf_layout 1, which
+ *   removes the reference's separate re-tiling pass, moe.py:44).  Requires k % 64 == 0. */
+int msc_nvfp4_quantize(const void* x, int x_dtype, const float* global_scale,
+                       const int32_t* masked_m, void* q, void* sf, int sf_layout, int l, int m,
+                       int k, void* stream);
+
+/* SiLU(gate) * up in fp32 followed by the same quantiser; gate is the first n columns of
+ * gateup (l, m, 2n) bf16.  Replaces silu_mul + quantize_nvfp4 (nvfp4.py:81-88, 39-57) and the
+ * kernel silu_mul_quantize_nvfp4_pallas (quantize_kernels.py:162-213).  q (l, m, n/2). */
+int msc_nvfp4_silu_mul_quantize(const void* gateup, const float* global_scale,
+                                const int32_t* masked_m, void* q, void* sf, int sf_layout, int l,
+                                int m, int n, void* stream);
+
+/* The same two quantisers over row-concatenated groups (see msc_grouped_gemm_nvfp4_ragged):
+ * x (rows_total, k) or, with silu != 0, (rows_total, 2k) bf16; scales always in the MMA tiling
+ * (ceil(rows_total/128), k/64, 32, 16).  Rows outside every group are skipped. */
+int msc_nvfp4_quantize_ragged(const void* x, int x_dtype, const float* global_scale,
+                              const int32_t* group_offsets, const int32_t* group_rows, void* q,
+                              void* sf, int l, int rows_total, int k, int silu, void* stream);
+
+/* Scale-factor re-tiling: (groups, mn, k_scales) row-major bytes -> (groups, ceil(mn/128),
+ * k_scales/4, 32, 16) with zero padding rows; element (row = 128t + 32a + b, col = 4c + d)
+ * lands at [t, c, b, 4a + d].  Replaces to_mma_scale_layout (nvfp4.py:121-131).  Works for
+ * e4m3 and ue8m0 scale bytes alike.  Requires k_scales % 4 == 0. */
+int msc_sf_swizzle(const void* sf_rowmajor, void* sf_tiled, int groups, int mn, int k_scales,
+                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,6 +42,10 @@ SIGNATURES = {
     "msc_grouped_gemm_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),
     "msc_grouped_gemm_nvfp4_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),
     "msc_grouped_gemm_mxfp8_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),
+    "msc_nvfp4_quantize": (_I, [_P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "msc_nvfp4_silu_mul_quantize": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "msc_nvfp4_quantize_ragged": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "msc_sf_swizzle": (_I, [_P, _P, _I, _I, _I, _P]),
 }
 
 _lib = None

@@ -20,7 +20,7 @@ PTX = PKG / "libmosaicist_sm100a.ptx"
 PTXAS_LOG = PKG / "libmosaicist_sm100a.ptxas.log"
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-COMMON = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math"]
+COMMON = ["-O3", "-std=c++17", "-lineinfo"]
 
 
 def sources() -> list[pathlib.Path]:

@@ -1,0 +1,266 @@
+// NVFP4 quantisation kernels (HBM-bound): activations -> packed e2m1 + one e4m3 scale per
+// 16 K-elements, with the scales written either row-major or directly in the 128-row MMA
+// tiling the GEMM reads; SiLU(gate)*up fused in front of the same quantiser; and the
+// stand-alone scale re-tiling kernel.
+//
+// Arithmetic follows quantize_nvfp4 (experiments/flashinfer-megamoe-sm100a/nvfp4.py:39-57):
+//   sf   = e4m3( clip(amax / 6 * gs, 0, 448) )        per block of 16
+//   step = f32(sf) / gs
+//   q    = e2m1_rne( clip(x / step, -6, 6) )           (0 when step == 0)
+// every operation in IEEE fp32 (explicit _rn intrinsics, so no contraction or approximate
+// division can change a rounding).  One thread owns four consecutive blocks (64
+// elements: 128 B of bf16 in, 32 B of e2m1 and 4 scale bytes out), so a warp reads 4 KB of
+// one row contiguously and the four scale bytes of a thread are one aligned 32-bit word in
+// both scale layouts.
+#include "host_common.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+namespace msc {
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t b) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
+  return __half2float(__half(h));
+}
+
+// Offset of scale (row, kblock/4 word) in the tiled layout (row_tiles, kwords, 32, 16):
+// row = 128 t + 32 a + b  ->  [t, c, b, 4 a + d], d = kblock % 4.
+__device__ __forceinline__ size_t tiled_sf_word(int row, int kword, int kwords) {
+  const int t = row >> 7, a = (row >> 5) & 3, b = row & 31;
+  return (((size_t)t * kwords + kword) * 32 + b) * 16 + 4 * a;
+}
+
+// Quantises 64 fp32 values held as v[64] into 32 bytes + 4 scale bytes.
+__device__ __forceinline__ void quantize_64(const float* v, float gs, uint32_t* q8, uint32_t& sf4) {
+  sf4 = 0;
+#pragma unroll
+  for (int blk = 0; blk < 4; ++blk) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[blk * 16 + i]));
+    float s = __fmul_rn(__fdiv_rn(amax, 6.0f), gs);
+    s = fminf(fmaxf(s, 0.0f), 448.0f);
+    const uint8_t sfb = (uint8_t)__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
+    const float step = __fdiv_rn(e4m3_to_float(sfb), gs);
+    // a dead block (step == 0) keeps the sign of x: x / 1 * 0 = +-0, as the reference computes
+    const float live = (step > 0.0f) ? 1.0f : 0.0f;
+    const float safe = (step == 0.0f) ? 1.0f : step;
+    sf4 |= (uint32_t)sfb << (8 * blk);
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int pr = 0; pr < 4; ++pr) {
+        const int i = blk * 16 + w * 8 + pr * 2;
+        float x0 = __fmul_rn(__fdiv_rn(v[i], safe), live);
+        float x1 = __fmul_rn(__fdiv_rn(v[i + 1], safe), live);
+        x0 = fminf(fmaxf(x0, -6.0f), 6.0f);
+        x1 = fminf(fmaxf(x1, -6.0f), 6.0f);
+        const __nv_fp4x2_storage_t b2 =
+            __nv_cvt_float2_to_fp4x2(make_float2(x0, x1), __NV_E2M1, cudaRoundNearest);
+        word |= (uint32_t)b2 << (8 * pr);
+      }
+      q8[blk * 2 + w] = word;
+    }
+  }
+}
+
+struct QuantParams {
+  const void* x;            // (rows_total, k) or, with silu, (rows_total, 2k)
+  const float* gs;          // (l) per-group global scale
+  const int* group_rows;    // (l) or null
+  const int* group_offsets; // (l) or null
+  uint8_t* q;               // (rows_total, k/2)
+  uint8_t* sf;
+  int l, m_stride, k;
+  long long rows_total;
+  int tiled, silu, f32_in;
+};
+
+// Group of a row in the ragged layout: linear scan over at most a few hundred groups.
+__device__ __forceinline__ int group_of_row(const QuantParams& p, long long row, bool& valid) {
+  if (!p.group_offsets) {
+    const int g = (int)(row / p.m_stride);
+    const int r = (int)(row - (long long)g * p.m_stride);
+    valid = !p.group_rows || r < __ldg(p.group_rows + g);
+    return g;
+  }
+  for (int g = 0; g < p.l; ++g) {
+    const int off = __ldg(p.group_offsets + g);
+    const int n = __ldg(p.group_rows + g);
+    if (row >= off && row < (long long)off + n) {
+      valid = true;
+      return g;
+    }
+  }
+  valid = false;
+  return 0;
+}
+
+__global__ void __launch_bounds__(256) nvfp4_quantize_kernel(const QuantParams p) {
+  const int kwords = p.k >> 6;  // 64-element units per row
+  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = unit / kwords;
+  const int kw = (int)(unit - row * kwords);
+  if (row >= p.rows_total) return;
+  bool valid;
+  const int g = group_of_row(p, row, valid);
+  if (!valid) return;
+  const float gs = __ldg(p.gs + g);
+
+  float v[64];
+  if (p.silu) {
+    // row holds [gate (k) | up (k)] in bf16; activation stays fp32 (nvfp4.py:81-88)
+    const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.x) + row * 2 * p.k + kw * 64;
+    const uint4* g4 = reinterpret_cast<const uint4*>(base);
+    const uint4* u4 = reinterpret_cast<const uint4*>(base + p.k);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 gv = __ldg(g4 + i), uv = __ldg(u4 + i);
+      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+      const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 gf = __bfloat1622float2(gp[j]), uf = __bfloat1622float2(up[j]);
+        const float s0 = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gf.x)));
+        const float s1 = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gf.y)));
+        v[i * 8 + j * 2] = __fmul_rn(__fmul_rn(s0, gf.x), uf.x);
+        v[i * 8 + j * 2 + 1] = __fmul_rn(__fmul_rn(s1, gf.y), uf.y);
+      }
+    }
+  } else if (p.f32_in) {
+    const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + row * p.k + kw * 64);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float4 f = __ldg(src + i);
+      v[i * 4] = f.x; v[i * 4 + 1] = f.y; v[i * 4 + 2] = f.z; v[i * 4 + 3] = f.w;
+    }
+  } else {
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.x) + row * p.k + kw * 64);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 raw = __ldg(src + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        v[i * 8 + j * 2] = f.x;
+        v[i * 8 + j * 2 + 1] = f.y;
+      }
+    }
+  }
+
+  uint32_t q8[8], sf4;
+  quantize_64(v, gs, q8, sf4);
+  uint4* qdst = reinterpret_cast<uint4*>(p.q + row * (p.k >> 1) + kw * 32);
+  qdst[0] = make_uint4(q8[0], q8[1], q8[2], q8[3]);
+  qdst[1] = make_uint4(q8[4], q8[5], q8[6], q8[7]);
+  if (p.tiled)
+    *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word((int)row, kw, kwords)) = sf4;
+  else
+    *reinterpret_cast<uint32_t*>(p.sf + row * (p.k >> 4) + kw * 4) = sf4;
+}
+
+// (groups, mn, kwords*4) row-major scale bytes -> (groups, ceil(mn/128), kwords, 32, 16),
+// padding rows zero.  One thread per 32-bit word of the output.
+__global__ void __launch_bounds__(256)
+sf_swizzle_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int groups, int mn,
+                  int kwords) {
+  const int tiles = (mn + 127) >> 7;
+  const long long total = (long long)groups * tiles * kwords * 128;
+  const long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (w >= total) return;
+  // w enumerates [g][t][c][b][a]: consecutive threads write consecutive words
+  const int a = (int)(w & 3);
+  const int b = (int)((w >> 2) & 31);
+  long long rest = w >> 7;
+  const int c = (int)(rest % kwords);
+  rest /= kwords;
+  const int t = (int)(rest % tiles);
+  const int g = (int)(rest / tiles);
+  const int row = t * 128 + a * 32 + b;
+  uint32_t val = 0;
+  if (row < mn)
+    val = __ldg(reinterpret_cast<const uint32_t*>(src + ((size_t)g * mn + row) * kwords * 4) + c);
+  reinterpret_cast<uint32_t*>(dst)[w] = val;
+}
+
+static int quantize_common(const void* x, int x_dtype, const float* gs, const int32_t* group_offsets,
+                           const int32_t* group_rows, void* q, void* sf, int sf_layout, int l,
+                           long long rows_total, int m_stride, int k, int silu, void* stream) {
+  if (!x || !gs || !q || !sf) return fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (l <= 0 || rows_total <= 0 || k <= 0) return fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (k % 64) return fail(MSC_ERR_BAD_ARG, "k=%d must be a multiple of 64", k);
+  if (x_dtype != 0 && x_dtype != 1) return fail(MSC_ERR_UNSUPPORTED, "x_dtype must be 0 (bf16) or 1 (f32)");
+  if (silu && x_dtype != 0) return fail(MSC_ERR_UNSUPPORTED, "the fused SiLU form takes bf16 input");
+  if (sf_layout != 0 && sf_layout != 1) return fail(MSC_ERR_BAD_ARG, "sf_layout must be 0 or 1");
+  if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(q) % 16 ||
+      reinterpret_cast<uintptr_t>(sf) % 4)
+    return fail(MSC_ERR_BAD_ARG, "x and q must be 16-byte aligned, sf 4-byte aligned");
+  QuantParams p;
+  p.x = x; p.gs = gs; p.group_rows = group_rows; p.group_offsets = group_offsets;
+  p.q = static_cast<uint8_t*>(q); p.sf = static_cast<uint8_t*>(sf);
+  p.l = l; p.m_stride = m_stride; p.k = k; p.rows_total = rows_total;
+  p.tiled = sf_layout; p.silu = silu; p.f32_in = x_dtype;
+  const long long units = rows_total * (k / 64);
+  const int threads = 256;
+  const long long blocks = (units + threads - 1) / threads;
+  if (blocks > 0x7fffffffLL) return fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
+  nvfp4_quantize_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+}  // namespace msc
+
+extern "C" {
+
+int msc_nvfp4_quantize(const void* x, int x_dtype, const float* global_scale,
+                       const int32_t* masked_m, void* q, void* sf, int sf_layout, int l, int m,
+                       int k, void* stream) {
+  if (m <= 0) return msc::fail(MSC_ERR_BAD_ARG, "m must be positive");
+  if (sf_layout == 1 && m % 128)
+    return msc::fail(MSC_ERR_BAD_ARG, "tiled scales need m %% 128 == 0 in the masked layout");
+  return msc::quantize_common(x, x_dtype, global_scale, nullptr, masked_m, q, sf, sf_layout, l,
+                              (long long)l * m, m, k, 0, stream);
+}
+
+int msc_nvfp4_silu_mul_quantize(const void* gateup, const float* global_scale,
+                                const int32_t* masked_m, void* q, void* sf, int sf_layout, int l,
+                                int m, int n, void* stream) {
+  if (m <= 0) return msc::fail(MSC_ERR_BAD_ARG, "m must be positive");
+  if (sf_layout == 1 && m % 128)
+    return msc::fail(MSC_ERR_BAD_ARG, "tiled scales need m %% 128 == 0 in the masked layout");
+  return msc::quantize_common(gateup, 0, global_scale, nullptr, masked_m, q, sf, sf_layout, l,
+                              (long long)l * m, m, n, 1, stream);
+}
+
+int msc_nvfp4_quantize_ragged(const void* x, int x_dtype, const float* global_scale,
+                              const int32_t* group_offsets, const int32_t* group_rows, void* q,
+                              void* sf, int l, int rows_total, int k, int silu, void* stream) {
+  if (!group_offsets || !group_rows)
+    return msc::fail(MSC_ERR_BAD_ARG, "group_offsets and group_rows are required");
+  return msc::quantize_common(x, x_dtype, global_scale, group_offsets, group_rows, q, sf, 1, l,
+                              rows_total, 0, k, silu, stream);
+}
+
+int msc_sf_swizzle(const void* sf_rowmajor, void* sf_tiled, int groups, int mn, int k_scales,
+                   void* stream) {
+  if (!sf_rowmajor || !sf_tiled) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (groups <= 0 || mn <= 0 || k_scales <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (k_scales % 4) return msc::fail(MSC_ERR_BAD_ARG, "k_scales=%d must be a multiple of 4", k_scales);
+  if (reinterpret_cast<uintptr_t>(sf_rowmajor) % 4 || reinterpret_cast<uintptr_t>(sf_tiled) % 4)
+    return msc::fail(MSC_ERR_BAD_ARG, "scale pointers must be 4-byte aligned");
+  const int kwords = k_scales / 4;
+  const long long total = (long long)groups * ((mn + 127) / 128) * kwords * 128;
+  const long long blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
+  msc::sf_swizzle_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(sf_rowmajor), static_cast<uint8_t*>(sf_tiled), groups, mn, kwords);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+}  // extern "C"

@@ -130,3 +130,74 @@ def ragged_grouped_gemm_mxfp8(a_q, a_sf, b_q, b_sf, group_offsets, group_rows, a
     _need(b_sf, "b_sf", _BYTES, (l, n // 128, k // 128, 32, 16))
     return _ragged("msc_grouped_gemm_mxfp8_ragged", k, a_q, a_sf, b_q, b_sf, alpha,
                    group_offsets, group_rows, row_scale, config, out)
+
+
+def quantize_nvfp4(x, global_scale, masked_m=None, tiled_scales: bool = True):
+    """(l, m, k) bf16/f32 -> (q (l, m, k/2) packed e2m1, sf e4m3).  Arithmetic of
+    quantize_nvfp4 (nvfp4.py:39-57) / quantize_nvfp4_pallas (quantize_kernels.py:119).
+    With tiled_scales the scales come out in the MMA tiling (l, m/128, k/64, 32, 16),
+    otherwise row-major (l, m, k/16) as the reference kernel writes them.  Rows at or
+    beyond masked_m[l] are left untouched."""
+    _need(x, "x", (torch.bfloat16, torch.float32))
+    l, m, k = x.shape
+    _need(global_scale, "global_scale", (torch.float32,), (l,))
+    if masked_m is not None:
+        _need(masked_m, "masked_m", (torch.int32,), (l,))
+    q = torch.empty((l, m, k // 2), dtype=torch.uint8, device=x.device)
+    shape = (l, m // 128, k // 64, 32, 16) if tiled_scales else (l, m, k // 16)
+    sf = torch.zeros(shape, dtype=torch.uint8, device=x.device)
+    _lib.check(_lib.load().msc_nvfp4_quantize(
+        _ptr(x), 0 if x.dtype == torch.bfloat16 else 1, _ptr(global_scale), _ptr(masked_m),
+        _ptr(q), _ptr(sf), 1 if tiled_scales else 0, l, m, k, _stream()))
+    return q, sf
+
+
+def silu_mul_quantize_nvfp4(gateup, global_scale, masked_m=None, tiled_scales: bool = True):
+    """(l, m, 2n) bf16 -> NVFP4 of silu(gate) * up, gate = first n columns, activation kept in
+    fp32 up to the quantiser (nvfp4.py:81-88; silu_mul_quantize_nvfp4_pallas,
+    quantize_kernels.py:162)."""
+    _need(gateup, "gateup", (torch.bfloat16,))
+    l, m, n2 = gateup.shape
+    n = n2 // 2
+    _need(global_scale, "global_scale", (torch.float32,), (l,))
+    if masked_m is not None:
+        _need(masked_m, "masked_m", (torch.int32,), (l,))
+    q = torch.empty((l, m, n // 2), dtype=torch.uint8, device=gateup.device)
+    shape = (l, m // 128, n // 64, 32, 16) if tiled_scales else (l, m, n // 16)
+    sf = torch.zeros(shape, dtype=torch.uint8, device=gateup.device)
+    _lib.check(_lib.load().msc_nvfp4_silu_mul_quantize(
+        _ptr(gateup), _ptr(global_scale), _ptr(masked_m), _ptr(q), _ptr(sf),
+        1 if tiled_scales else 0, l, m, n, _stream()))
+    return q, sf
+
+
+def quantize_nvfp4_ragged(x, global_scale, group_offsets, group_rows, silu: bool = False):
+    """Ragged-layout quantiser: x (rows_total, k) -> q (rows_total, k/2) and tiled scales
+    (ceil(rows_total/128), k/64, 32, 16); with silu, x is (rows_total, 2k) gate|up."""
+    _need(x, "x", (torch.bfloat16, torch.float32))
+    rows_total = x.shape[0]
+    k = x.shape[1] // 2 if silu else x.shape[1]
+    l = global_scale.shape[0]
+    _need(global_scale, "global_scale", (torch.float32,), (l,))
+    _need(group_offsets, "group_offsets", (torch.int32,), (l,))
+    _need(group_rows, "group_rows", (torch.int32,), (l,))
+    q = torch.empty((rows_total, k // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.zeros(((rows_total + 127) // 128, k // 64, 32, 16), dtype=torch.uint8, device=x.device)
+    _lib.check(_lib.load().msc_nvfp4_quantize_ragged(
+        _ptr(x), 0 if x.dtype == torch.bfloat16 else 1, _ptr(global_scale), _ptr(group_offsets),
+        _ptr(group_rows), _ptr(q), _ptr(sf), l, rows_total, k, 1 if silu else 0, _stream()))
+    return q, sf
+
+
+def to_mma_scale_layout(sf):
+    """(groups, mn, k_scales) row-major scale bytes -> (groups, ceil(mn/128), k_scales/4, 32, 16)
+    (a 2-D input is treated as one group and returns 4-D), as to_mma_scale_layout
+    (nvfp4.py:121-131)."""
+    _need(sf, "sf", _BYTES)
+    squeeze = sf.dim() == 2
+    if squeeze:
+        sf = sf.unsqueeze(0)
+    g, mn, ks = sf.shape
+    out = torch.empty((g, (mn + 127) // 128, ks // 4, 32, 16), dtype=sf.dtype, device=sf.device)
+    _lib.check(_lib.load().msc_sf_swizzle(_ptr(sf), _ptr(out), g, mn, ks, _stream()))
+    return out[0] if squeeze else out

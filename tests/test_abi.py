@@ -1,0 +1,123 @@
+"""CPU checks of the drop-in boundary: the shared library loads, exports every symbol the
+header declares, rejects bad arguments before touching CUDA, and the capture modules keep
+the reference's candidate-module contract.  No GPU work happens here."""
+
+import ctypes
+import json
+import pathlib
+import re
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from mosaicist_b200 import build
+
+    build.build()
+    from mosaicist_b200 import _lib
+
+    return _lib.load()
+
+
+def _declared():
+    text = "".join(p.read_text() for p in sorted((ROOT / "include").glob("*.h")))
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(msc_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(lib):
+    from mosaicist_b200 import _lib
+
+    names = _declared()
+    assert len(names) >= 11
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == names
+    assert lib.msc_version() >= 1
+    assert lib.msc_ptx_path().decode().endswith("libmosaicist_sm100a.ptx")
+    assert pathlib.Path(lib.msc_ptx_path().decode()).exists()
+
+
+def test_bad_arguments_are_rejected_with_a_message(lib):
+    from mosaicist_b200 import _lib
+
+    cfg = _lib.GemmCfg()
+    one = ctypes.c_void_p(16)  # non-null, aligned; never dereferenced on these paths
+    rc = lib.msc_grouped_gemm_nvfp4(None, one, one, one, None, None, one, 1, 128, 128, 64, cfg, None)
+    assert rc == _lib.ERR_BAD_ARG and b"NULL" in lib.msc_last_error()
+    rc = lib.msc_grouped_gemm_nvfp4(one, one, one, one, None, None, one, 1, 100, 128, 64, cfg, None)
+    assert rc == _lib.ERR_BAD_ARG and b"multiple of 128" in lib.msc_last_error()
+    rc = lib.msc_grouped_gemm_nvfp4(one, one, one, one, None, None, one, 1, 128, 128, 48, cfg, None)
+    assert rc == _lib.ERR_BAD_ARG and b"k=48" in lib.msc_last_error()
+    cfg.tile_n = 64
+    rc = lib.msc_grouped_gemm_nvfp4(one, one, one, one, None, None, one, 1, 128, 128, 64, cfg, None)
+    assert rc == _lib.ERR_UNSUPPORTED
+    cfg.tile_n = 256
+    rc = lib.msc_grouped_gemm_nvfp4(one, one, one, one, None, None, one, 1, 128, 384, 64, cfg, None)
+    assert rc == _lib.ERR_BAD_ARG and b"tile_n" in lib.msc_last_error()
+    rc = lib.msc_grouped_gemm_nvfp4_ragged(one, one, one, one, None, None, None, None, one, 1, 128,
+                                           128, 64, None, None)
+    assert rc == _lib.ERR_BAD_ARG and b"group_offsets" in lib.msc_last_error()
+    rc = lib.msc_grouped_gemm_mxfp8_ragged(one, one, one, one, None, one, one, None, one, 1, 128,
+                                           128, 96, None, None)
+    assert rc == _lib.ERR_BAD_ARG
+    rc = lib.msc_nvfp4_quantize(one, 0, one, None, one, one, 0, 1, 128, 100, None)
+    assert rc == _lib.ERR_BAD_ARG and b"multiple of 64" in lib.msc_last_error()
+    rc = lib.msc_sf_swizzle(one, one, 1, 128, 6, None)
+    assert rc == _lib.ERR_BAD_ARG
+    with pytest.raises(_lib.MscError) as e:
+        _lib.check(rc)
+    assert e.value.code == _lib.ERR_BAD_ARG
+
+
+def test_candidate_module_contract(monkeypatch):
+    import importlib
+
+    m = importlib.import_module("mosaicist_b200.candidates.cand_cuda_gemm")
+    assert callable(m.build) and callable(m.reference)
+    assert all(isinstance(v, list) and v for v in m.KNOBS.values())
+    assert {k: v[0] for k, v in m.KNOBS.items()} == m.DEFAULTS     # first value is the default
+    assert set(m.STRUCTURAL) <= set(m.KNOBS)
+    from mosaicist_b200.candidates._common import from_env
+
+    monkeypatch.setenv("MOSAICIST_KNOBS", json.dumps({"tile_n": 256}))
+    assert from_env(m.DEFAULTS)["tile_n"] == 256 and from_env(m.DEFAULTS)["stages"] == 0
+    spec = json.loads((ROOT / "mosaicist_b200/candidates/spec_nvfp4_gemm.json").read_text())
+    assert spec["dims"] == {"l": m.L, "m": m.M, "n": m.N, "k": m.K}
+    assert spec["out_dtype"] == "bfloat16"
+
+
+def test_candidate_module_against_reference_harness(monkeypatch):
+    """When the reference checkout is present, its own loader and knob space accept the
+    module unchanged."""
+    ref = pathlib.Path("/root/reference/src")
+    if not ref.exists():
+        pytest.skip("reference checkout not present")
+    monkeypatch.syspath_prepend(str(ref))
+    from mosaicist.capture import load_build
+    from mosaicist.converge.knobs import KnobSpace
+    import mosaicist_b200.candidates.cand_cuda_gemm as m
+
+    assert load_build("mosaicist_b200.candidates.cand_cuda_gemm") is m.build
+    assert KnobSpace.from_module(m).default() == m.DEFAULTS
+
+
+def test_byte_decoders_match_ml_dtypes():
+    import ml_dtypes
+    import numpy as np
+
+    from mosaicist_b200 import formats as F
+    from oracle import nvfp4 as O
+
+    allb = np.arange(256, dtype=np.uint8)
+    assert np.array_equal(F.E4M3_LUT, allb.view(ml_dtypes.float8_e4m3fn).astype(np.float64), equal_nan=True)
+    assert np.array_equal(F.E2M1_LUT, np.arange(16, dtype=np.uint8).view(ml_dtypes.float4_e2m1fn).astype(np.float64))
+    rng = np.random.default_rng(3)
+    q, sf = O.exact_operands(rng, 1, 200, 128)
+    got = F.dequant_nvfp4(O.pack_e2m1(q[0]), O.e4m3_bytes(O.to_mma_scale_layout(sf[0])))
+    want = q[0].astype(np.float64) * np.repeat(sf[0].astype(np.float64), 16, axis=-1)
+    assert np.array_equal(got, want)

@@ -1,0 +1,231 @@
+"""Parity of the CUDA block-scaled grouped GEMM with the CPU oracle, through the C ABI.
+
+Mirrors the reference's kernel tests (experiments/flashinfer-megamoe-sm100a/
+test_kernels.py:28-92, verify_b200.py:53-87): exact operands must agree bit for bit,
+random operands within tolerance, masked rows are compared only below masked_m, and every
+comparison proves it is non-trivial.  Tolerance for bf16 outputs against the float64
+oracle: |err| <= 2^-7 |ref| + 1e-3 rms(ref); the reference's own quantile gate must pass
+too."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gate, mxfp8 as X, nvfp4 as O
+
+pytestmark = pytest.mark.gpu
+
+
+def T(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _nontrivial(want):
+    w = np.asarray(want, np.float64)
+    assert np.count_nonzero(w) >= 0.5 * w.size and (w.max() - w.min()) >= 1e-3   # verify_b200.py:55-61
+
+
+def run_masked(a_q, a_sf, b_q, b_sf, alpha, masked_m, cfg):
+    from mosaicist_b200 import _lib, ops
+
+    l, m, _ = a_q.shape
+    n = b_q.shape[1]
+    out = torch.full((l, m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.masked_grouped_gemm(T(O.pack_e2m1(a_q)), T(O.e4m3_bytes(O.retile(a_sf))),
+                            T(O.pack_e2m1(b_q)), T(O.e4m3_bytes(O.retile(b_sf))),
+                            None if alpha is None else T(alpha),
+                            None if masked_m is None else T(masked_m), cfg, out=out)
+    assert _lib.status_word() == 0
+    return out.float().cpu().numpy()
+
+
+def _cfg(**kw):
+    from mosaicist_b200 import ops
+
+    return ops.GemmConfig(**kw)
+
+
+EXACT_CASES = [
+    # l, m, n, k, config                       (first two: test_kernels.py:78-83)
+    (2, 256, 256, 512, {}),
+    (3, 128, 256, 1024, {}),
+    (1, 128, 128, 64, {}),                     # a single MMA
+    (2, 256, 512, 576, {"stages": 2}),         # partial last K stage, shallow ring
+    (2, 256, 256, 512, {"tile_n": 256}),
+    (2, 256, 512, 4096, {"tile_n": 256, "stages": 3, "raster": 1}),   # verify_b200.py k=4096
+    (5, 384, 384, 320, {"max_ctas": 7}),       # more tiles than CTAs: persistent loop
+    (2, 128, 256, 2048, {"stages": 6, "raster": 1}),
+]
+
+
+@pytest.mark.parametrize("l,m,n,k,cfg", EXACT_CASES)
+@pytest.mark.parametrize("seed", [0, 1])
+def test_exact_operands_bit_exact(l, m, n, k, cfg, seed):
+    rng = np.random.default_rng([seed, l, m, n, k])
+    a_q, a_sf = O.exact_operands(rng, l, m, k)
+    b_q, b_sf = O.exact_operands(rng, l, n, k)
+    alpha = np.exp2(rng.integers(-1, 2, l)).astype(np.float32)
+    masked_m = np.array(([m, max(1, m // 2 - 3)] + [m] * l)[:l], np.int32)   # test_kernels.py:50
+    got = run_masked(a_q, a_sf, b_q, b_sf, alpha, masked_m, _cfg(**cfg))
+    want = O.bf16_round(O.grouped_gemm_f64(a_q, a_sf, b_q, b_sf, alpha, masked_m))
+    rows = np.arange(m)[None, :, None] < masked_m[:, None, None]
+    _nontrivial(want[0])
+    assert np.array_equal(np.where(rows, got, 0), want)
+    # rows at or beyond masked_m are never written
+    assert np.isnan(got[~np.broadcast_to(rows, got.shape)]).all()
+
+
+def test_edge_groups_empty_and_single_row():
+    l, m, n, k = 4, 256, 128, 256
+    rng = np.random.default_rng(7)
+    a_q, a_sf = O.exact_operands(rng, l, m, k)
+    b_q, b_sf = O.exact_operands(rng, l, n, k)
+    masked_m = np.array([0, 1, 256, 129], np.int32)
+    got = run_masked(a_q, a_sf, b_q, b_sf, None, masked_m, _cfg())
+    want = O.bf16_round(O.grouped_gemm_f64(a_q, a_sf, b_q, b_sf, None, masked_m))
+    rows = np.arange(m)[None, :, None] < masked_m[:, None, None]
+    assert np.array_equal(np.where(rows, got, 0), want)
+    assert np.isnan(got[0]).all()
+
+
+@pytest.mark.parametrize("cfg", [{}, {"tile_n": 256}])
+def test_random_operands_within_tolerance_and_gate(cfg):
+    """Seeded N(0,1) operands quantised by the oracle with gs = 64 (test_kernels.py:43-48)."""
+    l, m, n, k = 2, 256, 256, 512
+    a = np.random.default_rng([0, 0]).standard_normal((l, m, k)).astype(np.float32)
+    b = np.random.default_rng([0, 1]).standard_normal((l, n, k)).astype(np.float32)
+    gs = np.full((l,), 64.0, np.float32)
+    a_q, a_sf = O.quantize_nvfp4(a, gs)
+    b_q, b_sf = O.quantize_nvfp4(b, gs)
+    alpha = np.random.default_rng([0, 2]).uniform(0.5, 2.0, l).astype(np.float32)
+    got = run_masked(a_q, a_sf, b_q, b_sf, alpha, None, _cfg(**cfg))
+    ref64 = O.grouped_gemm_f64(a_q, a_sf, b_q, b_sf, alpha)
+    _nontrivial(ref64)
+    ok, worst = O.tolerance_ok(got, ref64)
+    assert ok, f"worst error / bound = {worst}"
+    assert np.abs(got - ref64).max() / np.abs(ref64).max() < 5e-3          # test_kernels.py:87-89
+    rep = gate.gate_bf16(got, ref64)
+    assert rep.passed, rep.failures
+
+
+def test_headline_shape_properties():
+    """l=8, m=512, n=2048, k=2048 on device-quantised N(0,1) data: size-independent checks
+    (linearity in alpha, agreement of the two tile shapes, a sampled float64 check)."""
+    from mosaicist_b200 import _lib, ops
+    from mosaicist_b200.formats import dequant_nvfp4
+
+    l, m, n, k = 8, 512, 2048, 2048
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn((l, m, k), device="cuda", generator=g)
+    b = torch.randn((l, n, k), device="cuda", generator=g)
+    gs = torch.full((l,), 64.0, device="cuda")
+    a_q, a_sf = ops.quantize_nvfp4(a, gs)
+    b_q, b_sf = ops.quantize_nvfp4(b, gs)
+    one = torch.ones((l,), device="cuda")
+    o1 = ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, one, None, ops.GemmConfig())
+    o2 = ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, 2 * one, None, ops.GemmConfig(tile_n=256))
+    assert _lib.status_word() == 0
+    assert torch.equal(o1.float() * 2, o2.float())        # power-of-two alpha is exact in bf16
+    gi = 5
+    rows = slice(128, 160)
+    ref = dequant_nvfp4(a_q[gi].cpu().numpy(), a_sf[gi].cpu().numpy())[rows] @ \
+        dequant_nvfp4(b_q[gi].cpu().numpy(), b_sf[gi].cpu().numpy()).T
+    ok, worst = O.tolerance_ok(o1[gi, rows].float().cpu().numpy(), ref)
+    assert ok, worst
+    assert np.array_equal(o1[gi, rows].float().cpu().numpy(), O.bf16_round(ref))
+
+
+RAGGED = [
+    ([128], 128, 128, {}),
+    ([200, 0, 50, 384], 256, 1024, {}),
+    ([200, 0, 50, 384], 256, 1024, {"tile_n": 256}),
+    ([1, 127, 129, 300, 5], 384, 640, {"max_ctas": 3}),
+]
+
+
+def _ragged_layout(rows_list):
+    offs, tot = [], 0
+    for r in rows_list:
+        offs.append(tot)
+        tot += (r + 127) // 128 * 128
+    return offs, max(tot, 128)
+
+
+@pytest.mark.parametrize("rows_list,n,k,cfg", RAGGED)
+def test_mxfp8_ragged_bit_exact(rows_list, n, k, cfg):
+    from mosaicist_b200 import _lib, ops
+
+    rng = np.random.default_rng([2, n, k, len(rows_list)])
+    l = len(rows_list)
+    offs, tot = _ragged_layout(rows_list)
+    a_q, a_sf = X.exact_operands(rng, tot, k)
+    b = [X.exact_operands(rng, n, k) for _ in range(l)]
+    b_q, b_sf = np.stack([x[0] for x in b]), np.stack([x[1] for x in b])
+    alpha = np.exp2(rng.integers(-1, 2, l)).astype(np.float32)
+    rs = np.exp2(rng.integers(-1, 2, tot)).astype(np.float32)
+    out = torch.full((tot, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.ragged_grouped_gemm_mxfp8(
+        T(a_q.view(np.uint8)), T(O.to_mma_scale_layout(a_sf)), T(b_q.view(np.uint8)),
+        T(np.stack([O.to_mma_scale_layout(s) for s in b_sf])), T(np.array(offs, np.int32)),
+        T(np.array(rows_list, np.int32)), T(alpha), T(rs), _cfg(**cfg), out=out)
+    assert _lib.status_word() == 0
+    got = out.float().cpu().numpy()
+    want = O.bf16_round(X.ragged_grouped_gemm_f64(a_q, a_sf, b_q, b_sf, offs, rows_list, alpha, rs))
+    mask = np.zeros((tot, 1), bool)
+    for o, r in zip(offs, rows_list):
+        mask[o:o + r] = True
+    _nontrivial(want[mask[:, 0]])
+    assert np.array_equal(np.where(mask, got, 0), want)
+    assert np.isnan(got[~mask[:, 0]]).all()
+
+
+@pytest.mark.parametrize("rows_list,n,k,cfg", RAGGED[1:])
+def test_nvfp4_ragged_row_scale_bit_exact(rows_list, n, k, cfg):
+    from mosaicist_b200 import _lib, ops
+
+    rng = np.random.default_rng([3, n, k])
+    l = len(rows_list)
+    offs, tot = _ragged_layout(rows_list)
+    a_q, a_sf = O.exact_operands(rng, 1, tot, k)
+    b_q, b_sf = O.exact_operands(rng, l, n, k)
+    alpha = np.exp2(rng.integers(-1, 2, l)).astype(np.float32)
+    rs = np.exp2(rng.integers(-1, 2, tot)).astype(np.float32)
+    out = torch.full((tot, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.ragged_grouped_gemm_nvfp4(
+        T(O.pack_e2m1(a_q[0])), T(O.e4m3_bytes(O.to_mma_scale_layout(a_sf[0]))),
+        T(O.pack_e2m1(b_q)), T(O.e4m3_bytes(O.retile(b_sf))), T(np.array(offs, np.int32)),
+        T(np.array(rows_list, np.int32)), T(alpha), T(rs), _cfg(**cfg), out=out)
+    assert _lib.status_word() == 0
+    got = out.float().cpu().numpy()
+    want = np.zeros((tot, n))
+    for g_, (o, r) in enumerate(zip(offs, rows_list)):
+        if r:
+            y = O.grouped_gemm_f64(a_q[:, o:o + r], a_sf[:, o:o + r], b_q[g_:g_ + 1], b_sf[g_:g_ + 1])[0]
+            want[o:o + r] = y * alpha[g_] * rs[o:o + r, None]
+    mask = np.zeros((tot, 1), bool)
+    for o, r in zip(offs, rows_list):
+        mask[o:o + r] = True
+    assert np.array_equal(np.where(mask, got, 0), O.bf16_round(want))
+
+
+def test_random_mxfp8_within_tolerance():
+    from mosaicist_b200 import _lib, ops
+
+    rows_list, n, k = [300, 128, 77], 256, 896
+    l = len(rows_list)
+    offs, tot = _ragged_layout(rows_list)
+    a = np.random.default_rng([4, 0]).standard_normal((tot, k)).astype(np.float32)
+    b = np.random.default_rng([4, 1]).standard_normal((l, n, k)).astype(np.float32)
+    a_q, a_sf = X.quantize_mxfp8(a)
+    b_q, b_sf = X.quantize_mxfp8(b)
+    out = ops.ragged_grouped_gemm_mxfp8(
+        T(a_q.view(np.uint8)), T(O.to_mma_scale_layout(a_sf)), T(b_q.view(np.uint8)),
+        T(np.stack([O.to_mma_scale_layout(s) for s in b_sf])), T(np.array(offs, np.int32)),
+        T(np.array(rows_list, np.int32)))
+    assert _lib.status_word() == 0
+    ref = X.ragged_grouped_gemm_f64(a_q, a_sf, b_q, b_sf, offs, rows_list)
+    got = out.float().cpu().numpy()
+    for o, r in zip(offs, rows_list):
+        ok, worst = O.tolerance_ok(got[o:o + r], ref[o:o + r])
+        assert ok, worst
+        assert gate.gate_bf16(got[o:o + r], ref[o:o + r]).passed
