@@ -6,6 +6,7 @@
 
 #include <mutex>
 #include <string>
+#include <unordered_map>
 
 namespace msc {
 
@@ -52,8 +53,55 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+namespace {
+struct TmapKey {
+  const void* base;
+  uint64_t rows, row_bytes;
+  uint32_t box_rows;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= k.row_bytes + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    return h ^ k.box_rows;
+  }
+};
+int encode_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                         uint32_t box_rows);
+}  // namespace
+
+// A tensor map only encodes address, shape and box, so one encoded for a buffer stays valid
+// for any later buffer at the same address with the same shape: cache them, the driver call
+// costs microseconds and the GEMM itself runs for about ten.
 int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                        uint32_t box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  const TmapKey key{base, rows, row_bytes, box_rows};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *map = it->second;
+      return MSC_OK;
+    }
+  }
+  const int rc = encode_tmap_bytes_2d(map, base, rows, row_bytes, box_rows);
+  if (rc == MSC_OK) {
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *map);
+  }
+  return rc;
+}
+
+namespace {
+int encode_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                         uint32_t box_rows) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return MSC_ERR_CUDA;
   if (reinterpret_cast<uintptr_t>(base) % 16 || row_bytes % 16)
@@ -70,6 +118,7 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
     return fail(MSC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return MSC_OK;
 }
+}  // namespace
 
 int num_sms() {
   static int cached[64] = {0};

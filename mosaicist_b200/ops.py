@@ -51,8 +51,28 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+class Plan:
+    """A validated call with its foreign-function arguments already built: running it costs
+    one ctypes call on the current stream.  Holds references to the tensors involved."""
+
+    def __init__(self, fn, args, out, keep):
+        self._fn, self._args, self.out, self._keep = fn, args, out, keep
+
+    def __call__(self):
+        code = self._fn(*self._args, torch.cuda.current_stream().cuda_stream)
+        if code:
+            _lib.check(code)
+        return self.out
+
+
 def masked_grouped_gemm(a_q, a_sf, b_q, b_sf, alpha=None, masked_m=None,
                         config: GemmConfig = GemmConfig(), out=None) -> torch.Tensor:
+    """See masked_grouped_gemm_plan; validates, launches once and returns `out`."""
+    return masked_grouped_gemm_plan(a_q, a_sf, b_q, b_sf, alpha, masked_m, config, out)()
+
+
+def masked_grouped_gemm_plan(a_q, a_sf, b_q, b_sf, alpha=None, masked_m=None,
+                             config: GemmConfig = GemmConfig(), out=None) -> Plan:
     """out[l, m, n] = bf16(alpha[l] * dequant(A)[l] @ dequant(B)[l].T), rows >= masked_m[l]
     left untouched.  Same operands as masked_grouped_gemm (masked_gemm.py:104-123):
     a_q (l, m, k/2) packed e2m1, a_sf (l, m/128, k/64, 32, 16) e4m3 in the MMA tiling,
@@ -74,10 +94,10 @@ def masked_grouped_gemm(a_q, a_sf, b_q, b_sf, alpha=None, masked_m=None,
     else:
         _need(out, "out", (torch.bfloat16,), (l, m, n))
     cfg = config.c()
-    _lib.check(_lib.load().msc_grouped_gemm_nvfp4(
-        _ptr(a_q), _ptr(a_sf), _ptr(b_q), _ptr(b_sf), _ptr(alpha), _ptr(masked_m), _ptr(out),
-        l, m, n, k, cfg, _stream()))
-    return out
+    args = (_ptr(a_q), _ptr(a_sf), _ptr(b_q), _ptr(b_sf), _ptr(alpha), _ptr(masked_m), _ptr(out),
+            l, m, n, k, cfg)
+    return Plan(_lib.load().msc_grouped_gemm_nvfp4, args, out,
+                (a_q, a_sf, b_q, b_sf, alpha, masked_m, cfg))
 
 
 def _ragged(fn_name, k, a_q, a_sf, b_q, b_sf, alpha, group_offsets, group_rows, row_scale,
