@@ -1,11 +1,12 @@
 // Block-scaled grouped GEMM for sm_100a: NVFP4 (e2m1 x e2m1, ue4m3 scale per 16) and
 // MXFP8 (e4m3 x e4m3, ue8m0 scale per 32), fp32 accumulation in TMEM, bf16 output.
 //
-// One persistent CTA per SM, 192 threads, three roles:
-//   warps 0-3  epilogue: tcgen05.ld their TMEM lane quadrant, scale, round to bf16, store
-//   warp 4     MMA issuer: one thread stages scale factors into TMEM (tcgen05.cp) and
-//              issues tcgen05.mma for each K step of the tile
-//   warp 5     producer: one thread issues TMA loads for the operand ring
+// One persistent CTA per SM, three roles:
+//   epilogue warps (4 for 128-wide tiles, 8 for 256-wide): tcgen05.ld a 32-row x 128-column
+//              block of the accumulator, scale, round to bf16, TMA-store through shared memory
+//   MMA warp:  one elected lane stages scale factors into TMEM (tcgen05.cp) and issues
+//              tcgen05.mma for each K step of the tile
+//   producer warp: one elected lane issues TMA loads for the operand ring
 // The accumulator is double-buffered in TMEM (when two fit) so the epilogue of tile i
 // overlaps the main loop of tile i+1.
 //
@@ -80,8 +81,14 @@ struct Smem {
   static constexpr int kOffB = kOffA + STAGES * kA;
   static constexpr int kOffSfa = kOffB + STAGES * kB;
   static constexpr int kOffSfb = kOffSfa + STAGES * kSfa;
-  static constexpr int kTotal = kOffSfb + STAGES * kSfb;
+  static constexpr int kEpiWarps = (TILE_N == 256) ? 8 : 4;  // one 128-column slab per warp
+  static constexpr int kThreads = (kEpiWarps + 2) * 32;
+  static constexpr int kOffC = kOffSfb + STAGES * kSfb;  // epilogue staging, 32 KB in all
+  static constexpr int kCPerWarp = 32768 / kEpiWarps;    // two 4 KB boxes (4 warps) or one (8)
+  static constexpr int kC = 32768;
+  static constexpr int kTotal = kOffC + kC;
   static constexpr int kAlloc = kTotal + 1024;  // slack to realign the base to 1024 B
+  static_assert(kAlloc <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
 // Walks the flattened (group, m-tile, n-tile) space in increasing tile id.
@@ -92,10 +99,12 @@ struct TileCursor {
     while (true) {
       if (!primed) {
         if (g >= p.l) return false;
-        rows = p.group_rows ? __ldg(p.group_rows + g) : p.m_stride;
+        // every lane reads the same word; the broadcast tells the compiler so
+        rows = p.group_rows ? __shfl_sync(0xffffffffu, __ldg(p.group_rows + g), 0) : p.m_stride;
         if (rows < 0) rows = 0;
         if (p.m_stride > 0 && rows > p.m_stride) rows = p.m_stride;
-        off = p.group_offsets ? __ldg(p.group_offsets + g) : g * p.m_stride;
+        off = p.group_offsets ? __shfl_sync(0xffffffffu, __ldg(p.group_offsets + g), 0)
+                              : g * p.m_stride;
         mtiles = (rows + 127) >> 7;
         primed = true;
       }
@@ -118,11 +127,14 @@ struct TileCursor {
 };
 
 template <int KIND, int TILE_N, int STAGES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(Smem<TILE_N, STAGES>::kThreads, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                        const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                        const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using L = Smem<TILE_N, STAGES>;
   constexpr int kSub = L::kSub;
+  constexpr int kMmaWarp = L::kEpiWarps;
+  constexpr int kProducerWarp = L::kEpiWarps + 1;
   constexpr int kAccBufs = (TILE_N == 128) ? 2 : 1;
   constexpr int kSfaCols = 16;             // 4 MMAs x 4 columns (NVFP4); MXFP8 uses 4
   constexpr int kSfbCols = 16 * kSub;
@@ -150,7 +162,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + 512);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(sgen + 516);
 
-  const int warp = threadIdx.x >> 5;
+  // broadcast from lane 0 so the compiler knows the role index is warp-uniform and keeps the
+  // role bodies (and the operands of their asynchronous instructions) on the uniform path
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const int ntiles = p.n / TILE_N;
 
@@ -161,15 +175,16 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full + 8 * b, 1);
-      mbar_init(bar_acc_empty + 8 * b, 4);
+      mbar_init(bar_acc_empty + 8 * b, L::kEpiWarps);
     }
     mbar_init(bar_drain, 1);
     *abort_flag = 0u;
     fence_barrier_init();
   }
-  if (warp == 5 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_c);
   }
   if (warp == 0) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -178,7 +193,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 #ifdef MSC_DEBUG
   if (p.trace && threadIdx.x == 0) {
     p.trace[(size_t)gridDim.x * 48 + blockIdx.x * 2] = clock64();
@@ -191,7 +206,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // The producer and MMA warps run their loops with all 32 lanes converged and issue each
   // asynchronous instruction from one elected lane: operands then stay warp-uniform, which
   // is what keeps the issue cost of TMA / tcgen05 instructions low.
-  if (warp == 5) {
+  if (warp == kProducerWarp) {
     // ------------------------------ producer ------------------------------------
     TileCursor cur;
     int it = 0, tl = 0;
@@ -241,107 +256,112 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int j = max(0, it - STAGES); j < it; ++j)
         mbar_wait_drain(bar_full + 8 * (j % STAGES), (j / STAGES) & 1);
     }
-  } else if (warp == 4) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer ----------------------------------
-    // Per K stage the elected lane issues the scale copies, the MMAs and one commit as a
-    // straight-line block; everything that can be is hoisted out of it (stage index and
-    // parity are stepped, not divided; the next stage's barrier is probed one stage ahead)
-    // because the tensor pipe idles whenever this warp is not feeding it.
+    // The tensor pipe takes instructions through a shallow queue, so it idles whenever this
+    // warp spends long between MMAs.  The loop is therefore software-pipelined: the wait for
+    // the NEXT stage's operands and the issue of its scale copies sit between the second and
+    // third MMA of the CURRENT stage, where two queued MMAs cover their latency.  Stage
+    // index, parity and descriptor words are stepped, never divided.
     TileCursor cur;
     int tl = 0;
     uint32_t s = 0, ph = 0, slot = 0;
     bool ok = true;
-    bool ready = mbar_test(bar_full, 0);
     const uint64_t adesc0 = operand_desc_sw128(sbase + L::kOffA);
     const uint64_t bdesc0 = operand_desc_sw128(sbase + L::kOffB);
     const uint64_t sfa_d0 = scale_desc(sbase + L::kOffSfa);
     const uint64_t sfb_d0 = scale_desc(sbase + L::kOffSfb);
+    // descriptor low words count 16-byte units: +32 per 512-byte scale chunk, +128 per
+    // 2048-byte sub-tile block, +2 per 32 bytes of K inside the swizzled operand tile
+    auto copy_scales = [&](uint32_t st, uint32_t sl, int nch) {
+      const uint32_t sfa_t = tmem_base + kSfCol0 + sl * kSlotCols;
+      const uint32_t sfb_t = sfa_t + kSfaCols;
+      const uint64_t sfa_d = sfa_d0 + st * (L::kSfa >> 4);
+      const uint64_t sfb_d = sfb_d0 + st * (L::kSfb >> 4);
+      if (MSC_FLAG(2)) return;
+#pragma unroll
+      for (int c = 0; c < kChunksPerStage; ++c) {
+        if (c < nch) {
+          tc_cp_32x128b_warpx4(sfa_t + 4 * c, sfa_d + 32 * c);
+#pragma unroll
+          for (int sub = 0; sub < kSub; ++sub)
+            tc_cp_32x128b_warpx4(sfb_t + 4 * kSub * c + 4 * sub, sfb_d + 128 * sub + 32 * c);
+        }
+      }
+    };
+    auto mma = [&](uint32_t acc, uint32_t st, uint32_t sl, int j, uint32_t accumulate) {
+      const uint32_t sfa_t = tmem_base + kSfCol0 + sl * kSlotCols;
+      const uint32_t sfb_t = sfa_t + kSfaCols;
+      const uint64_t adesc = adesc0 + st * (L::kA >> 4) + 2 * j;
+      const uint64_t bdesc = bdesc0 + st * (L::kB >> 4) + 2 * j;
+      if (MSC_FLAG(4)) return;
+      if (KIND == KIND_NVFP4) {
+        tc_mma_nvfp4(acc, adesc, bdesc, kIdescBase, sfa_t + 4 * j, sfb_t + 4 * kSub * j, accumulate);
+      } else {
+        const uint32_t idesc = kIdescBase | (uint32_t(j) << 29) | (uint32_t(j) << 4);
+        tc_mma_mxf8(acc, adesc, bdesc, idesc, sfa_t, sfb_t, accumulate);
+      }
+    };
+    const int nch_first = min(kChunksPerStage, p.sf_chunks);
+    bool primed = false;  // scale copies of the stage about to be consumed already issued
     for (int t = blockIdx.x; ok; t += gridDim.x, ++tl) {
       int mt, nt;
       if (!cur.seek(p, ntiles, t, mt, nt)) break;
+      TileCursor peek = cur;
+      int mt2, nt2;
+      const bool more_tiles = peek.seek(p, ntiles, t + gridDim.x, mt2, nt2);
+      if (!primed) {
+        ok = warp_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (elect_one()) copy_scales(s, slot, nch_first);
+        primed = true;
+      }
       const int buf = tl % kAccBufs;
       const uint32_t aph = (tl / kAccBufs) & 1;
       ok = warp_wait(bar_acc_empty + 8 * buf, aph ^ 1u, abort_flag, p.status, 2);
       if (!ok) break;
+      tc_fence_after_sync();
       MSC_STAMP(1, tl, 0);
       const uint32_t acc = tmem_base + buf * TILE_N;
       for (int kb = 0; kb < p.k_stages; ++kb) {
         if (lane == 0) MSC_FINE(8);
-        if (!__all_sync(0xffffffffu, ready)) {
-          ok = warp_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3);
-          if (!ok) break;
-        }
-        if (lane == 0) MSC_FINE(9);
+        const int nch = min(kChunksPerStage, p.sf_chunks - kb * kChunksPerStage);
+        const int nmma = (KIND == KIND_NVFP4) ? nch : 4;
+        const bool last_kb = kb + 1 == p.k_stages;
+        const bool has_next = !last_kb || more_tiles;
+        const int nch_next =
+            last_kb ? nch_first : min(kChunksPerStage, p.sf_chunks - (kb + 1) * kChunksPerStage);
         const uint32_t s_next = (s + 1 == STAGES) ? 0u : s + 1;
         const uint32_t ph_next = (s + 1 == STAGES) ? ph ^ 1u : ph;
-        ready = mbar_test(bar_full + 8 * s_next, ph_next);
-        tc_fence_after_sync();
-#ifdef MSC_DEBUG
-        if (p.trace && tl == 1 && kb < 12 && lane == 0)  // arrival cadence of tile 1's stages
-          p.trace[((size_t)blockIdx.x * 8 + 6) * 6 + kb] = clock64();
-#endif
-        const int c0 = kb * kChunksPerStage;
-        const int nch = min(kChunksPerStage, p.sf_chunks - c0);
-        const uint32_t sfa_t = tmem_base + kSfCol0 + slot * kSlotCols;
-        const uint32_t sfb_t = sfa_t + kSfaCols;
-        // descriptor low words count 16-byte units
-        const uint64_t sfa_d = sfa_d0 + s * (L::kSfa >> 4);
-        const uint64_t sfb_d = sfb_d0 + s * (L::kSfb >> 4);
-        const uint64_t adesc = adesc0 + s * (L::kA >> 4);
-        const uint64_t bdesc = bdesc0 + s * (L::kB >> 4);
+        const uint32_t slot_next = (slot + 1 == kSfSlots) ? 0u : slot + 1;
+        if (elect_one()) {
+          mma(acc, s, slot, 0, kb > 0 ? 1u : 0u);
+          if (nmma > 1) mma(acc, s, slot, 1, 1u);
+        }
+        if (lane == 0) MSC_FINE(9);
+        if (has_next) {
+          const bool ready = mbar_test(bar_full + 8 * s_next, ph_next);
+          if (!__all_sync(0xffffffffu, ready)) {
+            ok = warp_wait(bar_full + 8 * s_next, ph_next, abort_flag, p.status, 3);
+            if (!ok) break;
+          }
+          tc_fence_after_sync();
+        }
         if (lane == 0) MSC_FINE(10);
         if (elect_one()) {
+          if (has_next) copy_scales(s_next, slot_next, nch_next);
           MSC_FINE(11);
-          if (nch == kChunksPerStage && !MSC_FLAG(2 | 4)) {
-            // full stage: +32 per 512-byte scale chunk, +128 per 2048-byte sub-tile block,
-            // +2 per 32 bytes of K inside the swizzled operand tile
-#pragma unroll
-            for (int c = 0; c < kChunksPerStage; ++c) {
-              tc_cp_32x128b_warpx4(sfa_t + 4 * c, sfa_d + 32 * c);
-#pragma unroll
-              for (int sub = 0; sub < kSub; ++sub)
-                tc_cp_32x128b_warpx4(sfb_t + 4 * kSub * c + 4 * sub, sfb_d + 128 * sub + 32 * c);
-            }
-            MSC_FINE(12);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t accumulate = (j > 0 || kb > 0) ? 1u : 0u;
-              if (KIND == KIND_NVFP4) {
-                tc_mma_nvfp4(acc, adesc + 2 * j, bdesc + 2 * j, kIdescBase, sfa_t + 4 * j,
-                             sfb_t + 4 * kSub * j, accumulate);
-              } else {
-                const uint32_t idesc = kIdescBase | (uint32_t(j) << 29) | (uint32_t(j) << 4);
-                tc_mma_mxf8(acc, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, accumulate);
-              }
-            }
-          } else {
-            // last, partial K stage of an NVFP4 problem (or a debug run that skips work)
-            for (int c = 0; c < nch && !MSC_FLAG(2); ++c) {
-              tc_cp_32x128b_warpx4(sfa_t + 4 * c, sfa_d + 32 * c);
-              for (int sub = 0; sub < kSub; ++sub)
-                tc_cp_32x128b_warpx4(sfb_t + 4 * kSub * c + 4 * sub, sfb_d + 128 * sub + 32 * c);
-            }
-            MSC_FINE(12);
-            const int nmma = (KIND == KIND_NVFP4) ? nch : 4;
-            for (int j = 0; j < nmma && !MSC_FLAG(4); ++j) {
-              const uint32_t accumulate = (j > 0 || kb > 0) ? 1u : 0u;
-              if (KIND == KIND_NVFP4) {
-                tc_mma_nvfp4(acc, adesc + 2 * j, bdesc + 2 * j, kIdescBase, sfa_t + 4 * j,
-                             sfb_t + 4 * kSub * j, accumulate);
-              } else {
-                const uint32_t idesc = kIdescBase | (uint32_t(j) << 29) | (uint32_t(j) << 4);
-                tc_mma_mxf8(acc, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, accumulate);
-              }
-            }
-          }
-          MSC_FINE(13);
+          if (nmma > 2) mma(acc, s, slot, 2, 1u);
+          if (nmma > 3) mma(acc, s, slot, 3, 1u);
+          MSC_FINE(12);
           tc_commit(bar_empty + 8 * s);  // frees the smem stage once these MMAs have read it
-          MSC_FINE(14);
+          MSC_FINE(13);
         }
         if (lane == 0) MSC_FINE(15);
         s = s_next;
         ph = ph_next;
-        slot = (slot + 1 == kSfSlots) ? 0u : slot + 1;
+        slot = slot_next;
       }
       if (ok && elect_one()) tc_commit(bar_acc_full + 8 * buf);
       MSC_STAMP(1, tl, 1);
@@ -353,9 +373,20 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ------------------------------ epilogue ------------------------------------
+    // Warp w owns TMEM lane quadrant w % 4 (32 accumulator rows) and the 128-column slab
+    // w / 4 of the tile.  It pulls its 32 x 128 fp32 block into registers in one go and
+    // hands the accumulator back to the MMA warp as soon as those loads land; then, 64
+    // columns at a time: scale, round to bf16, park the rows in its shared-memory staging
+    // box in the 128-byte-swizzled layout and let one lane issue a TMA store of the box.
+    // A warp whose 32 rows are not all valid (the ragged end of a group) writes its valid
+    // rows with plain 16-byte stores instead, so rows past masked_m are never touched.
     TileCursor cur;
     int tl = 0;
-    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    const int quad = warp & 3;
+    const int slab = warp >> 2;
+    const uint32_t lane_base = uint32_t(quad * 32) << 16;
+    const uint32_t stage_c = sbase + L::kOffC + warp * L::kCPerWarp;
+    constexpr bool kTwoBoxes = (L::kCPerWarp == 8192);
     for (int t = blockIdx.x;; t += gridDim.x, ++tl) {
       int mt, nt;
       if (!cur.seek(p, ntiles, t, mt, nt)) break;
@@ -368,26 +399,72 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!ok) break;
       tc_fence_after_sync();
       if (warp == 0) MSC_STAMP(2, tl, 0);
-      const int row_local = mt * 128 + warp * 32 + lane;
-      const bool valid = row_local < cur.rows;
-      const size_t out_row = (size_t)cur.off + row_local;
+      const int row_warp = mt * 128 + quad * 32;
+      const bool valid = row_warp + lane < cur.rows;
+      const bool whole_warp = row_warp + 32 <= cur.rows;
+      const size_t out_row = (size_t)cur.off + row_warp + lane;
       float scale = p.alpha ? __ldg(p.alpha + cur.g) : 1.0f;
       if (p.row_scale && valid) scale *= __ldg(p.row_scale + out_row);
-      __nv_bfloat16* dst = p.out + out_row * p.n + (size_t)nt * TILE_N;
-#pragma unroll 1
-      for (int c = 0; c < TILE_N / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_base + buf * TILE_N + c * 32, v);
-        tmem_ld_wait();
-        if (valid && !MSC_FLAG(1)) {
+
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        tmem_ld_32x32b_x32(tmem_base + lane_base + buf * TILE_N + slab * 128 + c * 32, v[c]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+      if (warp == 0) MSC_STAMP(2, tl, 1);
+      if (MSC_FLAG(1)) continue;
+
+      const int col0 = nt * TILE_N + slab * 128;
+      if (whole_warp) {
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+          const uint32_t box = stage_c + (kTwoBoxes ? sub * 4096 : 0);
+          if (!kTwoBoxes || sub == 0) {
+            if (lane == 0) bulk_wait_group_read0();  // earlier stores have left the staging box
+            __syncwarp();
+          }
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = sub * 2 + cc;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float lo = __uint_as_float(v[c][q * 8 + 2 * e]) * scale;
+                const float hi = __uint_as_float(v[c][q * 8 + 2 * e + 1]) * scale;
+                __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
+                w[e] = *reinterpret_cast<uint32_t*>(&pr);
+              }
+              // row = lane; 16-byte chunk j of the 128-byte row sits at j ^ (row & 7)
+              const int j = cc * 4 + q;
+              const uint32_t addr = box + lane * 128 + ((j ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]),
+                           "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_c, box, col0 + sub * 64, cur.off + row_warp);
+            bulk_commit_group();
+          }
+        }
+      } else if (valid) {
+        __nv_bfloat16* dst = p.out + out_row * p.n + col0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
           uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float lo = __uint_as_float(v[q * 8 + 2 * e]) * scale;
-              const float hi = __uint_as_float(v[q * 8 + 2 * e + 1]) * scale;
+              const float lo = __uint_as_float(v[c][q * 8 + 2 * e]) * scale;
+              const float hi = __uint_as_float(v[c][q * 8 + 2 * e + 1]) * scale;
               __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
               w[e] = *reinterpret_cast<uint32_t*>(&pr);
             }
@@ -395,11 +472,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
-      if (warp == 0) MSC_STAMP(2, tl, 1);
     }
+    if (lane == 0) bulk_wait_group_read0();  // staging area must outlive the stores that read it
   }
 
   tc_fence_before_sync();
@@ -421,8 +495,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // ---------------------------------- host side -------------------------------------------
 
 template <int KIND, int TILE_N, int STAGES>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                  const GemmParams& p, int grid, cudaStream_t stream) {
   using L = Smem<TILE_N, STAGES>;
   auto kern = gemm_blockscaled_kernel<KIND, TILE_N, STAGES>;
   static bool configured[64] = {false};
@@ -432,25 +506,24 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
     configured[dev & 63] = true;
   }
-  kern<<<grid, 192, L::kAlloc, stream>>>(ta, tb, p);
+  kern<<<grid, L::kThreads, L::kAlloc, stream>>>(ta, tb, tc, p);
   MSC_CUDA_OK(cudaGetLastError());
   return MSC_OK;
 }
 
 template <int KIND, int TILE_N>
 static int pick_stages(int stages, const CUtensorMap& ta, const CUtensorMap& tb,
-                       const GemmParams& p, int grid, cudaStream_t stream) {
-  constexpr int kMax = (TILE_N == 128) ? 6 : 4;
+                       const CUtensorMap& tc, const GemmParams& p, int grid, cudaStream_t stream) {
+  constexpr int kMax = (TILE_N == 128) ? 5 : 3;  // what fits beside the 32 KB staging area
   if (stages <= 0 || stages > kMax) stages = kMax;
   switch (stages) {
-    case 2: return launch<KIND, TILE_N, 2>(ta, tb, p, grid, stream);
-    case 3: return launch<KIND, TILE_N, 3>(ta, tb, p, grid, stream);
-    case 4: return launch<KIND, TILE_N, 4>(ta, tb, p, grid, stream);
-    case 5:
-      if constexpr (TILE_N == 128) return launch<KIND, TILE_N, 5>(ta, tb, p, grid, stream);
+    case 2: return launch<KIND, TILE_N, 2>(ta, tb, tc, p, grid, stream);
+    case 3: return launch<KIND, TILE_N, 3>(ta, tb, tc, p, grid, stream);
+    case 4:
+      if constexpr (TILE_N == 128) return launch<KIND, TILE_N, 4>(ta, tb, tc, p, grid, stream);
       break;
-    case 6:
-      if constexpr (TILE_N == 128) return launch<KIND, TILE_N, 6>(ta, tb, p, grid, stream);
+    case 5:
+      if constexpr (TILE_N == 128) return launch<KIND, TILE_N, 5>(ta, tb, tc, p, grid, stream);
       break;
     default: break;
   }
@@ -488,10 +561,12 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   int* status = status_word();
   if (!status) return fail(MSC_ERR_CUDA, "status word unavailable on this device");
 
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tc;
   int rc = make_tmap_bytes_2d(&ta, a_q, (uint64_t)rows_total, (uint64_t)k_bytes, 128);
   if (rc) return rc;
   rc = make_tmap_bytes_2d(&tb, b_q, (uint64_t)l * n, (uint64_t)k_bytes, (uint32_t)tile_n);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tc, out, (uint64_t)rows_total, (uint64_t)n, 32);
   if (rc) return rc;
 
   GemmParams p;
@@ -521,11 +596,11 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
   if (kind == KIND_NVFP4) {
-    if (tile_n == 128) return pick_stages<KIND_NVFP4, 128>(cfg.stages, ta, tb, p, grid, stream);
-    return pick_stages<KIND_NVFP4, 256>(cfg.stages, ta, tb, p, grid, stream);
+    if (tile_n == 128) return pick_stages<KIND_NVFP4, 128>(cfg.stages, ta, tb, tc, p, grid, stream);
+    return pick_stages<KIND_NVFP4, 256>(cfg.stages, ta, tb, tc, p, grid, stream);
   }
-  if (tile_n == 128) return pick_stages<KIND_MXFP8, 128>(cfg.stages, ta, tb, p, grid, stream);
-  return pick_stages<KIND_MXFP8, 256>(cfg.stages, ta, tb, p, grid, stream);
+  if (tile_n == 128) return pick_stages<KIND_MXFP8, 128>(cfg.stages, ta, tb, tc, p, grid, stream);
+  return pick_stages<KIND_MXFP8, 256>(cfg.stages, ta, tb, tc, p, grid, stream);
 }
 
 }  // namespace msc

@@ -57,7 +57,7 @@ namespace {
 struct TmapKey {
   const void* base;
   uint64_t rows, row_bytes;
-  uint32_t box_rows;
+  uint32_t box_rows;  // bit 31 set: bf16 elements (store map), else bytes (operand map)
   bool operator==(const TmapKey& o) const {
     return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows;
   }
@@ -70,18 +70,18 @@ struct TmapKeyHash {
     return h ^ k.box_rows;
   }
 };
-int encode_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
-                         uint32_t box_rows);
+int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                   uint32_t box_rows, bool bf16);
 }  // namespace
 
 // A tensor map only encodes address, shape and box, so one encoded for a buffer stays valid
 // for any later buffer at the same address with the same shape: cache them, the driver call
 // costs microseconds and the GEMM itself runs for about ten.
-int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
-                       uint32_t box_rows) {
+static int cached_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                       uint32_t box_rows, bool bf16) {
   static std::mutex mu;
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
-  const TmapKey key{base, rows, row_bytes, box_rows};
+  const TmapKey key{base, rows, row_bytes, box_rows | (bf16 ? 0x80000000u : 0u)};
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
@@ -90,7 +90,7 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
       return MSC_OK;
     }
   }
-  const int rc = encode_tmap_bytes_2d(map, base, rows, row_bytes, box_rows);
+  const int rc = encode_tmap_2d(map, base, rows, row_bytes, box_rows, bf16);
   if (rc == MSC_OK) {
     std::lock_guard<std::mutex> lock(mu);
     if (cache.size() > 4096) cache.clear();
@@ -99,19 +99,31 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
   return rc;
 }
 
+int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                       uint32_t box_rows) {
+  return cached_tmap(map, base, rows, row_bytes, box_rows, false);
+}
+
+int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                      uint32_t box_rows) {
+  return cached_tmap(map, base, rows, cols * 2, box_rows, true);
+}
+
 namespace {
-int encode_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
-                         uint32_t box_rows) {
+int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                   uint32_t box_rows, bool bf16) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return MSC_ERR_CUDA;
   if (reinterpret_cast<uintptr_t>(base) % 16 || row_bytes % 16)
     return fail(MSC_ERR_BAD_ARG, "operand base and row pitch must be 16-byte aligned");
   if (box_rows == 0 || box_rows > 256) return fail(MSC_ERR_BAD_ARG, "box rows out of range");
-  cuuint64_t dims[2] = {row_bytes, rows};
+  // the box is always 128 bytes wide: 128 byte elements or 64 bf16 elements
+  cuuint64_t dims[2] = {bf16 ? row_bytes / 2 : row_bytes, rows};
   cuuint64_t strides[1] = {row_bytes};
-  cuuint32_t box[2] = {128u, box_rows};
+  cuuint32_t box[2] = {bf16 ? 64u : 128u, box_rows};
   cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+  CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                   const_cast<void*>(base), dims, strides,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)

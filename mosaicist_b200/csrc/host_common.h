@@ -30,6 +30,11 @@ EncodeTiledFn encode_tiled_fn();
 int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                        uint32_t box_rows);
 
+// 2-D bf16 tensor [rows][cols] with a [box_rows][64 columns = 128 B] box and 128-byte swizzle
+// (the epilogue's store map).
+int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                      uint32_t box_rows);
+
 int num_sms();
 
 #define MSC_CUDA_OK(expr)                                                              \
