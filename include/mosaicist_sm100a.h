@@ -45,7 +45,10 @@ typedef struct msc_gemm_cfg {
   int raster;    /* 0: n-tile fastest inside a group, 1: m-tile fastest                 */
   int max_ctas;  /* persistent grid size; 0 = one CTA per SM                            */
   int epilogue;  /* MSC_EPI_*                                                            */
-  int reserved[3];
+  int cta_pair;  /* 1: two CTAs share one 256x256 tile (tcgen05 cta_group::2; needs n % 256 == 0,
+                    ignores tile_n); the counterpart of the reference's `collective` knob
+                    (cand_pallas_gemm.py:31)                                              */
+  int reserved[2];
 } msc_gemm_cfg;
 
 int msc_version(void);

@@ -27,7 +27,7 @@ class MscError(RuntimeError):
 class GemmCfg(ctypes.Structure):
     _fields_ = [("tile_n", ctypes.c_int), ("stages", ctypes.c_int), ("raster", ctypes.c_int),
                 ("max_ctas", ctypes.c_int), ("epilogue", ctypes.c_int),
-                ("reserved", ctypes.c_int * 3)]
+                ("cta_pair", ctypes.c_int), ("reserved", ctypes.c_int * 2)]
 
 
 _P, _I = ctypes.c_void_p, ctypes.c_int

@@ -22,10 +22,11 @@ KNOBS = {
     "stages": [0, 2, 3, 4, 5, 6],
     "raster": [0, 1],
     "max_ctas": [0, 128, 74],
+    "cta_pair": [0, 1],
 }
 #: knobs that swap the tile shape rather than retune it
-STRUCTURAL = ("tile_n",)
-DEFAULTS = {"tile_n": 128, "stages": 0, "raster": 0, "max_ctas": 0}
+STRUCTURAL = ("tile_n", "cta_pair")
+DEFAULTS = {"tile_n": 128, "stages": 0, "raster": 0, "max_ctas": 0, "cta_pair": 0}
 
 
 def _host_inputs():
@@ -67,7 +68,7 @@ def build():
 
     k = from_env(DEFAULTS)
     cfg = ops.GemmConfig(tile_n=int(k["tile_n"]), stages=int(k["stages"]), raster=int(k["raster"]),
-                         max_ctas=int(k["max_ctas"]))
+                         max_ctas=int(k["max_ctas"]), cta_pair=int(k["cta_pair"]))
     a_q, a_sf, b_q, b_sf = _inputs()
     alpha = torch.ones((L,), dtype=torch.float32, device=a_q.device)
     masked_m = torch.full((L,), M, dtype=torch.int32, device=a_q.device)

@@ -1,0 +1,376 @@
+// Block-scaled grouped GEMM on CTA pairs (tcgen05 cta_group::2): two CTAs of a cluster
+// compute one 256 x 256 output tile.  Each CTA loads its own 128 rows of A, its own 128 of
+// the tile's 256 B rows, the scales of its A rows and the scales of all 256 B rows, and keeps
+// its 128 x 256 fp32 accumulator in its own TMEM; the even CTA issues every tcgen05
+// instruction for both.  Sharing B between two SMs cuts the L2->SM operand stream per MMA
+// by 30 % against a 128 x 256 single-CTA tile, which is what bounds that kernel.
+//
+// No load here is multicast: every CTA fetches its own boxes.  The only cluster-wide
+// signalling is tcgen05.commit arriving on both CTAs' barriers and plain remote
+// mbarrier arrives.
+//
+// Barriers.  full[s] lives in the leader: its producer arrives once with the byte count of
+// BOTH CTAs' loads, every load (cta_group::2 form) credits the leader's barrier.  empty[s]
+// and acc_full are per CTA and are signalled in both by one commit.  acc_empty lives in
+// the leader and collects the arrives of both CTAs' epilogue warps.
+//
+// Same arithmetic, operand layout and masking rules as gemm_blockscaled.cu.
+#include "gemm_common.cuh"
+
+namespace msc {
+
+template <int STAGES>
+struct PairSmem {
+  static constexpr int kHeader = 1024;
+  static constexpr int kA = 128 * 128;
+  static constexpr int kB = 128 * 128;       // this CTA's half of the 256 B rows
+  static constexpr int kSfa = 4 * 512;
+  static constexpr int kSfb = 2 * 4 * 512;   // scales of all 256 B rows
+  static constexpr int kOffA = kHeader;
+  static constexpr int kOffB = kOffA + STAGES * kA;
+  static constexpr int kOffSfa = kOffB + STAGES * kB;
+  static constexpr int kOffSfb = kOffSfa + STAGES * kSfa;
+  static constexpr int kOffC = kOffSfb + STAGES * kSfb;
+  static constexpr int kEpiWarps = 8;
+  static constexpr int kThreads = (kEpiWarps + 2) * 32;
+  static constexpr int kCPerWarp = 4096;
+  static constexpr int kC = kEpiWarps * kCPerWarp;
+  static constexpr int kTotal = kOffC + kC;
+  static constexpr int kAlloc = kTotal + 1024;
+  static_assert(kAlloc <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
+};
+
+template <int KIND, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<STAGES>::kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_sfa,
+                 const __grid_constant__ CUtensorMap tmap_sfb,
+                 const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+  using L = PairSmem<STAGES>;
+  constexpr int kTileN = 256;
+  constexpr int kMmaWarp = L::kEpiWarps;
+  constexpr int kProducerWarp = L::kEpiWarps + 1;
+  constexpr int kSfaCols = 16, kSfbCols = 32, kSlotCols = kSfaCols + kSfbCols;
+  constexpr int kSfCol0 = kTileN;
+  static_assert(kSfCol0 + STAGES * kSlotCols <= 512, "scale slots do not fit in TMEM");
+  constexpr int kChunksPerStage = (KIND == KIND_NVFP4) ? 4 : 1;
+  constexpr uint32_t kSfBoxBytes = kChunksPerStage * 512;
+  constexpr uint32_t kStageBytes = L::kA + L::kB + 3 * kSfBoxBytes;  // per CTA
+  constexpr uint32_t kIdescBase =
+      (KIND == KIND_NVFP4)
+          ? ((1u << 7) | (1u << 10) | (uint32_t(kTileN >> 3) << 17) | (16u << 24))
+          : ((uint32_t(kTileN >> 3) << 17) | (1u << 23) | (16u << 24));
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - raw);
+
+  const uint32_t bar_full = sbase;                    // STAGES x 8 (used in the leader)
+  const uint32_t bar_empty = sbase + 8 * STAGES;      // STAGES x 8
+  const uint32_t bar_acc_full = sbase + 16 * STAGES;  // 8
+  const uint32_t bar_acc_empty = bar_acc_full + 8;    // 8 (used in the leader)
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + 512);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(sgen + 516);
+
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int npairs = gridDim.x >> 1;
+  const int ntiles = p.n / kTileN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, 2 * L::kEpiWarps);
+    *abort_flag = 0u;
+    fence_barrier_init();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_sfa);
+    tma_prefetch_desc(&tmap_sfb);
+    tma_prefetch_desc(&tmap_c);
+  }
+  if (warp == 0) {
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync();  // both CTAs' barriers are initialised before either touches the other's
+  tc_fence_after_sync();
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+
+  if (warp == kProducerWarp) {
+    // ------------------------------ producer (both CTAs) ------------------------
+    TileCursor cur;
+    cur.mshift = 8;
+    uint32_t bits = 0;  // per-stage use parity
+    bool ok = true;
+    for (int t = pair; ok; t += npairs) {
+      int mt, nt;
+      if (!cur.seek(p, ntiles, t, mt, nt)) break;
+      const int row0 = cur.off + (2 * mt + (int)rank) * 128;
+      const int brow0 = cur.g * p.n + nt * kTileN + (int)rank * 128;
+      const int sfa_row = (row0 >> 7) * p.sf_chunks * 4;
+      const int sfb_row = (cur.g * (p.n >> 7) + nt * 2) * p.sf_chunks * 4;
+      uint32_t s = 0;
+      for (int kb = 0; kb < p.k_stages; ++kb) {
+        ok = warp_wait(bar_empty + 8 * s, ((bits >> s) & 1u) ^ 1u, abort_flag, p.status, 1);
+        if (!ok) break;
+        bits ^= 1u << s;
+        const uint32_t full = bar_full + 8 * s;
+        const int c4 = kb * kChunksPerStage * 4;
+        if (elect_one()) {
+          if (leader) mbar_arrive_expect_tx(full, 2 * kStageBytes);
+          tma_load_2d_pair(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
+          tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, brow0);
+          tma_load_2d_pair(sbase + L::kOffSfa + s * L::kSfa, &tmap_sfa, full, 0, sfa_row + c4);
+          tma_load_2d_pair(sbase + L::kOffSfb + s * L::kSfb, &tmap_sfb, full, 0, sfb_row + c4);
+          tma_load_2d_pair(sbase + L::kOffSfb + s * L::kSfb + 2048, &tmap_sfb, full, 0,
+                           sfb_row + p.sf_chunks * 4 + c4);
+        }
+        __syncwarp();
+        s = (s + 1 == STAGES) ? 0u : s + 1;
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------ MMA issuer (leader only) --------------------
+    if (leader) {
+      TileCursor cur;
+      cur.mshift = 8;
+      uint32_t bits = 0;
+      int tl = 0;
+      bool ok = true;
+      const uint64_t adesc0 = operand_desc_sw128(sbase + L::kOffA);
+      const uint64_t bdesc0 = operand_desc_sw128(sbase + L::kOffB);
+      const uint64_t sfa_d0 = scale_desc(sbase + L::kOffSfa);
+      const uint64_t sfb_d0 = scale_desc(sbase + L::kOffSfb);
+      const uint32_t acc = tmem_base;
+      for (int t = pair; ok; t += npairs, ++tl) {
+        int mt, nt;
+        if (!cur.seek(p, ntiles, t, mt, nt)) break;
+        ok = warp_wait(bar_acc_empty, (uint32_t)(tl & 1) ^ 1u, abort_flag, p.status, 2);
+        if (!ok) break;
+        tc_fence_after_sync();
+        for (int kb0 = 0; kb0 < p.k_stages && ok; kb0 += STAGES) {
+#pragma unroll
+          for (int s = 0; s < STAGES; ++s) {
+            const int kb = kb0 + s;
+            if (kb >= p.k_stages) break;
+            ok = warp_wait(bar_full + 8 * s, (bits >> s) & 1u, abort_flag, p.status, 3);
+            if (!ok) break;
+            bits ^= 1u << s;
+            tc_fence_after_sync();
+            const int nch = min(kChunksPerStage, p.sf_chunks - kb * kChunksPerStage);
+            const int nmma = (KIND == KIND_NVFP4) ? nch : 4;
+            const uint32_t sfa_t = tmem_base + kSfCol0 + s * kSlotCols;
+            const uint32_t sfb_t = sfa_t + kSfaCols;
+            // descriptor low words count 16-byte units: +32 per 512-byte scale chunk, +128
+            // per 2048-byte block of 128 B rows, +2 per 32 bytes of K in the operand tile
+            const uint64_t sfa_d = sfa_d0 + s * (L::kSfa >> 4);
+            const uint64_t sfb_d = sfb_d0 + s * (L::kSfb >> 4);
+            const uint64_t adesc = adesc0 + s * (L::kA >> 4);
+            const uint64_t bdesc = bdesc0 + s * (L::kB >> 4);
+            if (elect_one()) {
+#pragma unroll
+              for (int c = 0; c < kChunksPerStage; ++c) {
+                if (c < nch) {
+                  tc_cp_32x128b_warpx4_pair(sfa_t + 4 * c, sfa_d + 32 * c);
+                  tc_cp_32x128b_warpx4_pair(sfb_t + 8 * c, sfb_d + 32 * c);
+                  tc_cp_32x128b_warpx4_pair(sfb_t + 8 * c + 4, sfb_d + 128 + 32 * c);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (j < nmma) {
+                  const uint32_t accumulate = (j > 0 || kb > 0) ? 1u : 0u;
+                  if (KIND == KIND_NVFP4) {
+                    tc_mma_nvfp4_pair(acc, adesc + 2 * j, bdesc + 2 * j, kIdescBase, sfa_t + 4 * j,
+                                      sfb_t + 8 * j, accumulate);
+                  } else {
+                    const uint32_t idesc = kIdescBase | (uint32_t(j) << 29) | (uint32_t(j) << 4);
+                    tc_mma_mxf8_pair(acc, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t,
+                                     accumulate);
+                  }
+                }
+              }
+              tc_commit_pair(bar_empty + 8 * s, 3);  // frees this stage in both CTAs
+            }
+            __syncwarp();
+          }
+        }
+        if (ok && elect_one()) tc_commit_pair(bar_acc_full, 3);
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ------------------------
+    // As in the single-CTA kernel: warp w drains lane quadrant w % 4, 128-column slab w / 4.
+    TileCursor cur;
+    cur.mshift = 8;
+    int tl = 0;
+    const int quad = warp & 3;
+    const int slab = warp >> 2;
+    const uint32_t lane_base = uint32_t(quad * 32) << 16;
+    const uint32_t box = sbase + L::kOffC + warp * L::kCPerWarp;
+    for (int t = pair;; t += npairs, ++tl) {
+      int mt, nt;
+      if (!cur.seek(p, ntiles, t, mt, nt)) break;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait_bounded(bar_acc_full, tl & 1, abort_flag, p.status, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row_warp = (2 * mt + (int)rank) * 128 + quad * 32;
+      const bool valid = row_warp + lane < cur.rows;
+      const bool whole_warp = row_warp + 32 <= cur.rows;
+      const size_t out_row = (size_t)cur.off + row_warp + lane;
+      float scale = p.alpha ? __ldg(p.alpha + cur.g) : 1.0f;
+      if (p.row_scale && valid) scale *= __ldg(p.row_scale + out_row);
+
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        tmem_ld_32x32b_x32(tmem_base + lane_base + slab * 128 + c * 32, v[c]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(bar_acc_empty & kLeaderMask);
+
+      const int col0 = nt * kTileN + slab * 128;
+      if (whole_warp) {
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+          if (lane == 0) bulk_wait_group_read0();  // earlier stores have left the staging box
+          __syncwarp();
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = sub * 2 + cc;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float lo = __uint_as_float(v[c][q * 8 + 2 * e]) * scale;
+                const float hi = __uint_as_float(v[c][q * 8 + 2 * e + 1]) * scale;
+                __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
+                w[e] = *reinterpret_cast<uint32_t*>(&pr);
+              }
+              const int j = cc * 4 + q;
+              const uint32_t addr = box + lane * 128 + ((j ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]),
+                           "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_c, box, col0 + sub * 64, cur.off + row_warp);
+            bulk_commit_group();
+          }
+        }
+      } else if (valid) {
+        __nv_bfloat16* dst = p.out + out_row * p.n + col0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float lo = __uint_as_float(v[c][q * 8 + 2 * e]) * scale;
+              const float hi = __uint_as_float(v[c][q * 8 + 2 * e + 1]) * scale;
+              __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
+              w[e] = *reinterpret_cast<uint32_t*>(&pr);
+            }
+            d4[q] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+    if (lane == 0) bulk_wait_group_read0();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait gave up somewhere: give loads still in flight time to land before the shared
+    // memory they target is released
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  cluster_sync();  // neither CTA leaves while the other may still read its memory or signal it
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+template <int KIND, int STAGES>
+static int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStream_t stream) {
+  using L = PairSmem<STAGES>;
+  auto kern = gemm_pair_kernel<KIND, STAGES>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  MSC_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+    configured[dev & 63] = true;
+  }
+  kern<<<grid, L::kThreads, L::kAlloc, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_total,
+                     long long k_bytes, const GemmParams& p, int stages, int max_ctas,
+                     cudaStream_t stream) {
+  if (p.n % 256) return fail(MSC_ERR_BAD_ARG, "the CTA-pair kernel needs n %% 256 == 0, got n=%d", p.n);
+  const int chunks_per_stage = (kind == KIND_NVFP4) ? 4 : 1;
+  CUtensorMap maps[5];
+  int rc = make_tmap_bytes_2d(&maps[0], a_q, (uint64_t)rows_total, (uint64_t)k_bytes, 128);
+  if (rc) return rc;
+  rc = make_tmap_bytes_2d(&maps[1], b_q, (uint64_t)p.l * p.n, (uint64_t)k_bytes, 128);
+  if (rc) return rc;
+  const uint64_t row_tiles = (uint64_t)(rows_total + 127) / 128;
+  rc = make_tmap_sf_2d(&maps[2], p.sfa, row_tiles * p.sf_chunks * 4, chunks_per_stage * 4);
+  if (rc) return rc;
+  rc = make_tmap_sf_2d(&maps[3], p.sfb, (uint64_t)p.l * (p.n / 128) * p.sf_chunks * 4,
+                       chunks_per_stage * 4);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&maps[4], p.out, (uint64_t)rows_total, (uint64_t)p.n, 32);
+  if (rc) return rc;
+
+  const long long max_tiles = ((rows_total + 255) / 256 + p.l) * (long long)(p.n / 256);
+  int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
+  if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
+  if (pairs > max_tiles) pairs = (int)max_tiles;
+  const int grid = 2 * pairs;
+  if (stages <= 0 || stages > 5) stages = 5;
+  if (stages < 2) stages = 2;
+  if (kind == KIND_NVFP4) {
+    switch (stages) {
+      case 2: return launch_pair<KIND_NVFP4, 2>(maps, p, grid, stream);
+      case 3: return launch_pair<KIND_NVFP4, 3>(maps, p, grid, stream);
+      case 4: return launch_pair<KIND_NVFP4, 4>(maps, p, grid, stream);
+      default: return launch_pair<KIND_NVFP4, 5>(maps, p, grid, stream);
+    }
+  }
+  switch (stages) {
+    case 2: return launch_pair<KIND_MXFP8, 2>(maps, p, grid, stream);
+    case 3: return launch_pair<KIND_MXFP8, 3>(maps, p, grid, stream);
+    case 4: return launch_pair<KIND_MXFP8, 4>(maps, p, grid, stream);
+    default: return launch_pair<KIND_MXFP8, 5>(maps, p, grid, stream);
+  }
+}
+
+}  // namespace msc

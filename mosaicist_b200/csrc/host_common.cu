@@ -57,7 +57,7 @@ namespace {
 struct TmapKey {
   const void* base;
   uint64_t rows, row_bytes;
-  uint32_t box_rows;  // bit 31 set: bf16 elements (store map), else bytes (operand map)
+  uint32_t box_rows;  // bit 31: bf16 store map; bit 30: unswizzled scale map; else operand map
   bool operator==(const TmapKey& o) const {
     return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows;
   }
@@ -71,17 +71,17 @@ struct TmapKeyHash {
   }
 };
 int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
-                   uint32_t box_rows, bool bf16);
+                   uint32_t box_rows, int flavour);
 }  // namespace
 
 // A tensor map only encodes address, shape and box, so one encoded for a buffer stays valid
 // for any later buffer at the same address with the same shape: cache them, the driver call
 // costs microseconds and the GEMM itself runs for about ten.
 static int cached_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
-                       uint32_t box_rows, bool bf16) {
+                       uint32_t box_rows, int flavour) {
   static std::mutex mu;
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
-  const TmapKey key{base, rows, row_bytes, box_rows | (bf16 ? 0x80000000u : 0u)};
+  const TmapKey key{base, rows, row_bytes, box_rows | ((uint32_t)flavour << 30)};
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
@@ -90,7 +90,7 @@ static int cached_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64
       return MSC_OK;
     }
   }
-  const int rc = encode_tmap_2d(map, base, rows, row_bytes, box_rows, bf16);
+  const int rc = encode_tmap_2d(map, base, rows, row_bytes, box_rows, flavour);
   if (rc == MSC_OK) {
     std::lock_guard<std::mutex> lock(mu);
     if (cache.size() > 4096) cache.clear();
@@ -101,17 +101,23 @@ static int cached_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64
 
 int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                        uint32_t box_rows) {
-  return cached_tmap(map, base, rows, row_bytes, box_rows, false);
+  return cached_tmap(map, base, rows, row_bytes, box_rows, 0);
 }
 
 int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                       uint32_t box_rows) {
-  return cached_tmap(map, base, rows, cols * 2, box_rows, true);
+  return cached_tmap(map, base, rows, cols * 2, box_rows, 2);
+}
+
+int make_tmap_sf_2d(CUtensorMap* map, const void* base, uint64_t rows128, uint32_t box_rows) {
+  return cached_tmap(map, base, rows128, 128, box_rows, 1);
 }
 
 namespace {
 int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
-                   uint32_t box_rows, bool bf16) {
+                   uint32_t box_rows, int flavour) {
+  const bool bf16 = flavour == 2;
+  const bool swizzled = flavour != 1;
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return MSC_ERR_CUDA;
   if (reinterpret_cast<uintptr_t>(base) % 16 || row_bytes % 16)
@@ -124,7 +130,8 @@ int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t r
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                    const_cast<void*>(base), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(MSC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);

@@ -22,9 +22,11 @@ class GemmConfig:
     stages: int = 0
     raster: int = 0
     max_ctas: int = 0
+    cta_pair: int = 0
 
     def c(self, epilogue: int = _lib.EPI_PLAIN) -> _lib.GemmCfg:
-        return _lib.GemmCfg(self.tile_n, self.stages, self.raster, self.max_ctas, epilogue)
+        return _lib.GemmCfg(self.tile_n, self.stages, self.raster, self.max_ctas, epilogue,
+                            self.cta_pair)
 
 
 def _ptr(t):

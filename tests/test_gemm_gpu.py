@@ -55,6 +55,11 @@ EXACT_CASES = [
     (2, 256, 512, 4096, {"tile_n": 256, "stages": 3, "raster": 1}),   # verify_b200.py k=4096
     (5, 384, 384, 320, {"max_ctas": 7}),       # more tiles than CTAs: persistent loop
     (2, 128, 256, 2048, {"stages": 6, "raster": 1}),
+    # two CTAs per 256x256 tile (cta_group::2), incl. an odd number of m-tiles per group
+    (1, 256, 256, 64, {"cta_pair": 1}),
+    (2, 512, 512, 576, {"cta_pair": 1}),
+    (3, 384, 256, 1024, {"cta_pair": 1, "stages": 2}),
+    (5, 512, 768, 1280, {"cta_pair": 1, "max_ctas": 6}),
 ]
 
 
@@ -88,7 +93,7 @@ def test_edge_groups_empty_and_single_row():
     assert np.isnan(got[0]).all()
 
 
-@pytest.mark.parametrize("cfg", [{}, {"tile_n": 256}])
+@pytest.mark.parametrize("cfg", [{}, {"tile_n": 256}, {"cta_pair": 1}])
 def test_random_operands_within_tolerance_and_gate(cfg):
     """Seeded N(0,1) operands quantised by the oracle with gs = 64 (test_kernels.py:43-48)."""
     l, m, n, k = 2, 256, 256, 512
@@ -124,8 +129,10 @@ def test_headline_shape_properties():
     one = torch.ones((l,), device="cuda")
     o1 = ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, one, None, ops.GemmConfig())
     o2 = ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, 2 * one, None, ops.GemmConfig(tile_n=256))
+    o3 = ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, one, None, ops.GemmConfig(cta_pair=1))
     assert _lib.status_word() == 0
     assert torch.equal(o1.float() * 2, o2.float())        # power-of-two alpha is exact in bf16
+    assert torch.equal(o1, o3)                            # every kernel variant, same bits
     gi = 5
     rows = slice(128, 160)
     ref = dequant_nvfp4(a_q[gi].cpu().numpy(), a_sf[gi].cpu().numpy())[rows] @ \
@@ -140,6 +147,8 @@ RAGGED = [
     ([200, 0, 50, 384], 256, 1024, {}),
     ([200, 0, 50, 384], 256, 1024, {"tile_n": 256}),
     ([1, 127, 129, 300, 5], 384, 640, {"max_ctas": 3}),
+    ([200, 0, 50, 384, 257], 256, 1024, {"cta_pair": 1}),
+    ([1, 127, 129, 300, 5], 512, 640, {"cta_pair": 1, "max_ctas": 4}),
 ]
 
 
