@@ -183,6 +183,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--stages", type=int, default=0)
+    ap.add_argument("--cta-pair", type=int, default=0, help="0 auto, 1 CTA pairs, 2 single CTA")
     ap.add_argument("--e2e-steps", type=int, default=30)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -217,7 +218,7 @@ def main():
     # data-path collective).  Rotate over enough operand sets that a step never finds its
     # inputs in L2.
     nsets = int(L2_BYTES * 2.5 // ALGO_BYTES) + 1            # 8 sets, 323 MB
-    cfg = ops.GemmConfig(tile_n=args.tile_n, stages=args.stages)
+    cfg = ops.GemmConfig(tile_n=args.tile_n, stages=args.stages, cta_pair=args.cta_pair)
     sets = [make_operands(1000 * rank + i, device) for i in range(nsets)]
     outs = [torch.empty((L, M, N), dtype=torch.bfloat16, device=device) for _ in range(nsets)]
     plans = [ops.masked_grouped_gemm_plan(s[0], s[1], s[2], s[3], s[4], None, cfg, out=o)
@@ -321,7 +322,9 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "e2m1 x e2m1 -> f32 -> bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "groups_per_gpu": L, "tile_n": cfg.tile_n or 128,
+            "config": {"workload": WORKLOAD, "groups_per_gpu": L,
+                       "kernel": ("single-CTA tiles 128x%d" % (cfg.tile_n or 128))
+                       if (cfg.cta_pair == 2 or cfg.tile_n) else "CTA-pair tiles 256x256 (cta_group::2)",
                        "l2": f"rotating over {nsets} operand sets ({nsets * ALGO_BYTES / 1e6:.0f} MB) "
                              f"> 126 MB L2: every step reads its operands from HBM",
                        "launch": "CUDA graph of one pass over the operand sets"},

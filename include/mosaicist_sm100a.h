@@ -46,8 +46,9 @@ typedef struct msc_gemm_cfg {
   int max_ctas;  /* persistent grid size; 0 = one CTA per SM                            */
   int epilogue;  /* MSC_EPI_*                                                            */
   int cta_pair;  /* 1: two CTAs share one 256x256 tile (tcgen05 cta_group::2; needs n % 256 == 0,
-                    ignores tile_n); the counterpart of the reference's `collective` knob
-                    (cand_pallas_gemm.py:31)                                              */
+                    ignores tile_n); 2: one CTA per tile; 0: the library chooses (pairs when
+                    tile_n is 0, n % 256 == 0 and groups have >= 256 rows).  The counterpart
+                    of the reference's `collective` knob (cand_pallas_gemm.py:31)          */
   int reserved[2];
 } msc_gemm_cfg;
 

@@ -18,15 +18,15 @@ SEED = 0
 
 #: the space the tuner walks, first value = default (knobs.py:57-58)
 KNOBS = {
-    "tile_n": [128, 256],
+    "tile_n": [0, 128, 256],
     "stages": [0, 2, 3, 4, 5, 6],
     "raster": [0, 1],
     "max_ctas": [0, 128, 74],
-    "cta_pair": [0, 1],
+    "cta_pair": [0, 1, 2],
 }
 #: knobs that swap the tile shape rather than retune it
 STRUCTURAL = ("tile_n", "cta_pair")
-DEFAULTS = {"tile_n": 128, "stages": 0, "raster": 0, "max_ctas": 0, "cta_pair": 0}
+DEFAULTS = {"tile_n": 0, "stages": 0, "raster": 0, "max_ctas": 0, "cta_pair": 0}
 
 
 def _host_inputs():

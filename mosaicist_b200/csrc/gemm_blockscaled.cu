@@ -474,6 +474,8 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   const int chunk_elems = (kind == KIND_NVFP4) ? 64 : 128;
   if (k % chunk_elems)
     return fail(MSC_ERR_BAD_ARG, "k=%d must be a multiple of %d", k, chunk_elems);
+  if (cfg.cta_pair < 0 || cfg.cta_pair > 2)
+    return fail(MSC_ERR_BAD_ARG, "cta_pair must be 0 (auto), 1 (pair) or 2 (single CTA)");
   if (cfg.epilogue != MSC_EPI_PLAIN && cfg.epilogue != MSC_EPI_ROW_SCALE)
     return fail(MSC_ERR_UNSUPPORTED, "unknown epilogue %d", cfg.epilogue);
   if (cfg.epilogue == MSC_EPI_ROW_SCALE && !row_scale)
@@ -514,7 +516,11 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   p.debug_flags = g_debug_flags;
 #endif
 
-  if (cfg.cta_pair)
+  // 0 = choose: pairs pay off when whole 256-row tiles are common and n allows 256-wide tiles
+  bool pair = cfg.cta_pair == 1;
+  if (cfg.cta_pair == 0 && cfg.tile_n == 0)
+    pair = (n % 256 == 0) && ((m_stride > 0 ? m_stride : rows_total / l) >= 256);
+  if (pair)
     return launch_pair_gemm(kind, a_q, b_q, rows_total, k_bytes, p, cfg.stages, cfg.max_ctas,
                             static_cast<cudaStream_t>(stream_v));
 

@@ -33,7 +33,9 @@ struct PairSmem {
   static constexpr int kOffC = kOffSfb + STAGES * kSfb;
   static constexpr int kEpiWarps = 8;
   static constexpr int kThreads = (kEpiWarps + 2) * 32;
-  static constexpr int kCPerWarp = 4096;
+  // two 4 KB store boxes per epilogue warp when the ring leaves room (up to 4 stages), so the
+  // second 64-column half never waits for the first half's store to drain
+  static constexpr int kCPerWarp = (STAGES <= 4) ? 8192 : 4096;
   static constexpr int kC = kEpiWarps * kCPerWarp;
   static constexpr int kTotal = kOffC + kC;
   static constexpr int kAlloc = kTotal + 1024;
@@ -108,6 +110,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   cluster_sync();  // both CTAs' barriers are initialised before either touches the other's
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+#ifdef MSC_DEBUG
+  if (p.trace && threadIdx.x == 0) {
+    p.trace[(size_t)gridDim.x * 48 + blockIdx.x * 2] = clock64();
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    p.trace[(size_t)gridDim.x * 50 + (size_t)blockIdx.x * 32 + 30] = gt;
+  }
+#endif
 
   if (warp == kProducerWarp) {
     // ------------------------------ producer (both CTAs) ------------------------
@@ -115,7 +125,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     cur.mshift = 8;
     uint32_t bits = 0;  // per-stage use parity
     bool ok = true;
-    for (int t = pair; ok; t += npairs) {
+    int tl = 0;
+    for (int t = pair; ok; t += npairs, ++tl) {
       int mt, nt;
       if (!cur.seek(p, ntiles, t, mt, nt)) break;
       const int row0 = cur.off + (2 * mt + (int)rank) * 128;
@@ -123,6 +134,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int sfa_row = (row0 >> 7) * p.sf_chunks * 4;
       const int sfb_row = (cur.g * (p.n >> 7) + nt * 2) * p.sf_chunks * 4;
       uint32_t s = 0;
+      MSC_STAMP(0, tl, 0);
       for (int kb = 0; kb < p.k_stages; ++kb) {
         ok = warp_wait(bar_empty + 8 * s, ((bits >> s) & 1u) ^ 1u, abort_flag, p.status, 1);
         if (!ok) break;
@@ -141,6 +153,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         __syncwarp();
         s = (s + 1 == STAGES) ? 0u : s + 1;
       }
+      MSC_STAMP(0, tl, 1);
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer (leader only) --------------------
@@ -161,6 +174,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         ok = warp_wait(bar_acc_empty, (uint32_t)(tl & 1) ^ 1u, abort_flag, p.status, 2);
         if (!ok) break;
         tc_fence_after_sync();
+        MSC_STAMP(1, tl, 0);
         for (int kb0 = 0; kb0 < p.k_stages && ok; kb0 += STAGES) {
 #pragma unroll
           for (int s = 0; s < STAGES; ++s) {
@@ -210,6 +224,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (ok && elect_one()) tc_commit_pair(bar_acc_full, 3);
         __syncwarp();
+        MSC_STAMP(1, tl, 1);
       }
     }
   } else {
@@ -221,7 +236,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int quad = warp & 3;
     const int slab = warp >> 2;
     const uint32_t lane_base = uint32_t(quad * 32) << 16;
-    const uint32_t box = sbase + L::kOffC + warp * L::kCPerWarp;
+    const uint32_t box0 = sbase + L::kOffC + warp * L::kCPerWarp;
+    constexpr bool kTwoBoxes = (L::kCPerWarp == 8192);
     for (int t = pair;; t += npairs, ++tl) {
       int mt, nt;
       if (!cur.seek(p, ntiles, t, mt, nt)) break;
@@ -230,6 +246,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (warp == 0) MSC_STAMP(2, tl, 0);
       const int row_warp = (2 * mt + (int)rank) * 128 + quad * 32;
       const bool valid = row_warp + lane < cur.rows;
       const bool whole_warp = row_warp + 32 <= cur.rows;
@@ -245,13 +262,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(bar_acc_empty & kLeaderMask);
+      if (warp == 0) MSC_STAMP(2, tl, 1);
+      if (MSC_FLAG(1)) continue;
 
       const int col0 = nt * kTileN + slab * 128;
       if (whole_warp) {
 #pragma unroll
         for (int sub = 0; sub < 2; ++sub) {
-          if (lane == 0) bulk_wait_group_read0();  // earlier stores have left the staging box
-          __syncwarp();
+          const uint32_t box = box0 + (kTwoBoxes ? sub * 4096 : 0);
+          if (!kTwoBoxes || sub == 0) {
+            if (lane == 0) bulk_wait_group_read0();  // earlier stores have left the staging box
+            __syncwarp();
+          }
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
             const int c = sub * 2 + cc;
@@ -303,6 +325,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   tc_fence_before_sync();
   __syncthreads();
+#ifdef MSC_DEBUG
+  if (p.trace && threadIdx.x == 0) {
+    p.trace[(size_t)gridDim.x * 48 + blockIdx.x * 2 + 1] = clock64();
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    p.trace[(size_t)gridDim.x * 50 + (size_t)blockIdx.x * 32 + 31] = gt;
+  }
+#endif
   if (*abort_flag) {
     // a wait gave up somewhere: give loads still in flight time to land before the shared
     // memory they target is released
@@ -355,7 +385,8 @@ int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_
   if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
   if (pairs > max_tiles) pairs = (int)max_tiles;
   const int grid = 2 * pairs;
-  if (stages <= 0 || stages > 5) stages = 5;
+  if (stages <= 0) stages = 4;
+  if (stages > 5) stages = 5;
   if (stages < 2) stages = 2;
   if (kind == KIND_NVFP4) {
     switch (stages) {
