@@ -138,6 +138,46 @@ int msc_nvfp4_quantize_ragged(const void* x, int x_dtype, const float* global_sc
 int msc_sf_swizzle(const void* sf_rowmajor, void* sf_tiled, int groups, int mn, int k_scales,
                    void* stream);
 
+/* ---- MoE routing and token movement ---------------------------------------------------
+ * The reference's MoE takes per-expert padded batches and has no routing, permutation or
+ * exchange code (experiments/flashinfer-megamoe-sm100a/moe.py:47-79; the only hint is that
+ * the per-expert alphas "are the routing weights", flashinfer-megamoe-sm90a/moe.py:69).
+ * These entry points build, from router logits, the row-concatenated 128-aligned group
+ * layout the *_ragged GEMMs consume, and fold the expert outputs back per token. */
+
+/* softmax over `experts` (multiple of 32, <= 1024), the `topk` (<= 32) largest, weights
+ * renormalised to sum to 1; ties go to the lower expert index.
+ * logits (tokens, experts) f32 -> ids (tokens, topk) i32, weights (tokens, topk) f32. */
+int msc_moe_route_topk(const float* logits, int32_t* ids, float* weights, int tokens, int experts,
+                       int topk, void* stream);
+
+/* For the experts [expert_first, expert_first + experts_local): rows per expert, the rank of
+ * every (token, k) pair inside its expert (token order), and 128-aligned group offsets.
+ * ids (entries) i32 with entries = tokens * topk; rank (entries) i32 is written only where the
+ * pair is routed to a local expert; group_rows, group_offsets (experts_local); total_rows (1):
+ * the padded row count.  scratch: one int32 of device memory, zero before the first call,
+ * left zero by every call (a ticket counter; calls sharing it must not overlap). */
+int msc_moe_plan(const int32_t* ids, int entries, int expert_first, int experts_local,
+                 int32_t* rank, int32_t* group_rows, int32_t* group_offsets, int32_t* total_rows,
+                 int32_t* scratch, void* stream);
+
+/* Gathers each locally routed token row (tokens (tokens, hidden) bf16), quantises it to NVFP4
+ * with its expert's global scale (arithmetic of quantize_nvfp4, nvfp4.py:39-57) and writes it
+ * at row group_offsets[e] + rank: a_q (rows_cap, hidden/2), a_sf tiled
+ * (rows_cap/128, hidden/64, 32, 16), plus row_weight (rows_cap) f32 = the pair's routing weight
+ * and row_token (rows_cap) i32.  rows_cap is a multiple of 128 >= total_rows.  hidden % 64 == 0. */
+int msc_moe_permute_quantize(const void* tokens_bf16, const int32_t* ids, const float* weights,
+                             const int32_t* rank, const int32_t* group_offsets,
+                             const float* input_gs, int tokens, int hidden, int topk,
+                             int expert_first, int experts_local, void* a_q, void* a_sf,
+                             float* row_weight, int32_t* row_token, void* stream);
+
+/* out[token] = bf16( sum over k (ascending, fp32) of y[group_offsets[e] + rank] ) over the
+ * pairs routed to local experts; y (rows_cap, hidden) bf16, out (tokens, hidden) bf16. */
+int msc_moe_unpermute(const void* y, const int32_t* ids, const int32_t* rank,
+                      const int32_t* group_offsets, void* out, int tokens, int hidden, int topk,
+                      int expert_first, int experts_local, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

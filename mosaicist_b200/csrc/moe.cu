@@ -1,0 +1,292 @@
+// MoE routing and token movement around the grouped GEMMs (all HBM-bound):
+//   route_topk        softmax over experts, top-k, renormalised weights  (one warp per token)
+//   plan              per-expert row counts, each (token, k) pair's rank inside its expert in
+//                     token order, and the 128-row-aligned offsets of the expert groups
+//   permute_quantize  gathers each routed token row, quantises it to NVFP4 with its expert's
+//                     global scale and writes it (values + tiled scales) at its group row
+//   unpermute         out[token] = sum over k of the expert outputs of that token
+// The reference has no routing or permutation code (its MoE takes per-expert padded batches,
+// experiments/flashinfer-megamoe-sm100a/moe.py:47-79); these kernels produce exactly the
+// row-concatenated, 128-aligned group layout the ragged GEMM entry points consume, with the
+// per-row arithmetic of quantize_nvfp4 (nvfp4.py:39-57).
+#include "host_common.h"
+#include "quantize_common.cuh"
+
+namespace msc {
+
+constexpr int kMaxExpertsPerLane = 32;  // experts <= 1024
+
+// ---- routing -----------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+route_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights,
+                  int tokens, int experts, int topk) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= tokens) return;
+  const float* row = logits + (size_t)warp * experts;
+  const int per = experts >> 5;
+  float v[kMaxExpertsPerLane];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    v[i] = (i < per) ? __ldg(row + lane + 32 * i) : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    v[i] = (i < per) ? expf(__fsub_rn(v[i], mx)) : -1.0f;   // -1 marks "not a candidate"
+    if (i < per) sum = __fadd_rn(sum, v[i]);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+
+  float my_w = 0.0f;
+  int my_id = 0;
+  float wsum = 0.0f;
+  for (int k = 0; k < topk; ++k) {
+    float best = -1.0f;
+    int best_i = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+      const int idx = lane + 32 * i;
+      if (v[i] > best || (v[i] == best && v[i] >= 0.0f && idx < best_i)) {
+        best = v[i];
+        best_i = idx;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ob > best || (ob == best && oi < best_i)) {
+        best = ob;
+        best_i = oi;
+      }
+    }
+    // the owner of the winning entry retires it (ties go to the lower expert index)
+    if ((best_i & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kMaxExpertsPerLane; ++i)
+        if (i == (best_i >> 5)) v[i] = -1.0f;
+    }
+    const float pk = __fdiv_rn(best, sum);
+    wsum = __fadd_rn(wsum, pk);
+    if (lane == k) {
+      my_w = pk;
+      my_id = best_i;
+    }
+  }
+  if (lane < topk) {
+    ids[(size_t)warp * topk + lane] = my_id;
+    weights[(size_t)warp * topk + lane] = __fdiv_rn(my_w, wsum);
+  }
+}
+
+// ---- plan --------------------------------------------------------------------------------
+// One block per local expert.  The block walks all (token, k) pairs in order, hands out ranks
+// to the pairs routed to its expert (so rows inside a group keep token order) and records the
+// group's row count.  The last block to finish (a ticket counter in `scratch`) turns the
+// counts into 128-aligned group offsets and resets the ticket for the next call.
+__global__ void __launch_bounds__(256)
+moe_plan_kernel(const int* __restrict__ ids, int entries, int expert_first, int experts_local,
+                int* __restrict__ rank, int* __restrict__ group_rows, int* __restrict__ group_offsets,
+                int* __restrict__ total_rows, int* __restrict__ scratch) {
+  __shared__ int warp_tot[8];
+  __shared__ int is_last;
+  const int e = blockIdx.x;
+  const int want = expert_first + e;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int running = 0;
+  for (int base = 0; base < entries; base += 256) {
+    const int i = base + threadIdx.x;
+    const bool hit = i < entries && __ldg(ids + i) == want;
+    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) warp_tot[warp] = __popc(ballot);
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const int c = warp_tot[w];
+      if (w < warp) before += c;
+      total += c;
+    }
+    if (hit) rank[i] = running + before + __popc(ballot & ((1u << lane) - 1u));
+    running += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    group_rows[e] = running;
+    __threadfence();
+    const int ticket = atomicAdd(scratch, 1);
+    is_last = (ticket == experts_local - 1);
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x == 0) {
+    __threadfence();
+    int off = 0;
+    for (int g = 0; g < experts_local; ++g) {
+      group_offsets[g] = off;
+      off += (__ldcg(group_rows + g) + 127) & ~127;
+    }
+    *total_rows = off;
+    *scratch = 0;  // ready for the next call
+  }
+}
+
+// ---- dispatch: gather + quantise ---------------------------------------------------------
+struct PermuteParams {
+  const __nv_bfloat16* tokens;   // (tokens, hidden)
+  const int* ids;                // (tokens, topk)
+  const float* weights;          // (tokens, topk)
+  const int* rank;               // (tokens, topk)
+  const int* group_offsets;      // (experts_local)
+  const float* gs;               // (experts_local) input global scale per expert
+  uint8_t* q;                    // (rows_cap, hidden/2)
+  uint8_t* sf;                   // tiled (rows_cap/128, hidden/64, 32, 16)
+  float* row_weight;             // (rows_cap)
+  int* row_token;                // (rows_cap)
+  int entries, hidden, topk, expert_first, experts_local;
+};
+
+__global__ void __launch_bounds__(256) moe_permute_quantize_kernel(const PermuteParams p) {
+  const int kwords = p.hidden >> 6;
+  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long entry = unit / kwords;
+  const int kw = (int)(unit - entry * kwords);
+  if (entry >= p.entries) return;
+  const int e = __ldg(p.ids + entry) - p.expert_first;
+  if (e < 0 || e >= p.experts_local) return;
+  const int dest = __ldg(p.group_offsets + e) + __ldg(p.rank + entry);
+  const int token = (int)(entry / p.topk);
+  float v[64];
+  load64_bf16(p.tokens + (size_t)token * p.hidden + kw * 64, v);
+  uint32_t q8[8], sf4;
+  quantize_64(v, __ldg(p.gs + e), q8, sf4);
+  uint4* qdst = reinterpret_cast<uint4*>(p.q + (size_t)dest * (p.hidden >> 1) + kw * 32);
+  qdst[0] = make_uint4(q8[0], q8[1], q8[2], q8[3]);
+  qdst[1] = make_uint4(q8[4], q8[5], q8[6], q8[7]);
+  *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word(dest, kw, kwords)) = sf4;
+  if (kw == 0) {
+    p.row_weight[dest] = __ldg(p.weights + entry);
+    p.row_token[dest] = token;
+  }
+}
+
+// ---- combine -----------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+moe_unpermute_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ ids,
+                     const int* __restrict__ rank, const int* __restrict__ group_offsets,
+                     __nv_bfloat16* __restrict__ out, int tokens, int hidden, int topk,
+                     int expert_first, int experts_local) {
+  const int vecs = hidden >> 3;  // 8 bf16 per thread
+  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long token = unit / vecs;
+  const int vc = (int)(unit - token * vecs);
+  if (token >= tokens) return;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int k = 0; k < topk; ++k) {
+    const long long entry = token * topk + k;
+    const int e = __ldg(ids + entry) - expert_first;
+    if (e < 0 || e >= experts_local) continue;
+    const int row = __ldg(group_offsets + e) + __ldg(rank + entry);
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(y + (size_t)row * hidden) + vc);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      acc[2 * j] = __fadd_rn(acc[2 * j], f.x);
+      acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], f.y);
+    }
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 pr = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    w[j] = *reinterpret_cast<uint32_t*>(&pr);
+  }
+  reinterpret_cast<uint4*>(out + (size_t)token * hidden)[vc] = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+static int launch_plan(const int32_t* ids, int entries, int expert_first, int experts_local,
+                       int32_t* rank, int32_t* group_rows, int32_t* group_offsets,
+                       int32_t* total_rows, int32_t* scratch, void* stream) {
+  if (!ids || !rank || !group_rows || !group_offsets || !total_rows || !scratch)
+    return fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (entries <= 0 || experts_local <= 0) return fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  moe_plan_kernel<<<experts_local, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, entries, expert_first, experts_local, rank, group_rows, group_offsets, total_rows, scratch);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+}  // namespace msc
+
+extern "C" {
+
+int msc_moe_route_topk(const float* logits, int32_t* ids, float* weights, int tokens, int experts,
+                       int topk, void* stream) {
+  if (!logits || !ids || !weights) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (tokens <= 0) return msc::fail(MSC_ERR_BAD_ARG, "tokens must be positive");
+  if (experts < 32 || experts > 32 * msc::kMaxExpertsPerLane || experts % 32)
+    return msc::fail(MSC_ERR_UNSUPPORTED, "experts=%d must be a multiple of 32 in [32, 1024]", experts);
+  if (topk < 1 || topk > 32 || topk > experts)
+    return msc::fail(MSC_ERR_UNSUPPORTED, "topk=%d must be in [1, 32]", topk);
+  const int blocks = (tokens + 3) / 4;
+  msc::route_topk_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, ids, weights, tokens, experts, topk);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+int msc_moe_plan(const int32_t* ids, int entries, int expert_first, int experts_local,
+                 int32_t* rank, int32_t* group_rows, int32_t* group_offsets, int32_t* total_rows,
+                 int32_t* scratch, void* stream) {
+  return msc::launch_plan(ids, entries, expert_first, experts_local, rank, group_rows,
+                          group_offsets, total_rows, scratch, stream);
+}
+
+int msc_moe_permute_quantize(const void* tokens_bf16, const int32_t* ids, const float* weights,
+                             const int32_t* rank, const int32_t* group_offsets,
+                             const float* input_gs, int tokens, int hidden, int topk,
+                             int expert_first, int experts_local, void* a_q, void* a_sf,
+                             float* row_weight, int32_t* row_token, void* stream) {
+  if (!tokens_bf16 || !ids || !weights || !rank || !group_offsets || !input_gs || !a_q || !a_sf ||
+      !row_weight || !row_token)
+    return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (tokens <= 0 || topk <= 0 || experts_local <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (hidden <= 0 || hidden % 64) return msc::fail(MSC_ERR_BAD_ARG, "hidden=%d must be a multiple of 64", hidden);
+  msc::PermuteParams p;
+  p.tokens = static_cast<const __nv_bfloat16*>(tokens_bf16);
+  p.ids = ids; p.weights = weights; p.rank = rank; p.group_offsets = group_offsets; p.gs = input_gs;
+  p.q = static_cast<uint8_t*>(a_q); p.sf = static_cast<uint8_t*>(a_sf);
+  p.row_weight = row_weight; p.row_token = row_token;
+  p.entries = tokens * topk; p.hidden = hidden; p.topk = topk;
+  p.expert_first = expert_first; p.experts_local = experts_local;
+  const long long units = (long long)p.entries * (hidden / 64);
+  const long long blocks = (units + 255) / 256;
+  if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
+  msc::moe_permute_quantize_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+int msc_moe_unpermute(const void* y, const int32_t* ids, const int32_t* rank,
+                      const int32_t* group_offsets, void* out, int tokens, int hidden, int topk,
+                      int expert_first, int experts_local, void* stream) {
+  if (!y || !ids || !rank || !group_offsets || !out) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (tokens <= 0 || topk <= 0 || experts_local <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (hidden <= 0 || hidden % 8) return msc::fail(MSC_ERR_BAD_ARG, "hidden=%d must be a multiple of 8", hidden);
+  const long long units = (long long)tokens * (hidden / 8);
+  const long long blocks = (units + 255) / 256;
+  if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
+  msc::moe_unpermute_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y), ids, rank, group_offsets,
+      static_cast<__nv_bfloat16*>(out), tokens, hidden, topk, expert_first, experts_local);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+}  // extern "C"

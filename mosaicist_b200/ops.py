@@ -193,9 +193,11 @@ def silu_mul_quantize_nvfp4(gateup, global_scale, masked_m=None, tiled_scales: b
     return q, sf
 
 
-def quantize_nvfp4_ragged(x, global_scale, group_offsets, group_rows, silu: bool = False):
+def quantize_nvfp4_ragged(x, global_scale, group_offsets, group_rows, silu: bool = False,
+                          out=None):
     """Ragged-layout quantiser: x (rows_total, k) -> q (rows_total, k/2) and tiled scales
-    (ceil(rows_total/128), k/64, 32, 16); with silu, x is (rows_total, 2k) gate|up."""
+    (ceil(rows_total/128), k/64, 32, 16); with silu, x is (rows_total, 2k) gate|up.  `out`
+    may carry preallocated (q, sf)."""
     _need(x, "x", (torch.bfloat16, torch.float32))
     rows_total = x.shape[0]
     k = x.shape[1] // 2 if silu else x.shape[1]
@@ -203,8 +205,14 @@ def quantize_nvfp4_ragged(x, global_scale, group_offsets, group_rows, silu: bool
     _need(global_scale, "global_scale", (torch.float32,), (l,))
     _need(group_offsets, "group_offsets", (torch.int32,), (l,))
     _need(group_rows, "group_rows", (torch.int32,), (l,))
-    q = torch.empty((rows_total, k // 2), dtype=torch.uint8, device=x.device)
-    sf = torch.zeros(((rows_total + 127) // 128, k // 64, 32, 16), dtype=torch.uint8, device=x.device)
+    if out is None:
+        q = torch.empty((rows_total, k // 2), dtype=torch.uint8, device=x.device)
+        sf = torch.zeros(((rows_total + 127) // 128, k // 64, 32, 16), dtype=torch.uint8,
+                         device=x.device)
+    else:
+        q, sf = out
+        _need(q, "q", (torch.uint8,), (rows_total, k // 2))
+        _need(sf, "sf", (torch.uint8,), ((rows_total + 127) // 128, k // 64, 32, 16))
     _lib.check(_lib.load().msc_nvfp4_quantize_ragged(
         _ptr(x), 0 if x.dtype == torch.bfloat16 else 1, _ptr(global_scale), _ptr(group_offsets),
         _ptr(group_rows), _ptr(q), _ptr(sf), l, rows_total, k, 1 if silu else 0, _stream()))

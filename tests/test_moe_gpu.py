@@ -1,0 +1,212 @@
+"""MoE routing, token movement and the expert layer against the CPU oracle.
+
+Byte-producing kernels (plan, gather + quantise, unpermute of exact data) are compared bit
+for bit; the layer itself within the bounds the reference uses for its MoE
+(test_kernels.py:94-102: max error < 1e-1 and rms < 1e-2 of max|want|), because one bf16 ulp
+of GEMM1 can become a whole e2m1 step after the intermediate requantisation."""
+
+import ml_dtypes
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe as M, nvfp4 as O
+
+pytestmark = pytest.mark.gpu
+
+
+def T(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _weights(E, h, n, seed):
+    rng = np.random.default_rng([seed, 0])
+    w1 = (rng.standard_normal((E, 2 * n, h)) * 0.05).astype(np.float32)
+    w2 = (rng.standard_normal((E, h, n)) * 0.05).astype(np.float32)
+    w1_gs, w2_gs = O.global_scale_for(w1), O.global_scale_for(w2)
+    w1_q, w1_sf = O.quantize_nvfp4(w1, w1_gs)
+    w2_q, w2_sf = O.quantize_nvfp4(w2, w2_gs)
+    w1_alpha = rng.uniform(0.5, 1.5, E).astype(np.float32)
+    w2_alpha = rng.uniform(0.5, 1.5, E).astype(np.float32)
+    return dict(w1_q=w1_q, w1_sf=w1_sf, w1_gs=w1_gs, w1_alpha=w1_alpha,
+                w2_q=w2_q, w2_sf=w2_sf, w2_gs=w2_gs, w2_alpha=w2_alpha)
+
+
+def _dev_weights(w):
+    return dict(w1_q=T(O.pack_e2m1(w["w1_q"])), w1_sf=T(O.e4m3_bytes(O.retile(w["w1_sf"]))),
+                w1_gs=T(w["w1_gs"]), w1_alpha=T(w["w1_alpha"]),
+                w2_q=T(O.pack_e2m1(w["w2_q"])), w2_sf=T(O.e4m3_bytes(O.retile(w["w2_sf"]))),
+                w2_gs=T(w["w2_gs"]), w2_alpha=T(w["w2_alpha"]))
+
+
+def _close(got, want):
+    scale = max(np.abs(want).max(), 1e-6)
+    rel = np.abs(got - want).max() / scale
+    rms = np.sqrt(np.mean((got - want) ** 2)) / scale
+    assert rel < 1e-1 and rms < 1e-2, (rel, rms)
+    assert np.count_nonzero(want) > want.size // 2
+    return rel, rms
+
+
+@pytest.mark.parametrize("T_,E,k", [(64, 32, 2), (300, 256, 8), (17, 64, 1)])
+def test_route_topk(T_, E, k):
+    from mosaicist_b200 import _lib
+
+    logits = np.random.default_rng([T_, E]).standard_normal((T_, E)).astype(np.float32)
+    ids = torch.empty((T_, k), dtype=torch.int32, device="cuda")
+    w = torch.empty((T_, k), dtype=torch.float32, device="cuda")
+    lt = T(logits)
+    _lib.check(_lib.load().msc_moe_route_topk(lt.data_ptr(), ids.data_ptr(), w.data_ptr(), T_, E, k,
+                                              torch.cuda.current_stream().cuda_stream))
+    want_ids, want_w = M.route_topk(logits, k)
+    assert np.array_equal(ids.cpu().numpy(), want_ids)
+    assert np.allclose(w.cpu().numpy(), want_w, rtol=2e-6, atol=0)
+    assert np.allclose(w.cpu().numpy().sum(1), 1.0, atol=1e-6)
+
+
+def test_route_ties_go_to_lower_index():
+    from mosaicist_b200 import _lib
+
+    logits = np.zeros((4, 64), np.float32)
+    logits[1, 40] = logits[1, 7] = 3.0
+    ids = torch.empty((4, 3), dtype=torch.int32, device="cuda")
+    w = torch.empty((4, 3), dtype=torch.float32, device="cuda")
+    lt = T(logits)
+    _lib.check(_lib.load().msc_moe_route_topk(lt.data_ptr(), ids.data_ptr(), w.data_ptr(), 4, 64, 3,
+                                              torch.cuda.current_stream().cuda_stream))
+    got = ids.cpu().numpy()
+    assert got[0].tolist() == [0, 1, 2] and got[1].tolist() == [7, 40, 0]
+
+
+@pytest.mark.parametrize("first,local", [(0, 32), (8, 8), (0, 4)])
+def test_plan_and_gather_quantise_bit_exact(first, local):
+    from mosaicist_b200 import _lib
+
+    T_, E, k, h = 200, 32, 4, 256
+    rng = np.random.default_rng([first, local])
+    logits = rng.standard_normal((T_, E)).astype(np.float32)
+    logits[:, 5] = -30.0                              # an expert nobody picks: an empty group
+    ids, w = M.route_topk(logits, k)
+    tokens = rng.standard_normal((T_, h)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    gs = rng.uniform(200, 800, local).astype(np.float32)
+    want_rank, want_rows, want_offs, want_tot = M.plan(ids, first, local)
+
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    d_ids, d_w = T(ids), T(w)
+    rank = torch.full((T_, k), -7, dtype=torch.int32, device="cuda")
+    rows = torch.zeros(local, dtype=torch.int32, device="cuda")
+    offs = torch.zeros(local, dtype=torch.int32, device="cuda")
+    tot = torch.zeros(1, dtype=torch.int32, device="cuda")
+    scratch = torch.zeros(4, dtype=torch.int32, device="cuda")
+    for _ in range(2):                                # the ticket counter resets itself
+        _lib.check(lib.msc_moe_plan(d_ids.data_ptr(), T_ * k, first, local, rank.data_ptr(),
+                                    rows.data_ptr(), offs.data_ptr(), tot.data_ptr(),
+                                    scratch.data_ptr(), st))
+    assert int(scratch[0]) == 0
+    assert np.array_equal(rows.cpu().numpy(), want_rows) and np.array_equal(offs.cpu().numpy(), want_offs)
+    assert int(tot[0]) == want_tot
+    local_mask = (ids >= first) & (ids < first + local)
+    assert np.array_equal(rank.cpu().numpy()[local_mask], want_rank[local_mask])
+    assert (rank.cpu().numpy()[~local_mask] == -7).all()
+
+    cap = (T_ * k + 127 * local + 127) // 128 * 128
+    a_q = torch.zeros((cap, h // 2), dtype=torch.uint8, device="cuda")
+    a_sf = torch.zeros((cap // 128, h // 64, 32, 16), dtype=torch.uint8, device="cuda")
+    rw = torch.zeros(cap, dtype=torch.float32, device="cuda")
+    rt = torch.full((cap,), -1, dtype=torch.int32, device="cuda")
+    tk = T(np.asarray(tokens, np.float32)).to(torch.bfloat16)
+    gst = T(gs)
+    _lib.check(lib.msc_moe_permute_quantize(tk.data_ptr(), d_ids.data_ptr(), d_w.data_ptr(),
+                                            rank.data_ptr(), offs.data_ptr(), gst.data_ptr(), T_, h, k,
+                                            first, local, a_q.data_ptr(), a_sf.data_ptr(),
+                                            rw.data_ptr(), rt.data_ptr(), st))
+    qh, rth, rwh = a_q.cpu().numpy(), rt.cpu().numpy(), rw.cpu().numpy()
+    sfh = np.asarray(__import__("mosaicist_b200.formats", fromlist=["x"]).from_mma_scale_layout(
+        a_sf.cpu().numpy(), cap))
+    seen = 0
+    for t in range(T_):
+        for kk in range(k):
+            le = ids[t, kk] - first
+            if not 0 <= le < local:
+                continue
+            row = want_offs[le] + want_rank[t, kk]
+            q, sf = O.quantize_nvfp4(np.asarray(tokens[t:t + 1], np.float32)[None], gs[le:le + 1])
+            assert np.array_equal(qh[row], O.pack_e2m1(q)[0, 0])
+            assert np.array_equal(sfh[row], O.e4m3_bytes(sf)[0, 0])
+            assert rth[row] == t and rwh[row] == w[t, kk]
+            seen += 1
+    assert seen == int(want_rows.sum()) and seen > 0 and (want_rows == 0).any() == (first <= 5 < first + local)
+
+
+def test_unpermute_exact():
+    from mosaicist_b200 import _lib
+
+    T_, E, k, h = 100, 32, 4, 64
+    rng = np.random.default_rng(3)
+    ids, _ = M.route_topk(rng.standard_normal((T_, E)).astype(np.float32), k)
+    rank, rows, offs, tot = M.plan(ids, 0, E)
+    y = rng.integers(-8, 9, (tot, h)).astype(np.float32)       # exact in bf16, sums exact in fp32
+    want = np.zeros((T_, h), np.float32)
+    for t in range(T_):
+        for kk in range(k):
+            want[t] += y[offs[ids[t, kk]] + rank[t, kk]]
+    out = torch.empty((T_, h), dtype=torch.bfloat16, device="cuda")
+    yt = T(y).to(torch.bfloat16)
+    di, dr, do = T(ids), T(rank), T(offs)
+    _lib.check(_lib.load().msc_moe_unpermute(yt.data_ptr(), di.data_ptr(), dr.data_ptr(), do.data_ptr(),
+                                             out.data_ptr(), T_, h, k, 0, E,
+                                             torch.cuda.current_stream().cuda_stream))
+    assert np.array_equal(out.float().cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("l,m,k,n", [(2, 256, 512, 256), (3, 128, 512, 512)])     # test_kernels.py:94-95
+def test_moe_masked_matches_reference_layer(l, m, k, n):
+    from mosaicist_b200 import _lib
+    from mosaicist_b200.moe import moe_masked
+
+    w = _weights(l, k, n, seed=l)
+    rng = np.random.default_rng([l, 1])
+    hidden = rng.standard_normal((l, m, k)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    masked_m = np.array(([m, max(1, m // 2 - 3)] + [m] * l)[:l], np.int32)
+    in_gs = O.global_scale_for(np.asarray(hidden, np.float32))
+    a_q, a_sf = O.quantize_nvfp4(hidden, in_gs)
+    gateup = O.masked_grouped_gemm_reference(a_q, a_sf, in_gs, w["w1_q"], w["w1_sf"], w["w1_gs"],
+                                             w["w1_alpha"], masked_m)
+    a2_gs = O.global_scale_for(O.silu_mul(gateup))               # moe.py:101-106
+    want = np.asarray(O.moe_reference(hidden, w["w1_q"], w["w1_sf"], w["w1_gs"], w["w1_alpha"],
+                                      w["w2_q"], w["w2_sf"], w["w2_gs"], w["w2_alpha"], masked_m,
+                                      in_gs, a2_gs), np.float32)
+    d = _dev_weights(w)
+    got = moe_masked(T(np.asarray(hidden, np.float32)).to(torch.bfloat16), d["w1_q"], d["w1_sf"],
+                     d["w1_gs"], d["w1_alpha"], d["w2_q"], d["w2_sf"], d["w2_gs"], d["w2_alpha"],
+                     T(masked_m), T(in_gs), T(a2_gs))
+    assert _lib.status_word() == 0
+    rows = np.arange(m)[None, :, None] < masked_m[:, None, None]
+    _close(np.where(rows, got.float().cpu().numpy(), 0), want)
+
+
+@pytest.mark.parametrize("T_,E,k,h,n,first,local", [(256, 32, 4, 256, 128, 0, 32),
+                                                     (384, 32, 2, 512, 256, 8, 8)])
+def test_megamoe_layer(T_, E, k, h, n, first, local):
+    from mosaicist_b200 import _lib
+    from mosaicist_b200.moe import MegaMoE
+
+    w = _weights(local, h, n, seed=T_)
+    rng = np.random.default_rng([T_, 2])
+    tokens = rng.standard_normal((T_, h)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    logits = rng.standard_normal((T_, E)).astype(np.float32)
+    input_gs = np.full(local, 2688.0 / np.abs(np.asarray(tokens, np.float32)).max(), np.float32)
+    a2_gs = np.full(local, 2688.0 / 4.0, np.float32)
+    ids, wts = M.route_topk(logits, k)
+    want = M.routed_moe(tokens, ids, wts, w["w1_q"], w["w1_sf"], w["w1_gs"], w["w1_alpha"], w["w2_q"],
+                        w["w2_sf"], w["w2_gs"], w["w2_alpha"], input_gs, a2_gs, first)
+    d = _dev_weights(w)
+    layer = MegaMoE(d["w1_q"], d["w1_sf"], d["w1_gs"], d["w1_alpha"], d["w2_q"], d["w2_sf"], d["w2_gs"],
+                    d["w2_alpha"], T(input_gs), T(a2_gs), topk=k, max_tokens=T_, expert_first=first)
+    tk = T(np.asarray(tokens, np.float32)).to(torch.bfloat16)
+    for _ in range(2):                                 # workspaces and the plan ticket are reusable
+        got = layer.forward(tk, T(logits)).float().cpu().numpy()
+    assert _lib.status_word() == 0
+    assert np.array_equal(layer.ids.cpu().numpy(), ids)
+    _close(got, want)
