@@ -39,12 +39,12 @@ def _dev_weights(w):
                 w2_gs=T(w["w2_gs"]), w2_alpha=T(w["w2_alpha"]))
 
 
-def _close(got, want):
+def _close(got, want, nonzero_fraction=0.5):
     scale = max(np.abs(want).max(), 1e-6)
     rel = np.abs(got - want).max() / scale
     rms = np.sqrt(np.mean((got - want) ** 2)) / scale
     assert rel < 1e-1 and rms < 1e-2, (rel, rms)
-    assert np.count_nonzero(want) > want.size // 2
+    assert np.count_nonzero(want) > want.size * nonzero_fraction
     return rel, rms
 
 
@@ -209,4 +209,5 @@ def test_megamoe_layer(T_, E, k, h, n, first, local):
         got = layer.forward(tk, T(logits)).float().cpu().numpy()
     assert _lib.status_word() == 0
     assert np.array_equal(layer.ids.cpu().numpy(), ids)
-    _close(got, want)
+    # with 8 of 32 experts local most tokens get no contribution: expect about 1 - (3/4)^2 non-zero
+    _close(got, want, nonzero_fraction=0.5 if local == E else 0.25)
