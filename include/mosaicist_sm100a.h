@@ -161,6 +161,20 @@ int msc_moe_plan(const int32_t* ids, int entries, int expert_first, int experts_
                  int32_t* rank, int32_t* group_rows, int32_t* group_offsets, int32_t* total_rows,
                  int32_t* scratch, void* stream);
 
+/* msc_moe_plan for callers that cannot allocate device memory (a serving loop whose pool is
+ * frozen, a plugin inside a framework that owns all allocations): the ticket counter lives
+ * in a 4352-byte array built into the library, and so do the row counts / total when
+ * group_rows / total_rows are NULL.  No counterpart in the reference.  Limits and rules:
+ *   - experts_local <= 1024, larger values are rejected with MSC_ERR_BAD_ARG;
+ *   - the library never calls an allocator here; the first call on a device looks up the
+ *     array's device address (cudaGetSymbolAddress), so make that first call outside any
+ *     stream capture;
+ *   - all calls on a device share the one array (it keeps the last call's counts): two calls
+ *     that overlap on the GPU race, even on different streams. */
+int msc_moe_plan_noalloc(const int32_t* ids, int entries, int expert_first, int experts_local,
+                         int32_t* rank, int32_t* group_rows, int32_t* group_offsets,
+                         int32_t* total_rows, void* stream);
+
 /* Gathers each locally routed token row (tokens (tokens, hidden) bf16), quantises it to NVFP4
  * with its expert's global scale (arithmetic of quantize_nvfp4, nvfp4.py:39-57) and writes it
  * at row group_offsets[e] + rank: a_q (rows_cap, hidden/2), a_sf tiled

@@ -48,6 +48,7 @@ SIGNATURES = {
     "msc_sf_swizzle": (_I, [_P, _P, _I, _I, _I, _P]),
     "msc_moe_route_topk": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "msc_moe_plan": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "msc_moe_plan_noalloc": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P]),
     "msc_moe_permute_quantize": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "msc_moe_unpermute": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
 }

@@ -12,6 +12,8 @@
 #include "host_common.h"
 #include "quantize_common.cuh"
 
+#include <mutex>
+
 namespace msc {
 
 constexpr int kMaxExpertsPerLane = 32;  // experts <= 1024
@@ -222,9 +224,59 @@ static int launch_plan(const int32_t* ids, int entries, int expert_first, int ex
   return MSC_OK;
 }
 
+// ---- plan without caller-provided or allocated scratch ------------------------------------
+// Some hosts of this library may not allocate device memory at the point where they plan a
+// batch: a serving loop whose memory pool is frozen after start-up, a plugin called from a
+// framework that owns every allocation, code running between the steps of a captured
+// pipeline.  For them the ticket counter, and the row counts and total when the caller does
+// not ask for them, live in this fixed array inside the library image.  Every device that
+// loads the library carries these 4352 bytes until the process exits.
+constexpr int kPlanStaticMaxExperts = 1024;
+constexpr int kPlanStaticCountsAt = 64;   // [0] ticket, [1] total rows, [64...] row counts
+static __device__ __align__(256) int g_plan_scratch[kPlanStaticCountsAt + kPlanStaticMaxExperts];
+
+// Device address of g_plan_scratch on the current device.  In host code the symbol name is
+// only a handle, never an address a kernel may be given; the address comes from the runtime,
+// once per device, with that device current.
+static int plan_scratch_address(int** out) {
+  static std::mutex mu;
+  static int* cached[64] = {nullptr};
+  int dev = 0;
+  MSC_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(MSC_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    int* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_plan_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(MSC_ERR_CUDA, "cudaGetSymbolAddress(plan scratch): %s", cudaGetErrorString(e));
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return MSC_OK;
+}
+
 }  // namespace msc
 
 extern "C" {
+
+int msc_moe_plan_noalloc(const int32_t* ids, int entries, int expert_first, int experts_local,
+                         int32_t* rank, int32_t* group_rows, int32_t* group_offsets,
+                         int32_t* total_rows, void* stream) {
+  if (experts_local > msc::kPlanStaticMaxExperts)
+    return msc::fail(MSC_ERR_BAD_ARG,
+                     "experts_local=%d exceeds the %d experts the built-in scratch area holds; "
+                     "use msc_moe_plan with caller-provided scratch",
+                     experts_local, msc::kPlanStaticMaxExperts);
+  int* scratch = nullptr;
+  const int rc = msc::plan_scratch_address(&scratch);
+  if (rc) return rc;
+  // the ticket must be zero when the kernel starts, whatever an earlier call left behind
+  MSC_CUDA_OK(cudaMemsetAsync(scratch, 0, sizeof(int), static_cast<cudaStream_t>(stream)));
+  return msc::launch_plan(ids, entries, expert_first, experts_local, rank,
+                          group_rows ? group_rows : scratch + msc::kPlanStaticCountsAt,
+                          group_offsets, total_rows ? total_rows : scratch + 1, scratch, stream);
+}
 
 int msc_moe_route_topk(const float* logits, int32_t* ids, float* weights, int tokens, int experts,
                        int topk, void* stream) {
