@@ -207,6 +207,7 @@ def main():
     device = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG", "WARN")     # keep NCCL's banner off stdout
         dist.init_process_group("nccl", device_id=device)
 
     def barrier():

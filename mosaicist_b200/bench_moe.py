@@ -1,0 +1,145 @@
+"""Benchmark of the routed MoE layer at the DeepSeek-V3 shape: 8192 tokens, hidden 7168,
+256 experts, top-8 softmax routing, expert intermediate 2048, SwiGLU, NVFP4 weights and
+activations.
+
+    python -m mosaicist_b200.bench_moe [--tokens 8192] [--steps 20]
+    python -m torch.distributed.run --nproc-per-node N -m mosaicist_b200.bench_moe --gpus N
+
+One GPU runs all 256 experts; N GPUs run expert-parallel (256/N experts and 8192/N tokens per
+rank, NCCL all-to-all dispatch and combine).  Weights are random bytes in the NVFP4 layout
+(values uniform over the e2m1 codes, block scales in a narrow e4m3 range): the timing does not
+depend on their values, and quantising 6 GB of weights from fp32 would dominate set-up.
+Prints one JSON line: layer TFLOP/s (2 * routed rows * (hidden * 2n + n * hidden)), time per
+layer, and the time of each stage on one GPU.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+
+import torch
+
+
+def rand_weights(E, n, h, dev, seed):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    w1_q = torch.randint(0, 256, (E, 2 * n, h // 2), dtype=torch.uint8, device=dev, generator=g)
+    w2_q = torch.randint(0, 256, (E, h, n // 2), dtype=torch.uint8, device=dev, generator=g)
+    w1_sf = torch.randint(0x28, 0x38, (E, 2 * n // 128, h // 64, 32, 16), dtype=torch.uint8, device=dev, generator=g)
+    w2_sf = torch.randint(0x28, 0x38, (E, h // 128, n // 64, 32, 16), dtype=torch.uint8, device=dev, generator=g)
+    one = torch.ones((E,), dtype=torch.float32, device=dev)
+    return w1_q, w1_sf, one * 64, one, w2_q, w2_sf, one * 64, one
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--hidden", type=int, default=7168)
+    ap.add_argument("--inter", type=int, default=2048)
+    ap.add_argument("--experts", type=int, default=256)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+
+    import torch.distributed as dist
+
+    from . import _lib, ops
+    from .moe import MegaMoE
+    from .parallel import ExpertParallelMoE
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG", "WARN")
+        dist.init_process_group("nccl", device_id=dev)
+    E, k, h, n = args.experts, args.topk, args.hidden, args.inter
+    E_loc, T_loc = E // world, args.tokens // world
+    w = rand_weights(E_loc, n, h, dev, 17 + rank)
+    gs_in = torch.full((E_loc,), 2688.0 / 5.0, dtype=torch.float32, device=dev)
+    gs_a2 = torch.full((E_loc,), 2688.0 / 8.0, dtype=torch.float32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    tokens = torch.randn((T_loc, h), device=dev, generator=g).to(torch.bfloat16)
+    logits = torch.randn((T_loc, E), device=dev, generator=g)
+
+    if world == 1:
+        layer = MegaMoE(*w, gs_in, gs_a2, topk=k, max_tokens=T_loc)
+        run = lambda: layer.forward(tokens, logits)
+    else:
+        # a rank can receive up to 2x its even share before the workspace is exceeded
+        inner = MegaMoE(*w, gs_in, gs_a2, topk=1, max_tokens=2 * T_loc * k, expert_first=rank * E_loc)
+        layer = ExpertParallelMoE(inner, E, k)
+        run = lambda: layer.forward(tokens, logits)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        run()
+    barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(args.steps):
+        run()
+    e.record()
+    barrier()
+    ms = s.elapsed_time(e) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    assert _lib.status_word() == 0
+    flop = 2.0 * args.tokens * k * (h * 2 * n + n * h)
+    out = {"metric": "megamoe_layer_tflops", "value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "n_gpus": world, "ms_per_layer": ms, "steps": args.steps,
+           "config": {"workload": f"MegaMoE tokens={args.tokens} hidden={h} experts={E} top{k} inter={n}",
+                      "parallelism": "single GPU" if world == 1 else f"ep{world}, all-to-all bf16 dispatch + combine"}}
+
+    if world == 1:
+        # per-stage device times on one GPU
+        lib = _lib.load()
+        L = layer
+        st = torch.cuda.current_stream().cuda_stream
+        stages = {
+            "route": lambda: L.route(logits),
+            "plan": lambda: _lib.check(lib.msc_moe_plan(L.ids.data_ptr(), T_loc * k, 0, E_loc, L.rank.data_ptr(),
+                                                        L.group_rows.data_ptr(), L.group_offsets.data_ptr(),
+                                                        L.total_rows.data_ptr(), L.scratch.data_ptr(), st)),
+            "gather_quantize": lambda: _lib.check(lib.msc_moe_permute_quantize(
+                tokens.data_ptr(), L.ids.data_ptr(), L.weights.data_ptr(), L.rank.data_ptr(),
+                L.group_offsets.data_ptr(), L.input_gs.data_ptr(), T_loc, h, k, 0, E_loc, L.a_q.data_ptr(),
+                L.a_sf.data_ptr(), L.row_weight.data_ptr(), L.row_token.data_ptr(), st)),
+            "gemm1": lambda: ops.ragged_grouped_gemm_nvfp4(L.a_q, L.a_sf, L.w1_q, L.w1_sf, L.group_offsets,
+                                                            L.group_rows, L.alpha1, None, L.config, out=L.gateup),
+            "silu_mul_quantize": lambda: ops.quantize_nvfp4_ragged(L.gateup, L.a2_gs, L.group_offsets,
+                                                                    L.group_rows, silu=True, out=(L.d_q, L.d_sf)),
+            "gemm2": lambda: ops.ragged_grouped_gemm_nvfp4(L.d_q, L.d_sf, L.w2_q, L.w2_sf, L.group_offsets,
+                                                            L.group_rows, L.alpha2, L.row_weight, L.config, out=L.y),
+        }
+        per = {}
+        for name, fn in stages.items():
+            fn(); torch.cuda.synchronize()
+            s.record()
+            for _ in range(5):
+                fn()
+            e.record(); torch.cuda.synchronize()
+            per[name] = s.elapsed_time(e) * 1e3 / 5
+        out["stage_us"] = per
+        out["rows"] = int(L.total_rows[0])
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
