@@ -43,6 +43,8 @@ def main():
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--cta-pair", type=int, default=0)
+    ap.add_argument("--tile-n", type=int, default=0)
     args = ap.parse_args()
 
     import torch.distributed as dist
@@ -69,12 +71,14 @@ def main():
     tokens = torch.randn((T_loc, h), device=dev, generator=g).to(torch.bfloat16)
     logits = torch.randn((T_loc, E), device=dev, generator=g)
 
+    cfg = ops.GemmConfig(tile_n=args.tile_n, cta_pair=args.cta_pair)
     if world == 1:
-        layer = MegaMoE(*w, gs_in, gs_a2, topk=k, max_tokens=T_loc)
+        layer = MegaMoE(*w, gs_in, gs_a2, topk=k, max_tokens=T_loc, config=cfg)
         run = lambda: layer.forward(tokens, logits)
     else:
         # a rank can receive up to 2x its even share before the workspace is exceeded
-        inner = MegaMoE(*w, gs_in, gs_a2, topk=1, max_tokens=2 * T_loc * k, expert_first=rank * E_loc)
+        inner = MegaMoE(*w, gs_in, gs_a2, topk=1, max_tokens=2 * T_loc * k, expert_first=rank * E_loc,
+                        config=cfg)
         layer = ExpertParallelMoE(inner, E, k)
         run = lambda: layer.forward(tokens, logits)
 

@@ -154,27 +154,31 @@ struct PermuteParams {
 };
 
 __global__ void __launch_bounds__(256) moe_permute_quantize_kernel(const PermuteParams p) {
-  const int kwords = p.hidden >> 6;
+  const int kblocks = p.hidden >> 4;
   const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long entry = unit / kwords;
-  const int kw = (int)(unit - entry * kwords);
-  if (entry >= p.entries) return;
-  const int e = __ldg(p.ids + entry) - p.expert_first;
-  if (e < 0 || e >= p.experts_local) return;
-  const int dest = __ldg(p.group_offsets + e) + __ldg(p.rank + entry);
-  const int token = (int)(entry / p.topk);
-  float v[64];
-  load64_bf16(p.tokens + (size_t)token * p.hidden + kw * 64, v);
-  uint32_t q8[8], sf4;
-  quantize_64(v, __ldg(p.gs + e), q8, sf4);
-  uint4* qdst = reinterpret_cast<uint4*>(p.q + (size_t)dest * (p.hidden >> 1) + kw * 32);
-  qdst[0] = make_uint4(q8[0], q8[1], q8[2], q8[3]);
-  qdst[1] = make_uint4(q8[4], q8[5], q8[6], q8[7]);
-  *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word(dest, kw, kwords)) = sf4;
-  if (kw == 0) {
-    p.row_weight[dest] = __ldg(p.weights + entry);
-    p.row_token[dest] = token;
+  const long long entry = unit / kblocks;
+  const int kb = (int)(unit - entry * kblocks);
+  int e = -1;
+  if (entry < p.entries) e = __ldg(p.ids + entry) - p.expert_first;
+  const bool valid = e >= 0 && e < p.experts_local;   // uniform over the 4 lanes of a unit
+  uint32_t sfb = 0;
+  int dest = 0;
+  if (valid) {
+    dest = __ldg(p.group_offsets + e) + __ldg(p.rank + entry);
+    const int token = (int)(entry / p.topk);
+    float v[16];
+    load16_bf16(p.tokens + (size_t)token * p.hidden + kb * 16, v);
+    uint2 q8;
+    quantize_16(v, __ldg(p.gs + e), q8, sfb);
+    *reinterpret_cast<uint2*>(p.q + (size_t)dest * (p.hidden >> 1) + kb * 8) = q8;
+    if (kb == 0) {
+      p.row_weight[dest] = __ldg(p.weights + entry);
+      p.row_token[dest] = token;
+    }
   }
+  const uint32_t word = gather_scale_word(sfb);
+  if (valid && (kb & 3) == 0)
+    *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word(dest, kb >> 2, kblocks >> 2)) = word;
 }
 
 // ---- combine -----------------------------------------------------------------------------
@@ -317,7 +321,7 @@ int msc_moe_permute_quantize(const void* tokens_bf16, const int32_t* ids, const 
   p.row_weight = row_weight; p.row_token = row_token;
   p.entries = tokens * topk; p.hidden = hidden; p.topk = topk;
   p.expert_first = expert_first; p.experts_local = experts_local;
-  const long long units = (long long)p.entries * (hidden / 64);
+  const long long units = (long long)p.entries * (hidden / 16);
   const long long blocks = (units + 255) / 256;
   if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
   msc::moe_permute_quantize_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);

@@ -8,10 +8,9 @@
 //   step = f32(sf) / gs
 //   q    = e2m1_rne( clip(x / step, -6, 6) )           (0 when step == 0)
 // every operation in IEEE fp32 (explicit _rn intrinsics, so no contraction or approximate
-// division can change a rounding).  One thread owns four consecutive blocks (64
-// elements: 128 B of bf16 in, 32 B of e2m1 and 4 scale bytes out), so a warp reads 4 KB of
-// one row contiguously and the four scale bytes of a thread are one aligned 32-bit word in
-// both scale layouts.
+// division can change a rounding).  One thread owns one block of 16 elements (32 B of bf16
+// in, 8 B of e2m1 out); four neighbouring lanes pool their scale bytes into one aligned
+// 32-bit word, which is a unit of both scale layouts.
 #include "host_common.h"
 #include "quantize_common.cuh"
 
@@ -48,68 +47,55 @@ __device__ __forceinline__ int group_of_row(const QuantParams& p, long long row,
   return lo;
 }
 
+// One thread per block of 16 elements: a warp reads 1 KB of one row with two fully used
+// 16-byte loads per lane and writes 256 contiguous bytes of e2m1; four neighbouring lanes
+// pool their scale bytes into one aligned 32-bit store.
 __global__ void __launch_bounds__(256) nvfp4_quantize_kernel(const QuantParams p) {
-  const int kwords = p.k >> 6;  // 64-element units per row
+  const int kblocks = p.k >> 4;
   const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long row = unit / kwords;
-  const int kw = (int)(unit - row * kwords);
-  if (row >= p.rows_total) return;
-  bool valid;
-  const int g = group_of_row(p, row, valid);
-  if (!valid) return;
-  const float gs = __ldg(p.gs + g);
-
-  float v[64];
-  if (p.silu) {
-    // row holds [gate (k) | up (k)] in bf16; activation stays fp32 (nvfp4.py:81-88)
-    const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.x) + row * 2 * p.k + kw * 64;
-    const uint4* g4 = reinterpret_cast<const uint4*>(base);
-    const uint4* u4 = reinterpret_cast<const uint4*>(base + p.k);
+  const long long row = unit / kblocks;
+  const int kb = (int)(unit - row * kblocks);
+  // whole warps stay alive for the shuffle below; k % 64 == 0 keeps a row's lanes in fours
+  bool valid = row < p.rows_total;
+  int g = 0;
+  if (valid) g = group_of_row(p, row, valid);
+  float v[16];
+  uint2 q8 = make_uint2(0, 0);
+  uint32_t sfb = 0;
+  if (valid) {
+    const float gs = __ldg(p.gs + g);
+    if (p.silu) {
+      // row holds [gate (k) | up (k)] in bf16; activation stays fp32 (nvfp4.py:81-88)
+      const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.x) + row * 2 * p.k + kb * 16;
+      float gt[16], up[16];
+      load16_bf16(base, gt);
+      load16_bf16(base + p.k, up);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint4 gv = __ldg(g4 + i), uv = __ldg(u4 + i);
-      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
-      const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 gf = __bfloat1622float2(gp[j]), uf = __bfloat1622float2(up[j]);
-        const float s0 = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gf.x)));
-        const float s1 = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gf.y)));
-        v[i * 8 + j * 2] = __fmul_rn(__fmul_rn(s0, gf.x), uf.x);
-        v[i * 8 + j * 2 + 1] = __fmul_rn(__fmul_rn(s1, gf.y), uf.y);
+      for (int i = 0; i < 16; ++i) {
+        const float sg = __frcp_rn(__fadd_rn(1.0f, expf(-gt[i])));
+        v[i] = __fmul_rn(__fmul_rn(sg, gt[i]), up[i]);
       }
-    }
-  } else if (p.f32_in) {
-    const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + row * p.k + kw * 64);
+    } else if (p.f32_in) {
+      const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + row * p.k + kb * 16);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float4 f = __ldg(src + i);
-      v[i * 4] = f.x; v[i * 4 + 1] = f.y; v[i * 4 + 2] = f.z; v[i * 4 + 3] = f.w;
-    }
-  } else {
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.x) + row * p.k + kw * 64);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint4 raw = __ldg(src + i);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(h[j]);
-        v[i * 8 + j * 2] = f.x;
-        v[i * 8 + j * 2 + 1] = f.y;
+      for (int i = 0; i < 4; ++i) {
+        const float4 f = __ldg(src + i);
+        v[i * 4] = f.x; v[i * 4 + 1] = f.y; v[i * 4 + 2] = f.z; v[i * 4 + 3] = f.w;
       }
+    } else {
+      load16_bf16(static_cast<const __nv_bfloat16*>(p.x) + row * p.k + kb * 16, v);
     }
+    quantize_16(v, gs, q8, sfb);
+    *reinterpret_cast<uint2*>(p.q + row * (p.k >> 1) + kb * 8) = q8;
   }
-
-  uint32_t q8[8], sf4;
-  quantize_64(v, gs, q8, sf4);
-  uint4* qdst = reinterpret_cast<uint4*>(p.q + row * (p.k >> 1) + kw * 32);
-  qdst[0] = make_uint4(q8[0], q8[1], q8[2], q8[3]);
-  qdst[1] = make_uint4(q8[4], q8[5], q8[6], q8[7]);
-  if (p.tiled)
-    *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word((int)row, kw, kwords)) = sf4;
-  else
-    *reinterpret_cast<uint32_t*>(p.sf + row * (p.k >> 4) + kw * 4) = sf4;
+  const uint32_t word = gather_scale_word(sfb);
+  if (valid && (kb & 3) == 0) {
+    const int kw = kb >> 2, kwords = kblocks >> 2;
+    if (p.tiled)
+      *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word((int)row, kw, kwords)) = word;
+    else
+      *reinterpret_cast<uint32_t*>(p.sf + row * (p.k >> 4) + kw * 4) = word;
+  }
 }
 
 // (groups, mn, kwords*4) row-major scale bytes -> (groups, ceil(mn/128), kwords, 32, 16),
@@ -153,7 +139,7 @@ static int quantize_common(const void* x, int x_dtype, const float* gs, const in
   p.q = static_cast<uint8_t*>(q); p.sf = static_cast<uint8_t*>(sf);
   p.l = l; p.m_stride = m_stride; p.k = k; p.rows_total = rows_total;
   p.tiled = sf_layout; p.silu = silu; p.f32_in = x_dtype;
-  const long long units = rows_total * (k / 64);
+  const long long units = rows_total * (k / 16);
   const int threads = 256;
   const long long blocks = (units + threads - 1) / threads;
   if (blocks > 0x7fffffffLL) return fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");

@@ -23,46 +23,65 @@ __device__ __forceinline__ size_t tiled_sf_word(int row, int kword, int kwords) 
   return (((size_t)t * kwords + kword) * 32 + b) * 16 + 4 * a;
 }
 
-// Quantises 64 fp32 values held as v[64] into 32 bytes + 4 scale bytes.
-__device__ __forceinline__ void quantize_64(const float* v, float gs, uint32_t* q8, uint32_t& sf4) {
-  sf4 = 0;
-#pragma unroll
-  for (int blk = 0; blk < 4; ++blk) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[blk * 16 + i]));
-    float s = __fmul_rn(__fdiv_rn(amax, 6.0f), gs);
-    s = fminf(fmaxf(s, 0.0f), 448.0f);
-    const uint8_t sfb = (uint8_t)__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
-    const float step = __fdiv_rn(e4m3_to_float(sfb), gs);
-    // a dead block (step == 0) keeps the sign of x: x / 1 * 0 = +-0, as the reference computes
-    const float live = (step > 0.0f) ? 1.0f : 0.0f;
-    const float safe = (step == 0.0f) ? 1.0f : step;
-    sf4 |= (uint32_t)sfb << (8 * blk);
-#pragma unroll
-    for (int w = 0; w < 2; ++w) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int pr = 0; pr < 4; ++pr) {
-        const int i = blk * 16 + w * 8 + pr * 2;
-        float x0 = __fmul_rn(__fdiv_rn(v[i], safe), live);
-        float x1 = __fmul_rn(__fdiv_rn(v[i + 1], safe), live);
-        x0 = fminf(fmaxf(x0, -6.0f), 6.0f);
-        x1 = fminf(fmaxf(x1, -6.0f), 6.0f);
-        const __nv_fp4x2_storage_t b2 =
-            __nv_cvt_float2_to_fp4x2(make_float2(x0, x1), __NV_E2M1, cudaRoundNearest);
-        word |= (uint32_t)b2 << (8 * pr);
-      }
-      q8[blk * 2 + w] = word;
-    }
-  }
+// a / b rounded to nearest, given rb = RN(1 / b): one multiply and two fused multiply-adds
+// (q = RN(a rb); r = a - q b exactly; q' = RN(q + r rb)), which is the correctly rounded
+// quotient whenever rb is the correctly rounded reciprocal and nothing overflows; the block
+// quantiser divides 16 values by the same step, so the reciprocal is shared.
+__device__ __forceinline__ float div_rn_shared_rcp(float a, float b, float rb) {
+  const float q = __fmul_rn(a, rb);
+  const float r = __fmaf_rn(-q, b, a);
+  const float qc = __fmaf_rn(r, rb, q);
+  return (fabsf(q) <= 3.0e38f) ? qc : q;   // keep +-inf (and NaN) instead of inf - inf
 }
 
-// Loads 64 consecutive bf16 values (128 bytes, 16-byte aligned) as fp32.
-__device__ __forceinline__ void load64_bf16(const __nv_bfloat16* src, float* v) {
+// Quantises one block of 16 fp32 values into 8 bytes of e2m1 and its e4m3 scale byte.
+__device__ __forceinline__ void quantize_16(const float* v, float gs, uint2& q8, uint32_t& sfb) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  float s = __fmul_rn(__fdiv_rn(amax, 6.0f), gs);
+  s = fminf(fmaxf(s, 0.0f), 448.0f);
+  sfb = (uint32_t)(uint8_t)__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
+  const float step = __fdiv_rn(e4m3_to_float((uint8_t)sfb), gs);
+  // a dead block (step == 0) keeps the sign of x: x / 1 * 0 = +-0, as the reference computes
+  const float live = (step > 0.0f) ? 1.0f : 0.0f;
+  const float safe = (step == 0.0f) ? 1.0f : step;
+  const float rsafe = __frcp_rn(safe);
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int pr = 0; pr < 4; ++pr) {
+      const int i = h * 8 + pr * 2;
+      float x0 = __fmul_rn(div_rn_shared_rcp(v[i], safe, rsafe), live);
+      float x1 = __fmul_rn(div_rn_shared_rcp(v[i + 1], safe, rsafe), live);
+      x0 = fminf(fmaxf(x0, -6.0f), 6.0f);
+      x1 = fminf(fmaxf(x1, -6.0f), 6.0f);
+      const __nv_fp4x2_storage_t b2 =
+          __nv_cvt_float2_to_fp4x2(make_float2(x0, x1), __NV_E2M1, cudaRoundNearest);
+      word |= (uint32_t)b2 << (8 * pr);
+    }
+    w[h] = word;
+  }
+  q8 = make_uint2(w[0], w[1]);
+}
+
+// The four lanes that own the four blocks of one 64-element unit (lane & 3 = block index)
+// assemble their scale bytes into one 32-bit word, valid in the lane with (lane & 3) == 0.
+__device__ __forceinline__ uint32_t gather_scale_word(uint32_t sfb) {
+  uint32_t w = sfb;
+  w |= __shfl_down_sync(0xffffffffu, sfb, 1) << 8;
+  w |= __shfl_down_sync(0xffffffffu, sfb, 2) << 16;
+  w |= __shfl_down_sync(0xffffffffu, sfb, 3) << 24;
+  return w;
+}
+
+// Loads 16 consecutive bf16 values (32 bytes, 16-byte aligned) as fp32.
+__device__ __forceinline__ void load16_bf16(const __nv_bfloat16* src, float* v) {
   const uint4* s4 = reinterpret_cast<const uint4*>(src);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < 2; ++i) {
     const uint4 raw = __ldg(s4 + i);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
