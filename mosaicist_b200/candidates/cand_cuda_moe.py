@@ -1,0 +1,95 @@
+"""Capture module for the CUDA masked MoE path (drop-in for the reference's
+experiments/loop/cand_pallas_moe.py): quantise -> GEMM1 -> SiLU*up + quantise -> GEMM2 at
+l=8 experts, m=512 rows each, k=2048 hidden, n=1024 intermediate, the shape the reference
+times end to end (experiments/flashinfer-megamoe-sm100a/README.md:45-51).
+
+Weights ~ 0.05 N(0,1) quantised with their own global scales, alphas ~ U[0.5, 1.5], the
+second global scale taken from one forward pass of the activation (the recipe of
+make_moe_inputs, moe.py:82-115).  Time this module with `--measure all`: the path is four
+kernels, not one (src/mosaicist/capture.py:127-140).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+from ._common import drop_artifacts, from_env
+
+L, M, K, N = 8, 512, 2048, 1024
+SEED = 0
+
+KNOBS = {
+    "tile_n": [0, 128, 256],
+    "stages": [0, 2, 3, 4],
+    "cta_pair": [0, 1, 2],
+}
+STRUCTURAL = ("tile_n", "cta_pair")
+DEFAULTS = {"tile_n": 0, "stages": 0, "cta_pair": 0}
+
+
+def _inputs():
+    """Device tensors in the order moe_masked takes them."""
+    import torch
+
+    from .. import ops
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rng = [np.random.default_rng([SEED, i]) for i in range(4)]
+    hidden = torch.from_numpy(rng[0].standard_normal((L, M, K)).astype(np.float32)).to(dev).to(torch.bfloat16)
+    w1 = torch.from_numpy((rng[1].standard_normal((L, 2 * N, K)) * 0.05).astype(np.float32)).to(dev)
+    w2 = torch.from_numpy((rng[2].standard_normal((L, K, N)) * 0.05).astype(np.float32)).to(dev)
+    alphas = torch.from_numpy(rng[3].uniform(0.5, 1.5, (2, L)).astype(np.float32)).to(dev)
+
+    def gs_for(x):                                   # global_scale_for, nvfp4.py:29-36
+        amax = x.float().abs().amax(dim=(1, 2))
+        return (2688.0 / torch.where(amax == 0, torch.ones_like(amax), amax)).contiguous()
+
+    w1_gs, w2_gs, in_gs = gs_for(w1), gs_for(w2), gs_for(hidden)
+    w1_q, w1_sf = ops.quantize_nvfp4(w1, w1_gs)
+    w2_q, w2_sf = ops.quantize_nvfp4(w2, w2_gs)
+    masked_m = torch.full((L,), M, dtype=torch.int32, device=dev)
+    # a2 global scale from one pass of the activation (moe.py:101-106)
+    a_q, a_sf = ops.quantize_nvfp4(hidden, in_gs)
+    gateup = ops.masked_grouped_gemm(a_q, a_sf, w1_q, w1_sf,
+                                     (alphas[0] / (in_gs * w1_gs)).contiguous(), masked_m)
+    g, u = gateup.float().chunk(2, dim=-1)
+    a2_gs = gs_for(torch.sigmoid(g) * g * u)
+    return (hidden, w1_q, w1_sf, w1_gs, alphas[0].contiguous(), w2_q, w2_sf, w2_gs,
+            alphas[1].contiguous(), masked_m, in_gs, a2_gs)
+
+
+def reference():
+    """float64 opinion on the same inputs: the layer with exact (unrounded) intermediates
+    except where the path itself quantises (the two NVFP4 quantisations are part of the
+    definition of the layer, so they are applied here too, on float64 values)."""
+    from ..formats import dequant_nvfp4
+
+    (hidden, w1_q, w1_sf, w1_gs, w1_alpha, w2_q, w2_sf, w2_gs, w2_alpha, masked_m, in_gs,
+     a2_gs) = _inputs()
+    from .. import ops
+
+    a_q, a_sf = ops.quantize_nvfp4(hidden, in_gs)
+    gateup = ops.masked_grouped_gemm(a_q, a_sf, w1_q, w1_sf, (w1_alpha / (in_gs * w1_gs)).contiguous(),
+                                     masked_m)
+    d_q, d_sf = ops.silu_mul_quantize_nvfp4(gateup, a2_gs, masked_m)
+    out = np.empty((L, M, K), np.float64)
+    d_qh, d_sfh, w2_qh, w2_sfh = (t.cpu().numpy() for t in (d_q, d_sf, w2_q, w2_sf))
+    scale = (w2_alpha / (a2_gs * w2_gs)).double().cpu().numpy()
+    for g in range(L):
+        out[g] = dequant_nvfp4(d_qh[g], d_sfh[g]) @ dequant_nvfp4(w2_qh[g], w2_sfh[g]).T * scale[g]
+    return out
+
+
+def build():
+    from .. import ops
+    from ..moe import moe_masked
+
+    k = from_env(DEFAULTS)
+    cfg = ops.GemmConfig(tile_n=int(k["tile_n"]), stages=int(k["stages"]), cta_pair=int(k["cta_pair"]))
+    args = _inputs()
+    drop_artifacts()
+
+    def fn():
+        return moe_masked(*args, gemm1_config=cfg, gemm2_config=cfg)
+
+    return fn, ()

@@ -91,6 +91,16 @@ def test_candidate_module_contract(monkeypatch):
     assert spec["out_dtype"] == "bfloat16"
 
 
+def test_moe_candidate_module_contract():
+    import importlib
+
+    m = importlib.import_module("mosaicist_b200.candidates.cand_cuda_moe")
+    assert callable(m.build) and callable(m.reference)
+    assert {k: v[0] for k, v in m.KNOBS.items()} == m.DEFAULTS and set(m.STRUCTURAL) <= set(m.KNOBS)
+    spec = json.loads((ROOT / "mosaicist_b200/candidates/spec_nvfp4_moe.json").read_text())
+    assert spec["dims"] == {"l": m.L, "m": m.M, "k": m.K, "n": m.N}
+
+
 def test_candidate_module_against_reference_harness(monkeypatch):
     """When the reference checkout is present, its own loader and knob space accept the
     module unchanged."""
