@@ -138,6 +138,16 @@ int msc_nvfp4_quantize_ragged(const void* x, int x_dtype, const float* global_sc
 int msc_sf_swizzle(const void* sf_rowmajor, void* sf_tiled, int groups, int mn, int k_scales,
                    void* stream);
 
+/* Dense 16-bit GEMM: C(m, n) = A(m, k) * B(k, n), all row-major, fp16 (dtype 0) or bf16
+ * (dtype 1) in and out, fp32 accumulation.  The reference's dense benchmark problem
+ * (experiments/hopper_gemm/gen_inputs.py:26-27, ref_cutedsl.py:50-74; its kernels are
+ * third-party Hopper wgmma code, this is a tcgen05 CTA-pair kernel with 256x256 tiles).
+ * lda / ldb / ldc are row pitches in elements, so a column shard of B and C (the N-sharded
+ * multi-GPU form) is the shard's base pointer with the parent's pitch.  k, n and the pitches
+ * must be multiples of 8; m, n, k need not be tile multiples.  max_ctas 0 = one CTA per SM. */
+int msc_gemm_f16(const void* a, const void* b, void* c, int m, int n, int k, int lda, int ldb,
+                 int ldc, int dtype, int max_ctas, void* stream);
+
 /* ---- MoE routing and token movement ---------------------------------------------------
  * The reference's MoE takes per-expert padded batches and has no routing, permutation or
  * exchange code (experiments/flashinfer-megamoe-sm100a/moe.py:47-79; the only hint is that

@@ -139,6 +139,25 @@ int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t r
 }
 }  // namespace
 
+int make_tmap_pitched_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                         uint64_t pitch_bytes, uint32_t box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return MSC_ERR_CUDA;
+  if (reinterpret_cast<uintptr_t>(base) % 16 || pitch_bytes % 16 || row_bytes % 16)
+    return fail(MSC_ERR_BAD_ARG, "matrix base, row length and pitch must be 16-byte aligned");
+  if (box_rows == 0 || box_rows > 256) return fail(MSC_ERR_BAD_ARG, "box rows out of range");
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {128u, box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MSC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return MSC_OK;
+}
+
 int num_sms() {
   static int cached[64] = {0};
   int dev = 0;

@@ -39,6 +39,12 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
 // (each 512-byte chunk is four such rows).
 int make_tmap_sf_2d(CUtensorMap* map, const void* base, uint64_t rows128, uint32_t box_rows);
 
+// 2-D byte tensor [rows][row_bytes] whose rows are `pitch_bytes` apart, with a
+// [box_rows][128 B] box and 128-byte swizzle (operands and outputs of the dense GEMM, where a
+// shard of a larger matrix keeps the parent's pitch).
+int make_tmap_pitched_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                         uint64_t pitch_bytes, uint32_t box_rows);
+
 int num_sms();
 
 #define MSC_CUDA_OK(expr)                                                              \

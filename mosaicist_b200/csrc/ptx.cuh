@@ -322,6 +322,20 @@ __device__ __forceinline__ void tc_mma_mxf8_pair(uint32_t d_tmem, uint64_t adesc
       : "memory");
 }
 
+// Dense 16-bit MMA on a CTA pair: D[tmem] (+)= A[smem] * B[smem], fp32 accumulation,
+// K = 16 per instruction.
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // ---- descriptors -------------------------------------------------------------------
 // Shared-memory matrix descriptor (64-bit): start address >> 4 in bits [0,14), leading
 // byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1
@@ -331,6 +345,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t sbo_bytes
   const uint32_t lo = (saddr >> 4) & 0x3FFFu;
   const uint32_t hi = ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (swizzle_mode << 29);
   return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+// MN-major operand tile with the 128-byte swizzle (the operand's contiguous axis is M or N,
+// not K): 64-element groups of the contiguous axis are `lbo_bytes` apart, groups of 8 K rows
+// 1024 bytes apart.
+__device__ __forceinline__ uint64_t operand_desc_mn_sw128(uint32_t saddr, uint32_t lbo_bytes) {
+  return smem_desc(saddr, 1024u, 2u) | (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16);
 }
 // K-major operand tile, rows of 128 bytes, 128-byte swizzle: 8-row groups are 1024 B apart.
 __device__ __forceinline__ uint64_t operand_desc_sw128(uint32_t saddr) {

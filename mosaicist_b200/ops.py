@@ -231,3 +231,25 @@ def to_mma_scale_layout(sf):
     out = torch.empty((g, (mn + 127) // 128, ks // 4, 32, 16), dtype=sf.dtype, device=sf.device)
     _lib.check(_lib.load().msc_sf_swizzle(_ptr(sf), _ptr(out), g, mn, ks, _stream()))
     return out[0] if squeeze else out
+
+
+def gemm_f16(a, b, out=None, max_ctas: int = 0):
+    """C = A @ B for 2-D fp16 or bf16 CUDA tensors, A (m, k) and B (k, n) row-major (rows may be
+    strided: a column slice of a wider matrix works as is), fp32 accumulation, output in the
+    input dtype.  The reference's dense problem (experiments/hopper_gemm/ref_cutedsl.py:50-74)."""
+    if a.dtype != b.dtype or a.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("a and b must both be float16 or both bfloat16")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
+        raise ValueError(f"shapes {tuple(a.shape)} and {tuple(b.shape)} do not multiply")
+    if not (a.is_cuda and b.is_cuda) or a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("a and b must be CUDA tensors with unit stride along their rows")
+    m, k = a.shape
+    n = b.shape[1]
+    if out is None:
+        out = torch.empty((m, n), dtype=a.dtype, device=a.device)
+    elif out.dtype != a.dtype or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise ValueError("out must be (m, n) in the input dtype with unit stride along rows")
+    _lib.check(_lib.load().msc_gemm_f16(_ptr(a), _ptr(b), _ptr(out), m, n, k, a.stride(0), b.stride(0),
+                                        out.stride(0), 0 if a.dtype == torch.float16 else 1, max_ctas,
+                                        _stream()))
+    return out
