@@ -148,6 +148,23 @@ int msc_sf_swizzle(const void* sf_rowmajor, void* sf_tiled, int groups, int mn, 
 int msc_gemm_f16(const void* a, const void* b, void* c, int m, int n, int k, int lda, int ldb,
                  int ldc, int dtype, int max_ctas, void* stream);
 
+/* Mixed-dtype grouped GEMM (bf16 activations x int4 weights with bf16 group scales), as two
+ * launches.  Semantics of the reference's port of CUTLASS example 69
+ * (ports/hopper_mixed_dtype_grouped_gemm/problems.py:1-16, 75-87): dequant(B)[n, k] =
+ * bf16(bf16(Bq[n, k]) * scale[n, k / group_size]) with the multiply in bf16, then
+ * D_g = alpha_g * A_g dequant(B_g)^T accumulated in fp32.  (The reference never ported the int4
+ * variants, ports/.../README.md:95; its kernel is Hopper wgmma code.)
+ *   msc_int4_dequant_bf16: q (groups, n, k/2) bytes, two int4 per byte, element 2i in the low
+ *     nibble, two's complement [-8, 7]; scales (groups, n, k/group_size) bf16 -> out (groups, n, k) bf16.
+ *   msc_grouped_gemm_bf16_ragged: a (rows_total, k) bf16, row-concatenated groups as in
+ *     msc_grouped_gemm_nvfp4_ragged; b (l, n, k) bf16 K-contiguous; alpha (l) f32 or NULL;
+ *     out (rows_total, n) bf16.  n % 256 == 0, k % 8 == 0. */
+int msc_int4_dequant_bf16(const void* q, const void* scales, void* out, int groups, int n, int k,
+                          int group_size, void* stream);
+int msc_grouped_gemm_bf16_ragged(const void* a, const void* b, const float* alpha,
+                                 const int32_t* group_offsets, const int32_t* group_rows, void* out,
+                                 int l, int rows_total, int n, int k, int max_ctas, void* stream);
+
 /* ---- MoE routing and token movement ---------------------------------------------------
  * The reference's MoE takes per-expert padded batches and has no routing, permutation or
  * exchange code (experiments/flashinfer-megamoe-sm100a/moe.py:47-79; the only hint is that

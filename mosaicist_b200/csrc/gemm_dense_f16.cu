@@ -11,20 +11,28 @@
 // 512 TMEM columns hold two 256-column accumulators, so the epilogue of one tile overlaps
 // the main loop of the next.  Edges: TMA zero-fills loads and clips stores outside the
 // matrices, so M, N and K only need 16-byte alignment, not tile multiples.
-#include "host_common.h"
-#include "ptx.cuh"
+//
+// The same kernel has a grouped form (GROUPED = true): A is a row-concatenated batch of groups
+// (group g owns rows [group_offsets[g], + group_rows[g]), offsets multiples of 128), B is
+// (groups, n, k) with K contiguous ("NT", what a weight matrix per group looks like), C is
+// (rows_total, n) bf16 scaled by alpha[g]; rows outside every group are never written.  It is
+// the second half of the mixed-dtype grouped GEMM: int4 weights are expanded to bf16 by
+// int4_dequant_kernel (convert to bf16, multiply by the group scale in bf16 — the order the
+// reference prescribes, ports/hopper_mixed_dtype_grouped_gemm/problems.py:75-81) and then
+// multiplied here with fp32 accumulation (problems.py:84-87).
+#include "gemm_common.cuh"
 
-#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 namespace msc {
 
 struct DenseParams {
-  int m_tiles, n_tiles;   // 256 x 256 pair tiles
+  int m_tiles, n_tiles;   // 256 x 256 pair tiles (dense form)
   int k_stages;           // ceil(K / 64)
   int band;               // m-tiles per raster band
   int is_bf16;
   int* status;
+  GemmParams g;           // grouped form: group_rows / group_offsets / alpha / out / l / n
 };
 
 template <int STAGES>
@@ -54,7 +62,7 @@ __device__ __forceinline__ void dense_tile(const DenseParams& p, int t, int& mt,
   mt = b * p.band + (u - nt * rows);
 }
 
-template <int STAGES>
+template <int STAGES, bool GROUPED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DenseSmem<STAGES>::kThreads, 1)
 gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                       const __grid_constant__ CUtensorMap tmap_b,
@@ -82,9 +90,12 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
   const int total_tiles = p.m_tiles * p.n_tiles;
-  // instruction descriptor: fp32 accumulate, A K-major, B MN-major, M = 256, N = 256
-  const uint32_t idesc = (1u << 4) | (p.is_bf16 ? ((1u << 7) | (1u << 10)) : 0u) | (1u << 16) |
-                         (uint32_t(256 >> 3) << 17) | (uint32_t(256 >> 4) << 24);
+  // instruction descriptor: fp32 accumulate, A K-major, B MN-major (dense) or K-major
+  // (grouped), M = 256, N = 256
+  const uint32_t idesc = (1u << 4) | (p.is_bf16 ? ((1u << 7) | (1u << 10)) : 0u) |
+                         (GROUPED ? 0u : (1u << 16)) | (uint32_t(256 >> 3) << 17) |
+                         (uint32_t(256 >> 4) << 24);
+  const int ntiles_g = GROUPED ? p.g.n / 256 : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -117,11 +128,20 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------ producer (both CTAs) ------------------------
     uint32_t bits = 0, s = 0;
     bool ok = true;
-    for (int t = pair; t < total_tiles && ok; t += npairs) {
-      int mt, nt;
-      dense_tile(p, t, mt, nt);
-      const int row0 = (2 * mt + (int)rank) * 128;                  // rows of A
-      const int col0 = (nt * 256 + (int)rank * 128) * 2;            // byte column of B
+    TileCursor cur;
+    cur.mshift = 8;
+    for (int t = pair; ok; t += npairs) {
+      int mt, nt, row0, col0;
+      if (GROUPED) {
+        if (!cur.seek(p.g, ntiles_g, t, mt, nt)) break;
+        row0 = cur.off + (2 * mt + (int)rank) * 128;                // rows of A
+        col0 = cur.g * p.g.n + nt * 256 + (int)rank * 128;          // rows of B (K-major)
+      } else {
+        if (t >= total_tiles) break;
+        dense_tile(p, t, mt, nt);
+        row0 = (2 * mt + (int)rank) * 128;                          // rows of A
+        col0 = (nt * 256 + (int)rank * 128) * 2;                    // byte column of B
+      }
       for (int kb = 0; kb < p.k_stages; ++kb) {
         ok = warp_wait(bar_empty + 8 * s, ((bits >> s) & 1u) ^ 1u, abort_flag, p.status, 1);
         if (!ok) break;
@@ -130,8 +150,12 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (elect_one()) {
           if (leader) mbar_arrive_expect_tx(full, 2 * kStageBytes);
           tma_load_2d_pair(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
-          tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, col0, kb * 64);
-          tma_load_2d_pair(sbase + L::kOffB + s * L::kB + 8192, &tmap_b, full, col0 + 128, kb * 64);
+          if (GROUPED) {
+            tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, col0);
+          } else {
+            tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, col0, kb * 64);
+            tma_load_2d_pair(sbase + L::kOffB + s * L::kB + 8192, &tmap_b, full, col0 + 128, kb * 64);
+          }
         }
         __syncwarp();
         s = (s + 1 == STAGES) ? 0u : s + 1;
@@ -144,8 +168,18 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int tl = 0;
       bool ok = true;
       const uint64_t adesc0 = operand_desc_sw128(sbase + L::kOffA);
-      const uint64_t bdesc0 = operand_desc_mn_sw128(sbase + L::kOffB, 8192u);
-      for (int t = pair; t < total_tiles && ok; t += npairs, ++tl) {
+      const uint64_t bdesc0 = GROUPED ? operand_desc_sw128(sbase + L::kOffB)
+                                      : operand_desc_mn_sw128(sbase + L::kOffB, 8192u);
+      constexpr int kBStep = GROUPED ? 2 : 128;
+      TileCursor cur;
+      cur.mshift = 8;
+      for (int t = pair; ok; t += npairs, ++tl) {
+        if (GROUPED) {
+          int mt, nt;
+          if (!cur.seek(p.g, ntiles_g, t, mt, nt)) break;
+        } else if (t >= total_tiles) {
+          break;
+        }
         const int buf = tl & 1;
         ok = warp_wait(bar_acc_empty + 8 * buf, ((uint32_t)(tl >> 1) & 1u) ^ 1u, abort_flag, p.status, 2);
         if (!ok) break;
@@ -157,13 +191,13 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           bits ^= 1u << s;
           tc_fence_after_sync();
           // A advances 32 bytes of K per MMA inside its swizzled rows (+2 in 16-byte units);
-          // B advances 16 K rows = 2048 bytes (+128)
+          // an MN-major B advances 16 K rows = 2048 bytes (+128), a K-major B like A
           const uint64_t adesc = adesc0 + s * (L::kA >> 4);
           const uint64_t bdesc = bdesc0 + s * (L::kB >> 4);
           if (elect_one()) {
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              tc_mma_f16_pair(acc, adesc + 2 * j, bdesc + 128 * j, idesc, (kb | j) ? 1u : 0u);
+              tc_mma_f16_pair(acc, adesc + 2 * j, bdesc + kBStep * j, idesc, (kb | j) ? 1u : 0u);
             tc_commit_pair(bar_empty + 8 * s, 3);
           }
           __syncwarp();
@@ -182,9 +216,16 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int slab = warp >> 2;
     const uint32_t lane_base = uint32_t(quad * 32) << 16;
     const uint32_t box = sbase + L::kOffC + warp * L::kCPerWarp;
-    for (int t = pair; t < total_tiles; t += npairs, ++tl) {
+    TileCursor cur;
+    cur.mshift = 8;
+    for (int t = pair;; t += npairs, ++tl) {
       int mt, nt;
-      dense_tile(p, t, mt, nt);
+      if (GROUPED) {
+        if (!cur.seek(p.g, ntiles_g, t, mt, nt)) break;
+      } else {
+        if (t >= total_tiles) break;
+        dense_tile(p, t, mt, nt);
+      }
       const int buf = tl & 1;
       bool ok = true;
       if (lane == 0)
@@ -201,8 +242,35 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster((bar_acc_empty + 8 * buf) & kLeaderMask);
 
-      const int row0 = (2 * mt + (int)rank) * 128 + quad * 32;
+      const int row_in = (2 * mt + (int)rank) * 128 + quad * 32;   // row inside the group / matrix
+      const int row0 = (GROUPED ? cur.off : 0) + row_in;
       const int colb = (nt * 256 + slab * 128) * 2;   // byte column
+      float scale = 1.0f;
+      if (GROUPED) {
+        scale = p.g.alpha ? __ldg(p.g.alpha + cur.g) : 1.0f;
+        if (row_in + 32 > cur.rows) {
+          // ragged end of a group: plain stores of the valid rows only
+          if (row_in + lane < cur.rows) {
+            __nv_bfloat16* dst = p.g.out + (size_t)(row0 + lane) * p.g.n + (colb >> 1);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(v[c][q * 8 + 2 * e]) * scale,
+                                                            __uint_as_float(v[c][q * 8 + 2 * e + 1]) * scale);
+                  w[e] = *reinterpret_cast<uint32_t*>(&pr);
+                }
+                d4[q] = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          }
+          continue;
+        }
+      }
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
         if (lane == 0) bulk_wait_group_read0();
@@ -215,8 +283,8 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float lo = __uint_as_float(v[c][q * 8 + 2 * e]);
-              const float hi = __uint_as_float(v[c][q * 8 + 2 * e + 1]);
+              const float lo = __uint_as_float(v[c][q * 8 + 2 * e]) * scale;
+              const float hi = __uint_as_float(v[c][q * 8 + 2 * e + 1]) * scale;
               if (p.is_bf16) {
                 __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
                 w[e] = *reinterpret_cast<uint32_t*>(&pr);
@@ -254,7 +322,104 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
+// Expands int4 weights to bf16: out[g, n, k] = bf16( bf16(q[g, n, k]) * scale[g, n, k / group] ),
+// q in [-8, 7] two per byte (element 2i in the low nibble).  One thread per 16 elements.
+__global__ void __launch_bounds__(256)
+int4_dequant_kernel(const uint8_t* __restrict__ q, const __nv_bfloat16* __restrict__ scales,
+                    __nv_bfloat16* __restrict__ out, long long rows, int k, int group) {
+  const int units = k >> 4;
+  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = unit / units;
+  const int u = (int)(unit - row * units);
+  if (row >= rows) return;
+  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(q + row * (k >> 1)) + u);
+  const __nv_bfloat16 sc = scales[row * (k / group) + (u * 16) / group];
+  uint32_t words[2] = {raw.x, raw.y};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t byte = (words[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+    const int lo = (int)(byte & 0xF), hi = (int)(byte >> 4);
+    const __nv_bfloat16 a = __hmul(__int2bfloat16_rn(lo >= 8 ? lo - 16 : lo), sc);
+    const __nv_bfloat16 b = __hmul(__int2bfloat16_rn(hi >= 8 ? hi - 16 : hi), sc);
+    __nv_bfloat162 pr = __halves2bfloat162(a, b);
+    o[i] = *reinterpret_cast<uint32_t*>(&pr);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + row * k + u * 16);
+  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
 }  // namespace msc
+
+extern "C" int msc_int4_dequant_bf16(const void* q, const void* scales, void* out, int groups, int n,
+                                     int k, int group_size, void* stream) {
+  using namespace msc;
+  if (!q || !scales || !out) return fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (groups <= 0 || n <= 0 || k <= 0 || group_size <= 0) return fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (k % 16 || group_size % 16 || k % group_size)
+    return fail(MSC_ERR_BAD_ARG, "k and group_size must be multiples of 16 and group_size must divide k");
+  const long long rows = (long long)groups * n;
+  const long long blocks = (rows * (k / 16) + 255) / 256;
+  if (blocks > 0x7fffffffLL) return fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
+  int4_dequant_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(q), static_cast<const __nv_bfloat16*>(scales),
+      static_cast<__nv_bfloat16*>(out), rows, k, group_size);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+extern "C" int msc_grouped_gemm_bf16_ragged(const void* a, const void* b, const float* alpha,
+                                            const int32_t* group_offsets, const int32_t* group_rows,
+                                            void* out, int l, int rows_total, int n, int k,
+                                            int max_ctas, void* stream) {
+  using namespace msc;
+  if (!a || !b || !out || !group_offsets || !group_rows) return fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (l <= 0 || rows_total <= 0 || n <= 0 || k <= 0) return fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (n % 256) return fail(MSC_ERR_BAD_ARG, "n=%d must be a multiple of 256", n);
+  if (k % 8) return fail(MSC_ERR_BAD_ARG, "k=%d must be a multiple of 8", k);
+  int* status = status_word();
+  if (!status) return fail(MSC_ERR_CUDA, "status word unavailable on this device");
+  CUtensorMap ta, tb, tc;
+  int rc = make_tmap_pitched_2d(&ta, a, (uint64_t)rows_total, (uint64_t)k * 2, (uint64_t)k * 2, 128);
+  if (rc) return rc;
+  rc = make_tmap_pitched_2d(&tb, b, (uint64_t)l * n, (uint64_t)k * 2, (uint64_t)k * 2, 128);
+  if (rc) return rc;
+  rc = make_tmap_pitched_2d(&tc, out, (uint64_t)rows_total, (uint64_t)n * 2, (uint64_t)n * 2, 32);
+  if (rc) return rc;
+  DenseParams p;
+  p.m_tiles = p.n_tiles = 0;
+  p.k_stages = (k + 63) / 64;
+  p.band = 8;
+  p.is_bf16 = 1;
+  p.status = status;
+  p.g = GemmParams{};
+  p.g.alpha = alpha;
+  p.g.group_rows = group_rows;
+  p.g.group_offsets = group_offsets;
+  p.g.out = static_cast<__nv_bfloat16*>(out);
+  p.g.l = l;
+  p.g.m_stride = 0;
+  p.g.n = n;
+  p.g.raster = 0;
+  int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
+  if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
+  const long long tiles = ((long long)(rows_total + 255) / 256 + l) * (n / 256);
+  if (pairs > tiles) pairs = (int)tiles;
+  constexpr int kStages = 6;
+  using L = DenseSmem<kStages>;
+  auto kern = gemm_dense_f16_kernel<kStages, true>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  MSC_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+    configured[dev & 63] = true;
+  }
+  kern<<<2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream)>>>(ta, tb, tc, p);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
 
 extern "C" int msc_gemm_f16(const void* a, const void* b, void* c, int m, int n, int k, int lda,
                             int ldb, int ldc, int dtype, int max_ctas, void* stream) {
@@ -281,13 +446,14 @@ extern "C" int msc_gemm_f16(const void* a, const void* b, void* c, int m, int n,
   p.band = 8;
   p.is_bf16 = dtype;
   p.status = status;
+  p.g = GemmParams{};
   int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
   if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   if (pairs > tiles) pairs = (int)tiles;
   constexpr int kStages = 6;
   using L = DenseSmem<kStages>;
-  auto kern = gemm_dense_f16_kernel<kStages>;
+  auto kern = gemm_dense_f16_kernel<kStages, false>;
   static bool configured[64] = {false};
   int dev = 0;
   MSC_CUDA_OK(cudaGetDevice(&dev));

@@ -253,3 +253,44 @@ def gemm_f16(a, b, out=None, max_ctas: int = 0):
                                         out.stride(0), 0 if a.dtype == torch.float16 else 1, max_ctas,
                                         _stream()))
     return out
+
+
+def dequant_int4(b_q, scales, group_size: int = 128, out=None):
+    """(l, n, k/2) packed int4 + (l, n, k/group_size) bf16 scales -> (l, n, k) bf16, the multiply
+    done in bf16 (ports/hopper_mixed_dtype_grouped_gemm/problems.py:75-81)."""
+    _need(b_q, "b_q", (torch.uint8, torch.int8))
+    l, n, kh = b_q.shape
+    k = kh * 2
+    _need(scales, "scales", (torch.bfloat16,), (l, n, k // group_size))
+    if out is None:
+        out = torch.empty((l, n, k), dtype=torch.bfloat16, device=b_q.device)
+    _lib.check(_lib.load().msc_int4_dequant_bf16(_ptr(b_q), _ptr(scales), _ptr(out), l, n, k, group_size,
+                                                 _stream()))
+    return out
+
+
+def ragged_grouped_gemm_bf16(a, b, group_offsets, group_rows, alpha=None, out=None, max_ctas: int = 0):
+    """out[off_g + r] = bf16(alpha_g * a[off_g + r] @ b[g].T), r < group_rows[g]; a (rows_total, k)
+    bf16, b (l, n, k) bf16, fp32 accumulation."""
+    _need(a, "a", (torch.bfloat16,))
+    rows_total, k = a.shape
+    l, n = b.shape[0], b.shape[1]
+    _need(b, "b", (torch.bfloat16,), (l, n, k))
+    _need(group_offsets, "group_offsets", (torch.int32,), (l,))
+    _need(group_rows, "group_rows", (torch.int32,), (l,))
+    if alpha is not None:
+        _need(alpha, "alpha", (torch.float32,), (l,))
+    if out is None:
+        out = torch.empty((rows_total, n), dtype=torch.bfloat16, device=a.device)
+    _lib.check(_lib.load().msc_grouped_gemm_bf16_ragged(_ptr(a), _ptr(b), _ptr(alpha), _ptr(group_offsets),
+                                                        _ptr(group_rows), _ptr(out), l, rows_total, n, k,
+                                                        max_ctas, _stream()))
+    return out
+
+
+def mixed_grouped_gemm_int4(a, b_q, scales, group_offsets, group_rows, alpha=None, group_size: int = 128,
+                            workspace=None, out=None):
+    """bf16 activations x int4 weights: expands the weights to bf16 (`workspace`, (l, n, k) bf16,
+    reusable while the weights do not change) and runs the grouped bf16 GEMM."""
+    b = dequant_int4(b_q, scales, group_size, out=workspace)
+    return ragged_grouped_gemm_bf16(a, b, group_offsets, group_rows, alpha, out=out)
