@@ -336,7 +336,11 @@ def main():
                         "reference_cutedsl_us": 13.4,
                         "note": "same operand set every launch, the reference's timing convention"},
             "roofline": {"bound": "hbm", "achieved": hbm_achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": hbm_achieved / pk["hbm_gbs"], "traffic": None,
+                         "frac": hbm_achieved / pk["hbm_gbs"],
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this
+                         # workload under ncu (profiles/gemm_pair_nvfp4_c1.md): inputs are read
+                         # once, the output is still in L2 when the launch ends
+                         "traffic": 23.63e6 if not (cfg.cta_pair == 2 or cfg.tile_n) else 23.62e6,
                          "peak_source": pk["source"],
                          "algorithmic_bytes_per_launch": ALGO_BYTES,
                          "tensor": {"achieved": per_gpu, "peak": fp4_derived, "unit": "TFLOP/s",

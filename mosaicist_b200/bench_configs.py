@@ -1,0 +1,134 @@
+"""Times the other benchmark configurations on one GPU (the headline NVFP4 grouped GEMM has
+its own bench.py at the repository root, the MoE layer bench_moe.py):
+
+  C2  dense fp16 GEMM 8192^3 (also N-sharded: each of `--gpus` ranks takes 8192/N columns)
+  C3  MXFP8 grouped GEMM, 32 groups with Zipf(1.2) row counts summing to 16384, n=4096, k=7168
+  C4  bf16 x int4 grouped GEMM, 64 groups with m ~ U[64, 512], n=2048, k=7168, group size 128
+
+    python -m mosaicist_b200.bench_configs [--reps 20]
+
+Inputs are seeded synthetic data of those shapes; every timed launch is preceded by an L2
+flush (a 256 MB memset) outside the CUDA-event window.  One JSON line per configuration.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+
+import numpy as np
+import torch
+
+
+def _time(fn, reps, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def _layout(rows):
+    offs, tot = [], 0
+    for r in rows:
+        offs.append(tot)
+        tot += (r + 127) // 128 * 128
+    return offs, tot
+
+
+def zipf_rows(groups=32, total=16384, s=1.2):
+    w = 1.0 / np.arange(1, groups + 1) ** s
+    rows = np.maximum(1, np.floor(w / w.sum() * total)).astype(int)
+    rows[0] += total - rows.sum()
+    return rows.tolist()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--gpus", type=int, default=1)
+    args = ap.parse_args()
+    from . import _lib, ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    pk = pathlib.Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
+    bf16_peak = json.loads(pk.read_text())["bf16_tflops"] if pk.exists() else 1590.0
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    out = []
+
+    # C2: dense fp16, this rank's column shard
+    n = 8192
+    from .parallel import column_range
+    cols = column_range(n, world, rank)
+    a = (torch.randn((n, n), device=dev, generator=g) / n ** 0.5).half()
+    b = (torch.randn((n, n), device=dev, generator=g) / n ** 0.5).half()
+    c = torch.empty((n, n), dtype=torch.float16, device=dev)
+    bs, cs = b[:, cols.start:cols.stop], c[:, cols.start:cols.stop]
+    ms = _time(lambda: ops.gemm_f16(a, bs, out=cs), args.reps, flush)
+    ms_lib = _time(lambda: torch.matmul(a, bs, out=cs), args.reps, flush)
+    fl = 2.0 * n * n * len(cols)
+    out.append({"config": "C2 dense fp16 8192^3", "columns_per_rank": len(cols), "ms": ms,
+                "tflops": fl / ms / 1e9, "pct_measured_bf16_peak": 100 * fl / ms / 1e9 / bf16_peak,
+                "cublas_ms": ms_lib, "cublas_tflops": fl / ms_lib / 1e9})
+    del a, b, c
+
+    # C3: MXFP8 grouped, ragged rows
+    rows = zipf_rows()
+    offs, tot = _layout(rows)
+    nn, kk = 4096, 7168
+    a_q = torch.randint(0, 256, (tot, kk), dtype=torch.uint8, device=dev, generator=g) & 0x77      # finite e4m3
+    b_q = torch.randint(0, 256, (len(rows), nn, kk), dtype=torch.uint8, device=dev, generator=g) & 0x77
+    a_sf = torch.randint(120, 130, (tot // 128, kk // 128, 32, 16), dtype=torch.uint8, device=dev, generator=g)
+    b_sf = torch.randint(120, 130, (len(rows), nn // 128, kk // 128, 32, 16), dtype=torch.uint8, device=dev, generator=g)
+    o_t = torch.tensor(offs, dtype=torch.int32, device=dev)
+    r_t = torch.tensor(rows, dtype=torch.int32, device=dev)
+    y = torch.empty((tot, nn), dtype=torch.bfloat16, device=dev)
+    ms = _time(lambda: ops.ragged_grouped_gemm_mxfp8(a_q, a_sf, b_q, b_sf, o_t, r_t, out=y), args.reps, flush)
+    fl = 2.0 * sum(rows) * nn * kk
+    out.append({"config": "C3 MXFP8 grouped 32 groups Zipf(1.2) sum 16384, n=4096 k=7168", "rows": rows,
+                "ms": ms, "tflops": fl / ms / 1e9, "pct_2x_measured_bf16_peak": 100 * fl / ms / 1e9 / (2 * bf16_peak),
+                "pct_nominal_fp8_4500": 100 * fl / ms / 1e9 / 4500})
+    del a_q, b_q, a_sf, b_sf, y
+
+    # C4: bf16 x int4 grouped
+    rng = np.random.default_rng(4)
+    rows = rng.integers(64, 513, 64).tolist()
+    offs, tot = _layout(rows)
+    nn, kk = 2048, 7168
+    a = torch.randn((tot, kk), device=dev, generator=g).bfloat16()
+    bq = torch.randint(0, 256, (64, nn, kk // 2), dtype=torch.uint8, device=dev, generator=g)
+    sc = (torch.randn((64, nn, kk // 128), device=dev, generator=g) * 0.02).abs().bfloat16()
+    ws = torch.empty((64, nn, kk), dtype=torch.bfloat16, device=dev)
+    y = torch.empty((tot, nn), dtype=torch.bfloat16, device=dev)
+    o_t = torch.tensor(offs, dtype=torch.int32, device=dev)
+    r_t = torch.tensor(rows, dtype=torch.int32, device=dev)
+    ms_all = _time(lambda: ops.mixed_grouped_gemm_int4(a, bq, sc, o_t, r_t, workspace=ws, out=y), args.reps, flush)
+    ms_gemm = _time(lambda: ops.ragged_grouped_gemm_bf16(a, ws, o_t, r_t, out=y), args.reps, flush)
+    fl = 2.0 * sum(rows) * nn * kk
+    out.append({"config": "C4 bf16 x int4 grouped 64 groups m~U[64,512], n=2048 k=7168 gs=128", "sum_m": sum(rows),
+                "ms": ms_all, "tflops": fl / ms_all / 1e9, "ms_gemm_only": ms_gemm,
+                "tflops_gemm_only": fl / ms_gemm / 1e9,
+                "pct_measured_bf16_peak": 100 * fl / ms_all / 1e9 / bf16_peak})
+    assert _lib.status_word() == 0
+    if rank == 0:
+        for line in out:
+            print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()
