@@ -207,7 +207,7 @@ def main():
     device = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("NCCL_DEBUG", "WARN")     # keep NCCL's banner off stdout
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's banner goes to stderr, not stdout
         dist.init_process_group("nccl", device_id=device)
 
     def barrier():
