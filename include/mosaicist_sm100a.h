@@ -91,6 +91,21 @@ int msc_grouped_gemm_nvfp4_ragged(const void* a_q, const void* a_sf, const void*
                                   const float* row_scale, void* out, int l, int rows_total,
                                   int n, int k, const msc_gemm_cfg* cfg, void* stream);
 
+/* First expert GEMM with the SwiGLU activation and the requantisation fused into its epilogue:
+ *   gateup = bf16(alpha[g] * A w1[g]^T);  act = silu(gate) * up in fp32;  (d_q, d_sf) = NVFP4(act)
+ * w1_q (l, n2, k/2) holds the n2/2 gate rows first, then the n2/2 up rows (nvfp4.py:81-88);
+ * d_q (rows_total, n2/4) bytes, d_sf tiled (ceil(rows_total/128), n2/128, 32, 16), quantised
+ * with out_global_scale[g].  Replaces gemm1_silu_quantize
+ * (experiments/flashinfer-megamoe-sm100a/gemm1_silu_quantize.py:94-241) and produces exactly
+ * the bytes of msc_grouped_gemm_nvfp4_ragged followed by msc_nvfp4_quantize_ragged(silu=1),
+ * without the (rows_total, n2) bf16 round trip.  CTA-pair kernel; n2 % 256 == 0, k % 64 == 0. */
+int msc_grouped_gemm_nvfp4_swiglu_ragged(const void* a_q, const void* a_sf, const void* w1_q,
+                                         const void* w1_sf, const float* alpha,
+                                         const int32_t* group_offsets, const int32_t* group_rows,
+                                         const float* out_global_scale, void* d_q, void* d_sf, int l,
+                                         int rows_total, int n2, int k, const msc_gemm_cfg* cfg,
+                                         void* stream);
+
 /* MXFP8 grouped GEMM (e4m3 values, one ue8m0 scale per 32 K-elements), ragged rows as
  * above.  The nearest reference arithmetic is the Hopper analog's block-scaled FP8 GEMM
  * (experiments/flashinfer-megamoe-sm90a/quant.py:47-75) with the scale format and block

@@ -41,6 +41,7 @@ SIGNATURES = {
     "msc_status_word_read": (_I, [ctypes.POINTER(ctypes.c_int)]),
     "msc_grouped_gemm_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),
     "msc_grouped_gemm_nvfp4_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),
+    "msc_grouped_gemm_nvfp4_swiglu_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),
     "msc_grouped_gemm_mxfp8_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),
     "msc_nvfp4_quantize": (_I, [_P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "msc_nvfp4_silu_mul_quantize": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),

@@ -511,6 +511,9 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   p.k_stages = (int)((k_bytes + 127) / 128);
   p.sf_chunks = k / chunk_elems;
   p.raster = cfg.raster ? 1 : 0;
+  p.out_q = nullptr;
+  p.out_sf = nullptr;
+  p.out_gs = nullptr;
 #ifdef MSC_DEBUG
   p.trace = g_trace;
   p.debug_flags = g_debug_flags;
@@ -522,7 +525,7 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
     pair = (n % 256 == 0) && ((m_stride > 0 ? m_stride : rows_total / l) >= 256);
   if (pair)
     return launch_pair_gemm(kind, a_q, b_q, rows_total, k_bytes, p, cfg.stages, cfg.max_ctas,
-                            static_cast<cudaStream_t>(stream_v));
+                            static_cast<cudaStream_t>(stream_v), cfg.reserved[0] == 1);
 
   const long long max_tiles = ((rows_total + 127) / 128 + l) * (long long)(n / tile_n);
   int grid = cfg.max_ctas > 0 ? cfg.max_ctas : num_sms();
@@ -570,6 +573,48 @@ int msc_grouped_gemm_nvfp4_ragged(const void* a_q, const void* a_sf, const void*
     return msc::fail(MSC_ERR_BAD_ARG, "group_offsets and group_rows are required");
   return msc::grouped_gemm(msc::KIND_NVFP4, a_q, a_sf, b_q, b_sf, alpha, group_offsets, group_rows,
                            row_scale, out, l, rows_total, 0, n, k, cfg, stream);
+}
+
+int msc_grouped_gemm_nvfp4_swiglu_ragged(const void* a_q, const void* a_sf, const void* w1_q,
+                                         const void* w1_sf, const float* alpha,
+                                         const int32_t* group_offsets, const int32_t* group_rows,
+                                         const float* out_global_scale, void* d_q, void* d_sf, int l,
+                                         int rows_total, int n2, int k, const msc_gemm_cfg* cfg,
+                                         void* stream) {
+  using namespace msc;
+  if (!a_q || !a_sf || !w1_q || !w1_sf || !group_offsets || !group_rows || !out_global_scale || !d_q || !d_sf)
+    return fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (l <= 0 || rows_total <= 0 || n2 <= 0 || k <= 0) return fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (n2 % 256) return fail(MSC_ERR_BAD_ARG, "n2=%d (gate + up rows) must be a multiple of 256", n2);
+  if (k % 64) return fail(MSC_ERR_BAD_ARG, "k=%d must be a multiple of 64", k);
+  if (reinterpret_cast<uintptr_t>(d_q) % 16 || reinterpret_cast<uintptr_t>(d_sf) % 4)
+    return fail(MSC_ERR_BAD_ARG, "d_q must be 16-byte aligned, d_sf 4-byte aligned");
+  int* status = status_word();
+  if (!status) return fail(MSC_ERR_CUDA, "status word unavailable on this device");
+  GemmParams p;
+  p.sfa = static_cast<const uint8_t*>(a_sf);
+  p.sfb = static_cast<const uint8_t*>(w1_sf);
+  p.alpha = alpha;
+  p.row_scale = nullptr;
+  p.group_rows = group_rows;
+  p.group_offsets = group_offsets;
+  p.out = nullptr;
+  p.status = status;
+  p.l = l;
+  p.m_stride = 0;
+  p.n = n2;
+  p.k_stages = (k / 2 + 127) / 128;
+  p.sf_chunks = k / 64;
+  p.raster = 0;
+  p.out_q = static_cast<uint8_t*>(d_q);
+  p.out_sf = static_cast<uint8_t*>(d_sf);
+  p.out_gs = out_global_scale;
+#ifdef MSC_DEBUG
+  p.trace = g_trace;
+  p.debug_flags = g_debug_flags;
+#endif
+  return launch_pair_gemm(KIND_NVFP4, a_q, w1_q, rows_total, k / 2, p, cfg ? cfg->stages : 0,
+                          cfg ? cfg->max_ctas : 0, static_cast<cudaStream_t>(stream), false);
 }
 
 int msc_grouped_gemm_mxfp8_ragged(const void* a_q, const void* a_sf, const void* b_q,

@@ -16,10 +16,11 @@
 //
 // Same arithmetic, operand layout and masking rules as gemm_blockscaled.cu.
 #include "gemm_common.cuh"
+#include "quantize_common.cuh"
 
 namespace msc {
 
-template <int STAGES>
+template <int STAGES, bool SFW = false>
 struct PairSmem {
   static constexpr int kHeader = 1024;
   static constexpr int kA = 128 * 128;
@@ -32,7 +33,8 @@ struct PairSmem {
   static constexpr int kOffSfb = kOffSfa + STAGES * kSfa;
   static constexpr int kOffC = kOffSfb + STAGES * kSfb;
   static constexpr int kEpiWarps = 8;
-  static constexpr int kThreads = (kEpiWarps + 2) * 32;
+  static constexpr int kSfWarps = SFW ? 4 : 0;   // warps that write scale factors into TMEM
+  static constexpr int kThreads = (kEpiWarps + 2 + kSfWarps) * 32;
   // two 4 KB store boxes per epilogue warp when the ring leaves room (up to 4 stages), so the
   // second 64-column half never waits for the first half's store to drain
   static constexpr int kCPerWarp = (STAGES <= 4) ? 8192 : 4096;
@@ -42,17 +44,18 @@ struct PairSmem {
   static_assert(kAlloc <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
-template <int KIND, int STAGES>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<STAGES>::kThreads, 1)
+template <int KIND, int STAGES, bool SFW, bool SWIGLU>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<STAGES, SFW>::kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa,
                  const __grid_constant__ CUtensorMap tmap_sfb,
                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
-  using L = PairSmem<STAGES>;
+  using L = PairSmem<STAGES, SFW>;
   constexpr int kTileN = 256;
   constexpr int kMmaWarp = L::kEpiWarps;
   constexpr int kProducerWarp = L::kEpiWarps + 1;
+  constexpr int kFirstSfWarp = L::kEpiWarps + 2;
   constexpr int kSfaCols = 16, kSfbCols = 32, kSlotCols = kSfaCols + kSfbCols;
   constexpr int kSfCol0 = kTileN;
   static_assert(kSfCol0 + STAGES * kSlotCols <= 512, "scale slots do not fit in TMEM");
@@ -73,6 +76,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t bar_empty = sbase + 8 * STAGES;      // STAGES x 8
   const uint32_t bar_acc_full = sbase + 16 * STAGES;  // 8
   const uint32_t bar_acc_empty = bar_acc_full + 8;    // 8 (used in the leader)
+  const uint32_t bar_sf_full = bar_acc_empty + 8;     // STAGES x 8: this CTA's scale boxes landed
+  const uint32_t bar_sf_ready = bar_sf_full + 8 * STAGES;  // STAGES x 8 (leader): scales in TMEM
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + 512);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(sgen + 516);
 
@@ -91,6 +96,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_acc_empty, 2 * L::kEpiWarps);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_sf_full + 8 * s, 1);
+      mbar_init(bar_sf_ready + 8 * s, 8);
+    }
     *abort_flag = 0u;
     fence_barrier_init();
   }
@@ -130,9 +139,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int mt, nt;
       if (!cur.seek(p, ntiles, t, mt, nt)) break;
       const int row0 = cur.off + (2 * mt + (int)rank) * 128;
-      const int brow0 = cur.g * p.n + nt * kTileN + (int)rank * 128;
+      // plain: the tile's 256 B rows are consecutive, this CTA takes its half.  SwiGLU: the
+      // tile pairs 128 gate rows (first half of B) with the 128 up rows of the same output
+      // columns (second half); the even CTA feeds the gate rows, the odd CTA the up rows, so
+      // accumulator columns 0-127 are gate and 128-255 are up.
+      const int brow0 = SWIGLU ? cur.g * p.n + (int)rank * (p.n >> 1) + nt * 128
+                               : cur.g * p.n + nt * kTileN + (int)rank * 128;
       const int sfa_row = (row0 >> 7) * p.sf_chunks * 4;
-      const int sfb_row = (cur.g * (p.n >> 7) + nt * 2) * p.sf_chunks * 4;
+      const int sfb_row = SWIGLU ? (cur.g * (p.n >> 7) + nt) * p.sf_chunks * 4
+                                 : (cur.g * (p.n >> 7) + nt * 2) * p.sf_chunks * 4;
+      const int sfb_row1 = sfb_row + (SWIGLU ? (p.n >> 8) : 1) * p.sf_chunks * 4;
       uint32_t s = 0;
       MSC_STAMP(0, tl, 0);
       for (int kb = 0; kb < p.k_stages; ++kb) {
@@ -142,13 +158,25 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t full = bar_full + 8 * s;
         const int c4 = kb * kChunksPerStage * 4;
         if (elect_one()) {
-          if (leader) mbar_arrive_expect_tx(full, 2 * kStageBytes);
-          tma_load_2d_pair(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
-          tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, brow0);
-          tma_load_2d_pair(sbase + L::kOffSfa + s * L::kSfa, &tmap_sfa, full, 0, sfa_row + c4);
-          tma_load_2d_pair(sbase + L::kOffSfb + s * L::kSfb, &tmap_sfb, full, 0, sfb_row + c4);
-          tma_load_2d_pair(sbase + L::kOffSfb + s * L::kSfb + 2048, &tmap_sfb, full, 0,
-                           sfb_row + p.sf_chunks * 4 + c4);
+          if (SFW) {
+            // scale boxes report to this CTA's own barrier: its scale warps consume them
+            const uint32_t sff = bar_sf_full + 8 * s;
+            if (leader) mbar_arrive_expect_tx(full, 2 * (L::kA + L::kB));
+            mbar_arrive_expect_tx(sff, 3 * kSfBoxBytes);
+            tma_load_2d_pair(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
+            tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, brow0);
+            tma_load_2d(sbase + L::kOffSfa + s * L::kSfa, &tmap_sfa, sff, 0, sfa_row + c4);
+            tma_load_2d(sbase + L::kOffSfb + s * L::kSfb, &tmap_sfb, sff, 0, sfb_row + c4);
+            tma_load_2d(sbase + L::kOffSfb + s * L::kSfb + 2048, &tmap_sfb, sff, 0, sfb_row1 + c4);
+          } else {
+            if (leader) mbar_arrive_expect_tx(full, 2 * kStageBytes);
+            tma_load_2d_pair(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
+            tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, brow0);
+            tma_load_2d_pair(sbase + L::kOffSfa + s * L::kSfa, &tmap_sfa, full, 0, sfa_row + c4);
+            tma_load_2d_pair(sbase + L::kOffSfb + s * L::kSfb, &tmap_sfb, full, 0, sfb_row + c4);
+            tma_load_2d_pair(sbase + L::kOffSfb + s * L::kSfb + 2048, &tmap_sfb, full, 0,
+                             sfb_row1 + c4);
+          }
         }
         __syncwarp();
         s = (s + 1 == STAGES) ? 0u : s + 1;
@@ -182,6 +210,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (kb >= p.k_stages) break;
             ok = warp_wait(bar_full + 8 * s, (bits >> s) & 1u, abort_flag, p.status, 3);
             if (!ok) break;
+            if (SFW) {
+              ok = warp_wait(bar_sf_ready + 8 * s, (bits >> s) & 1u, abort_flag, p.status, 5);
+              if (!ok) break;
+            }
             bits ^= 1u << s;
             tc_fence_after_sync();
             const int nch = min(kChunksPerStage, p.sf_chunks - kb * kChunksPerStage);
@@ -196,7 +228,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint64_t bdesc = bdesc0 + s * (L::kB >> 4);
             if (elect_one()) {
 #pragma unroll
-              for (int c = 0; c < kChunksPerStage; ++c) {
+              for (int c = 0; c < kChunksPerStage && !SFW; ++c) {
                 if (c < nch) {
                   tc_cp_32x128b_warpx4_pair(sfa_t + 4 * c, sfa_d + 32 * c);
                   tc_cp_32x128b_warpx4_pair(sfb_t + 8 * c, sfb_d + 32 * c);
@@ -227,6 +259,60 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         MSC_STAMP(1, tl, 1);
       }
     }
+  } else if (SFW && warp >= kFirstSfWarp) {
+    // ------------------------------ scale writers (both CTAs) -------------------
+    // Four warps, one per TMEM lane quadrant, move each stage's scale factors from shared
+    // memory into TMEM through registers (tcgen05.st) instead of tcgen05.cp: the copies then
+    // no longer take turns with the MMAs in the tensor pipe.  Lane b reads the 16 bytes of
+    // row b of every 512-byte chunk (scales of rows b, 32+b, 64+b, 96+b for 64 K-elements) and
+    // writes them to its own lane in the four columns of that chunk; every quadrant holds the
+    // same copy, which is the layout the MMA expects.
+    TileCursor cur;
+    cur.mshift = 8;
+    uint32_t bits = 0;
+    bool ok = true;
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    constexpr int kA4 = 4 * kChunksPerStage;        // columns of A scales per stage
+    constexpr int kB4 = 8 * kChunksPerStage;        // columns of B scales per stage
+    for (int t = pair; ok; t += npairs) {
+      int mt, nt;
+      if (!cur.seek(p, ntiles, t, mt, nt)) break;
+      uint32_t s = 0;
+      for (int kb = 0; kb < p.k_stages; ++kb) {
+        ok = warp_wait(bar_sf_full + 8 * s, (bits >> s) & 1u, abort_flag, p.status, 6);
+        if (!ok) break;
+        bits ^= 1u << s;
+        const uint32_t sa = sbase + L::kOffSfa + s * L::kSfa + lane * 16;
+        const uint32_t sb = sbase + L::kOffSfb + s * L::kSfb + lane * 16;
+        uint32_t ra[kA4], rb[kB4];
+#pragma unroll
+        for (int c = 0; c < kChunksPerStage; ++c) {
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(ra[4 * c]), "=r"(ra[4 * c + 1]), "=r"(ra[4 * c + 2]), "=r"(ra[4 * c + 3])
+                       : "r"(sa + c * 512) : "memory");
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub)
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(rb[8 * c + 4 * sub]), "=r"(rb[8 * c + 4 * sub + 1]),
+                           "=r"(rb[8 * c + 4 * sub + 2]), "=r"(rb[8 * c + 4 * sub + 3])
+                         : "r"(sb + sub * 2048 + c * 512) : "memory");
+        }
+        const uint32_t sfa_t = tmem_base + lane_base + kSfCol0 + s * kSlotCols;
+        const uint32_t sfb_t = sfa_t + kSfaCols;
+        if (KIND == KIND_NVFP4) {
+          tmem_st_32x32b_x16(sfa_t, ra);
+          tmem_st_32x32b_x32(sfb_t, rb);
+        } else {
+          tmem_st_32x32b_x4(sfa_t, ra);
+          tmem_st_32x32b_x8(sfb_t, rb);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster((bar_sf_ready + 8 * s) & kLeaderMask);
+        s = (s + 1 == STAGES) ? 0u : s + 1;
+      }
+    }
   } else {
     // ------------------------------ epilogue (both CTAs) ------------------------
     // As in the single-CTA kernel: warp w drains lane quadrant w % 4, 128-column slab w / 4.
@@ -255,15 +341,61 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (p.row_scale && valid) scale *= __ldg(p.row_scale + out_row);
 
       uint32_t v[4][32];
+      if (SWIGLU) {
+        // this warp's 64 output columns: gate from accumulator columns [64 slab, +64), up from
+        // [128 + 64 slab, +64)
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-        tmem_ld_32x32b_x32(tmem_base + lane_base + slab * 128 + c * 32, v[c]);
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld_32x32b_x32(tmem_base + lane_base + slab * 64 + c * 32, v[c]);
+          tmem_ld_32x32b_x32(tmem_base + lane_base + 128 + slab * 64 + c * 32, v[2 + c]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          tmem_ld_32x32b_x32(tmem_base + lane_base + slab * 128 + c * 32, v[c]);
+      }
       tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(bar_acc_empty & kLeaderMask);
       if (warp == 0) MSC_STAMP(2, tl, 1);
       if (MSC_FLAG(1)) continue;
+
+      if (SWIGLU) {
+        // gate and up are rounded to bf16 exactly as the unfused path stores them
+        // (gemm1_silu_quantize.py:195-197), the activation stays fp32 (nvfp4.py:81-88), then the
+        // thread quantises its four 16-column blocks: 32 bytes of e2m1 and one scale word,
+        // which is one unit of the tiled scale layout the second GEMM reads.
+        if (valid) {
+          const float gs = __ldg(p.out_gs + cur.g);
+          const int width = p.n >> 1;                       // columns of the activation
+          const int col = nt * 128 + slab * 64;             // first output column of this thread
+          uint32_t q8[8], sfw = 0;
+#pragma unroll
+          for (int blk = 0; blk < 4; ++blk) {
+            float act[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int c = blk >> 1, e = (blk & 1) * 16 + i;
+              const float gt = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[c][e]) * scale));
+              const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[2 + c][e]) * scale));
+              const float sg = __frcp_rn(__fadd_rn(1.0f, expf(-gt)));
+              act[i] = __fmul_rn(__fmul_rn(sg, gt), up);
+            }
+            uint2 q2;
+            uint32_t sfb;
+            quantize_16(act, gs, q2, sfb);
+            q8[2 * blk] = q2.x;
+            q8[2 * blk + 1] = q2.y;
+            sfw |= sfb << (8 * blk);
+          }
+          uint4* qdst = reinterpret_cast<uint4*>(p.out_q + out_row * (width >> 1) + (col >> 1));
+          qdst[0] = make_uint4(q8[0], q8[1], q8[2], q8[3]);
+          qdst[1] = make_uint4(q8[4], q8[5], q8[6], q8[7]);
+          *reinterpret_cast<uint32_t*>(p.out_sf + tiled_sf_word((int)out_row, col >> 6, width >> 6)) = sfw;
+        }
+        continue;
+      }
 
       const int col0 = nt * kTileN + slab * 128;
       if (whole_warp) {
@@ -345,10 +477,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-template <int KIND, int STAGES>
+template <int KIND, int STAGES, bool SFW, bool SWIGLU = false>
 static int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStream_t stream) {
-  using L = PairSmem<STAGES>;
-  auto kern = gemm_pair_kernel<KIND, STAGES>;
+  using L = PairSmem<STAGES, SFW>;
+  auto kern = gemm_pair_kernel<KIND, STAGES, SFW, SWIGLU>;
   static bool configured[64] = {false};
   int dev = 0;
   MSC_CUDA_OK(cudaGetDevice(&dev));
@@ -361,9 +493,24 @@ static int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, c
   return MSC_OK;
 }
 
+template <int KIND, int STAGES>
+static int launch_pair_v(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStream_t stream,
+                         bool sf_by_warps) {
+  if (p.out_q) {
+    if (KIND != KIND_NVFP4 || STAGES != 4)
+      return fail(MSC_ERR_UNSUPPORTED, "the fused SwiGLU epilogue is built for NVFP4 with 4 stages");
+    return launch_pair<KIND_NVFP4, 4, false, true>(maps, p, grid, stream);
+  }
+  if (sf_by_warps) {
+    if (STAGES != 4) return fail(MSC_ERR_UNSUPPORTED, "scale-writer warps are built for 4 stages");
+    return launch_pair<KIND, 4, true>(maps, p, grid, stream);
+  }
+  return launch_pair<KIND, STAGES, false>(maps, p, grid, stream);
+}
+
 int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_total,
                      long long k_bytes, const GemmParams& p, int stages, int max_ctas,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, bool sf_by_warps) {
   if (p.n % 256) return fail(MSC_ERR_BAD_ARG, "the CTA-pair kernel needs n %% 256 == 0, got n=%d", p.n);
   const int chunks_per_stage = (kind == KIND_NVFP4) ? 4 : 1;
   CUtensorMap maps[5];
@@ -377,8 +524,13 @@ int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_
   rc = make_tmap_sf_2d(&maps[3], p.sfb, (uint64_t)p.l * (p.n / 128) * p.sf_chunks * 4,
                        chunks_per_stage * 4);
   if (rc) return rc;
-  rc = make_tmap_bf16_2d(&maps[4], p.out, (uint64_t)rows_total, (uint64_t)p.n, 32);
-  if (rc) return rc;
+  if (p.out_q) {
+    maps[4] = maps[0];  // the fused epilogue stores with plain writes: no store map needed
+    if (stages <= 0) stages = 4;
+  } else {
+    rc = make_tmap_bf16_2d(&maps[4], p.out, (uint64_t)rows_total, (uint64_t)p.n, 32);
+    if (rc) return rc;
+  }
 
   const long long max_tiles = ((rows_total + 255) / 256 + p.l) * (long long)(p.n / 256);
   int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
@@ -390,17 +542,17 @@ int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_
   if (stages < 2) stages = 2;
   if (kind == KIND_NVFP4) {
     switch (stages) {
-      case 2: return launch_pair<KIND_NVFP4, 2>(maps, p, grid, stream);
-      case 3: return launch_pair<KIND_NVFP4, 3>(maps, p, grid, stream);
-      case 4: return launch_pair<KIND_NVFP4, 4>(maps, p, grid, stream);
-      default: return launch_pair<KIND_NVFP4, 5>(maps, p, grid, stream);
+      case 2: return launch_pair_v<KIND_NVFP4, 2>(maps, p, grid, stream, sf_by_warps);
+      case 3: return launch_pair_v<KIND_NVFP4, 3>(maps, p, grid, stream, sf_by_warps);
+      case 4: return launch_pair_v<KIND_NVFP4, 4>(maps, p, grid, stream, sf_by_warps);
+      default: return launch_pair_v<KIND_NVFP4, 5>(maps, p, grid, stream, sf_by_warps);
     }
   }
   switch (stages) {
-    case 2: return launch_pair<KIND_MXFP8, 2>(maps, p, grid, stream);
-    case 3: return launch_pair<KIND_MXFP8, 3>(maps, p, grid, stream);
-    case 4: return launch_pair<KIND_MXFP8, 4>(maps, p, grid, stream);
-    default: return launch_pair<KIND_MXFP8, 5>(maps, p, grid, stream);
+    case 2: return launch_pair_v<KIND_MXFP8, 2>(maps, p, grid, stream, sf_by_warps);
+    case 3: return launch_pair_v<KIND_MXFP8, 3>(maps, p, grid, stream, sf_by_warps);
+    case 4: return launch_pair_v<KIND_MXFP8, 4>(maps, p, grid, stream, sf_by_warps);
+    default: return launch_pair_v<KIND_MXFP8, 5>(maps, p, grid, stream, sf_by_warps);
   }
 }
 

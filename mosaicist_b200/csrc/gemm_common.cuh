@@ -24,6 +24,10 @@ struct GemmParams {
   int k_stages;              // ceil(k_bytes / 128)
   int sf_chunks;             // scale chunks along K per 128-row tile
   int raster;
+  // fused SwiGLU + requantise epilogue (B holds gate rows then up rows, n = 2 x width):
+  uint8_t* out_q;            // (rows_total, n/4) packed e2m1 of silu(gate) * up
+  uint8_t* out_sf;           // its e4m3 scales, tiled (rows_total/128, n/128, 32, 16)
+  const float* out_gs;       // [l] global scale of the activation
 #ifdef MSC_DEBUG
   unsigned long long* trace;  // [cta][8 tiles][3 roles][2] clock64 stamps, then [cta][2] at the end
   int debug_flags;            // 1: skip global stores, 2: skip scale loads/copies, 4: skip MMAs
@@ -89,6 +93,7 @@ struct TileCursor {
 
 // Launcher of the CTA-pair kernel (gemm_blockscaled_pair.cu).
 int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_total, long long k_bytes,
-                     const GemmParams& p, int stages, int max_ctas, cudaStream_t stream);
+                     const GemmParams& p, int stages, int max_ctas, cudaStream_t stream,
+                     bool sf_by_warps);
 
 }  // namespace msc

@@ -42,10 +42,13 @@ class MegaMoE:
 
     def __init__(self, w1_q, w1_sf, w1_gs, w1_alpha, w2_q, w2_sf, w2_gs, w2_alpha, input_gs, a2_gs,
                  topk: int, max_tokens: int, expert_first: int = 0,
-                 config: ops.GemmConfig = ops.GemmConfig()):
+                 config: ops.GemmConfig = ops.GemmConfig(), fuse_gemm1: bool = True):
         self.E, n2, hh = w1_q.shape
         self.h, self.n, self.topk = hh * 2, n2 // 2, topk
         self.expert_first, self.config = expert_first, config
+        # GEMM1 + SiLU*up + requantise as one kernel (needs 2n % 256 == 0); bit-identical to the
+        # two-kernel path, which stays available for comparison
+        self.fuse_gemm1 = fuse_gemm1 and (n2 % 256 == 0)
         self.w1_q, self.w1_sf, self.w2_q, self.w2_sf = w1_q, w1_sf, w2_q, w2_sf
         self.input_gs, self.a2_gs = input_gs.contiguous(), a2_gs.contiguous()
         self.alpha1 = (w1_alpha / (input_gs * w1_gs)).float().contiguous()
@@ -101,10 +104,15 @@ class MegaMoE:
             self.group_offsets.data_ptr(), self.input_gs.data_ptr(), T, self.h, K,
             self.expert_first, E, self.a_q.data_ptr(), self.a_sf.data_ptr(),
             self.row_weight.data_ptr(), self.row_token.data_ptr(), st))
-        ops.ragged_grouped_gemm_nvfp4(self.a_q, self.a_sf, self.w1_q, self.w1_sf, self.group_offsets,
-                                      self.group_rows, self.alpha1, None, self.config, out=self.gateup)
-        ops.quantize_nvfp4_ragged(self.gateup, self.a2_gs, self.group_offsets, self.group_rows,
-                                  silu=True, out=(self.d_q, self.d_sf))
+        if self.fuse_gemm1:
+            ops.ragged_gemm1_swiglu_quantize(self.a_q, self.a_sf, self.w1_q, self.w1_sf,
+                                             self.group_offsets, self.group_rows, self.alpha1,
+                                             self.a2_gs, out=(self.d_q, self.d_sf))
+        else:
+            ops.ragged_grouped_gemm_nvfp4(self.a_q, self.a_sf, self.w1_q, self.w1_sf, self.group_offsets,
+                                          self.group_rows, self.alpha1, None, self.config, out=self.gateup)
+            ops.quantize_nvfp4_ragged(self.gateup, self.a2_gs, self.group_offsets, self.group_rows,
+                                      silu=True, out=(self.d_q, self.d_sf))
         ops.ragged_grouped_gemm_nvfp4(self.d_q, self.d_sf, self.w2_q, self.w2_sf, self.group_offsets,
                                       self.group_rows, self.alpha2, self.row_weight, self.config,
                                       out=self.y)

@@ -23,10 +23,13 @@ class GemmConfig:
     raster: int = 0
     max_ctas: int = 0
     cta_pair: int = 0
+    sf_warps: int = 0
 
     def c(self, epilogue: int = _lib.EPI_PLAIN) -> _lib.GemmCfg:
-        return _lib.GemmCfg(self.tile_n, self.stages, self.raster, self.max_ctas, epilogue,
-                            self.cta_pair)
+        cfg = _lib.GemmCfg(self.tile_n, self.stages, self.raster, self.max_ctas, epilogue,
+                           self.cta_pair)
+        cfg.reserved[0] = self.sf_warps
+        return cfg
 
 
 def _ptr(t):
@@ -294,3 +297,34 @@ def mixed_grouped_gemm_int4(a, b_q, scales, group_offsets, group_rows, alpha=Non
     reusable while the weights do not change) and runs the grouped bf16 GEMM."""
     b = dequant_int4(b_q, scales, group_size, out=workspace)
     return ragged_grouped_gemm_bf16(a, b, group_offsets, group_rows, alpha, out=out)
+
+
+def ragged_gemm1_swiglu_quantize(a_q, a_sf, w1_q, w1_sf, group_offsets, group_rows, alpha, out_global_scale,
+                                 config: GemmConfig = GemmConfig(), out=None):
+    """GEMM1 + SiLU(gate) * up + NVFP4 requantisation in one kernel (the reference's
+    gemm1_silu_quantize, gemm1_silu_quantize.py:94): returns (d_q (rows_total, n/2),
+    d_sf tiled (rows_total/128, n/64, 32, 16)) with n = w1 rows / 2, bit-identical to the GEMM
+    followed by the stand-alone SiLU quantiser."""
+    _need(a_q, "a_q", _BYTES)
+    rows_total, kh = a_q.shape
+    k = kh * 2
+    l, n2 = w1_q.shape[0], w1_q.shape[1]
+    n = n2 // 2
+    _need(w1_q, "w1_q", _BYTES, (l, n2, kh))
+    _need(a_sf, "a_sf", _BYTES, ((rows_total + 127) // 128, k // 64, 32, 16))
+    _need(w1_sf, "w1_sf", _BYTES, (l, n2 // 128, k // 64, 32, 16))
+    _need(group_offsets, "group_offsets", (torch.int32,), (l,))
+    _need(group_rows, "group_rows", (torch.int32,), (l,))
+    _need(alpha, "alpha", (torch.float32,), (l,))
+    _need(out_global_scale, "out_global_scale", (torch.float32,), (l,))
+    if out is None:
+        d_q = torch.empty((rows_total, n // 2), dtype=torch.uint8, device=a_q.device)
+        d_sf = torch.zeros(((rows_total + 127) // 128, n // 64, 32, 16), dtype=torch.uint8, device=a_q.device)
+    else:
+        d_q, d_sf = out
+        _need(d_q, "d_q", (torch.uint8,), (rows_total, n // 2))
+        _need(d_sf, "d_sf", (torch.uint8,), ((rows_total + 127) // 128, n // 64, 32, 16))
+    _lib.check(_lib.load().msc_grouped_gemm_nvfp4_swiglu_ragged(
+        _ptr(a_q), _ptr(a_sf), _ptr(w1_q), _ptr(w1_sf), _ptr(alpha), _ptr(group_offsets), _ptr(group_rows),
+        _ptr(out_global_scale), _ptr(d_q), _ptr(d_sf), l, rows_total, n2, k, config.c(), _stream()))
+    return d_q, d_sf

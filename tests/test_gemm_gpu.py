@@ -60,6 +60,8 @@ EXACT_CASES = [
     (2, 512, 512, 576, {"cta_pair": 1}),
     (3, 384, 256, 1024, {"cta_pair": 1, "stages": 2}),
     (5, 512, 768, 1280, {"cta_pair": 1, "max_ctas": 6}),
+    # scale factors written into TMEM by dedicated warps (tcgen05.st) instead of tcgen05.cp
+    (2, 512, 512, 576, {"cta_pair": 1, "sf_warps": 1}),
 ]
 
 

@@ -211,3 +211,48 @@ def test_megamoe_layer(T_, E, k, h, n, first, local):
     assert np.array_equal(layer.ids.cpu().numpy(), ids)
     # with 8 of 32 experts local most tokens get no contribution: expect about 1 - (3/4)^2 non-zero
     _close(got, want, nonzero_fraction=0.5 if local == E else 0.25)
+
+
+@pytest.mark.parametrize("rows_list,n,k", [([256], 128, 256), ([300, 0, 77, 512, 129], 256, 640)])
+def test_fused_gemm1_swiglu_quantize_equals_two_kernel_path(rows_list, n, k):
+    """The fused epilogue must produce the very bytes of GEMM1 -> bf16 -> SiLU*up -> quantise."""
+    from mosaicist_b200 import _lib, ops
+    from mosaicist_b200.formats import from_mma_scale_layout
+
+    l = len(rows_list)
+    offs, tot = [], 0
+    for r in rows_list:
+        offs.append(tot)
+        tot += (r + 127) // 128 * 128
+    rng = np.random.default_rng([l, n, k])
+    x = rng.standard_normal((1, tot, k)).astype(np.float32)
+    a_q, a_sf = O.quantize_nvfp4(x, np.array([300.0], np.float32))
+    w1 = (rng.standard_normal((l, 2 * n, k)) * 0.05).astype(np.float32)
+    w1_gs = O.global_scale_for(w1)
+    w1_q, w1_sf = O.quantize_nvfp4(w1, w1_gs)
+    alpha = (rng.uniform(0.5, 1.5, l) / (300.0 * w1_gs)).astype(np.float32)
+    a2_gs = rng.uniform(300, 900, l).astype(np.float32)
+    dev = dict(a_q=T(O.pack_e2m1(a_q[0])), a_sf=T(O.e4m3_bytes(O.to_mma_scale_layout(a_sf[0]))),
+               w1_q=T(O.pack_e2m1(w1_q)), w1_sf=T(O.e4m3_bytes(O.retile(w1_sf))))
+    o_t, r_t = T(np.array(offs, np.int32)), T(np.array(rows_list, np.int32))
+    gateup = ops.ragged_grouped_gemm_nvfp4(dev["a_q"], dev["a_sf"], dev["w1_q"], dev["w1_sf"], o_t, r_t, T(alpha))
+    want_q, want_sf = ops.quantize_nvfp4_ragged(gateup, T(a2_gs), o_t, r_t, silu=True)
+    got_q, got_sf = ops.ragged_gemm1_swiglu_quantize(dev["a_q"], dev["a_sf"], dev["w1_q"], dev["w1_sf"], o_t, r_t,
+                                                     T(alpha), T(a2_gs))
+    assert _lib.status_word() == 0
+    wq, gq = want_q.cpu().numpy(), got_q.cpu().numpy()
+    wsf = from_mma_scale_layout(want_sf.cpu().numpy(), tot)
+    gsf = from_mma_scale_layout(got_sf.cpu().numpy(), tot)
+    seen = 0
+    for o, r in zip(offs, rows_list):
+        assert np.array_equal(gq[o:o + r], wq[o:o + r]) and np.array_equal(gsf[o:o + r], wsf[o:o + r])
+        seen += int(np.count_nonzero(wq[o:o + r]))
+    assert seen > sum(rows_list) * n // 8
+    # and the oracle agrees on the dequantised activation to within one e2m1 step per block
+    g0 = next(i for i, r in enumerate(rows_list) if r)
+    gu = O.masked_grouped_gemm_reference(a_q[:, offs[g0]:offs[g0] + rows_list[g0]], a_sf[:, offs[g0]:offs[g0] + rows_list[g0]],
+                                         np.ones(1, np.float32), w1_q[g0:g0 + 1], w1_sf[g0:g0 + 1], np.ones(1, np.float32),
+                                         alpha[g0:g0 + 1], [rows_list[g0]])
+    oq, osf = O.quantize_nvfp4(O.silu_mul(gu), a2_gs[g0:g0 + 1])
+    sl = slice(offs[g0], offs[g0] + rows_list[g0])
+    assert np.mean(gq[sl] == O.pack_e2m1(oq)[0]) > 0.99
