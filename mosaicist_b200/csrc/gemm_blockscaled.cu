@@ -119,6 +119,10 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+  // set-up done; wait for the previous kernel in the stream before touching global memory
+  // (a no-op unless launched with programmatic stream serialization) and let the next one in
+  grid_dependency_wait();
+  grid_launch_dependents();
 #ifdef MSC_DEBUG
   if (p.trace && threadIdx.x == 0) {
     p.trace[(size_t)gridDim.x * 48 + blockIdx.x * 2] = clock64();
@@ -431,8 +435,9 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
     MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
     configured[dev & 63] = true;
   }
-  kern<<<grid, L::kThreads, L::kAlloc, stream>>>(ta, tb, tc, p);
-  MSC_CUDA_OK(cudaGetLastError());
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t lc = pdl_launch_config(grid, L::kThreads, L::kAlloc, stream, attr);
+  MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p));
   return MSC_OK;
 }
 

@@ -119,6 +119,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   cluster_sync();  // both CTAs' barriers are initialised before either touches the other's
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+  // set-up is done: from here on global memory is touched, so wait for the previous kernel in
+  // the stream (no-op unless launched with programmatic stream serialization), and let the
+  // next one begin its own set-up as SMs free up
+  grid_dependency_wait();
+  grid_launch_dependents();
 #ifdef MSC_DEBUG
   if (p.trace && threadIdx.x == 0) {
     p.trace[(size_t)gridDim.x * 48 + blockIdx.x * 2] = clock64();
@@ -488,8 +493,11 @@ static int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, c
     MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
     configured[dev & 63] = true;
   }
-  kern<<<grid, L::kThreads, L::kAlloc, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
-  MSC_CUDA_OK(cudaGetLastError());
+  // programmatic stream serialization: this kernel's set-up may overlap the tail of the kernel
+  // before it in the stream (it waits for that kernel before touching global memory)
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t lc = pdl_launch_config(grid, L::kThreads, L::kAlloc, stream, attr);
+  MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, maps[0], maps[1], maps[2], maps[3], maps[4], p));
   return MSC_OK;
 }
 

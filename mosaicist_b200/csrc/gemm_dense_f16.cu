@@ -123,6 +123,8 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   cluster_sync();
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+  grid_dependency_wait();    // set-up may overlap the previous kernel; its data is read after this
+  grid_launch_dependents();
 
   if (warp == kProducerWarp) {
     // ------------------------------ producer (both CTAs) ------------------------
@@ -416,8 +418,10 @@ extern "C" int msc_grouped_gemm_bf16_ragged(const void* a, const void* b, const 
     MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
     configured[dev & 63] = true;
   }
-  kern<<<2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream)>>>(ta, tb, tc, p);
-  MSC_CUDA_OK(cudaGetLastError());
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t lc =
+      pdl_launch_config(2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream), attr);
+  MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p));
   return MSC_OK;
 }
 
@@ -461,7 +465,9 @@ extern "C" int msc_gemm_f16(const void* a, const void* b, void* c, int m, int n,
     MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
     configured[dev & 63] = true;
   }
-  kern<<<2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream)>>>(ta, tb, tc, p);
-  MSC_CUDA_OK(cudaGetLastError());
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t lc =
+      pdl_launch_config(2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream), attr);
+  MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p));
   return MSC_OK;
 }

@@ -47,6 +47,23 @@ int make_tmap_pitched_2d(CUtensorMap* map, const void* base, uint64_t rows, uint
 
 int num_sms();
 
+// Launch configuration with programmatic stream serialization: the kernel's set-up may overlap
+// the tail of its predecessor in the stream; the kernel calls grid_dependency_wait() before it
+// touches global memory.  `attr` must outlive the launch call.
+inline cudaLaunchConfig_t pdl_launch_config(int grid, int threads, int smem, cudaStream_t stream,
+                                            cudaLaunchAttribute* attr) {
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid);
+  lc.blockDim = dim3(threads);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = stream;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  return lc;
+}
+
 #define MSC_CUDA_OK(expr)                                                              \
   do {                                                                                 \
     cudaError_t e__ = (expr);                                                          \

@@ -21,6 +21,19 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while its
+// predecessor in the stream is still running: its CTAs take SMs as they free up and do their
+// set-up.  grid_dependency_wait() then blocks until the predecessor has finished and its
+// writes are visible; nothing that the predecessor may have produced is read before it.
+// Without the attribute both calls do nothing.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- mbarrier ----------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
