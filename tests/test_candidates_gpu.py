@@ -33,3 +33,26 @@ def test_capture_module(name, knobs, tmp_path, monkeypatch):
     assert ok, worst
     assert gate.gate_bf16(got, ref).passed
     assert np.count_nonzero(ref) > ref.size // 2
+
+
+def test_flashinfer_reference_kernel_on_identical_inputs():
+    """The reference project's reference kernel (FlashInfer CuTeDSL), run on our operand bytes,
+    must agree with our kernel; skipped where FlashInfer / CuTeDSL cannot run."""
+    import torch
+
+    try:
+        from mosaicist_b200.candidates import ref_flashinfer_gemm as ref
+        fn, args = ref.build()
+        theirs = fn(*args)
+        torch.cuda.synchronize()
+    except Exception as exc:  # noqa: BLE001 - third-party stack missing or unable to compile here
+        pytest.skip(f"FlashInfer reference kernel unavailable: {type(exc).__name__}")
+    from mosaicist_b200.candidates import cand_cuda_gemm as cand
+
+    ours_fn, ours_args = cand.build()
+    ours = ours_fn(*ours_args)
+    torch.cuda.synchronize()
+    oracle = cand.reference()
+    rep = gate.compare_outputs(theirs.float().cpu().numpy(), ours.float().cpu().numpy(), oracle, "bf16")
+    assert rep.passed, rep.failures
+    assert rep.bitwise_equal_fraction > 0.999
