@@ -5,7 +5,10 @@ its own bench.py at the repository root, the MoE layer bench_moe.py):
   C3  MXFP8 grouped GEMM, 32 groups with Zipf(1.2) row counts summing to 16384, n=4096, k=7168
   C4  bf16 x int4 grouped GEMM, 64 groups with m ~ U[64, 512], n=2048, k=7168, group size 128
 
-    python -m mosaicist_b200.bench_configs [--reps 20]
+  C1x the headline NVFP4 grouped GEMM against FlashInfer's CuTeDSL kernel on the same operand
+      bytes (`--vs-flashinfer`; needs the third-party flashinfer + nvidia-cutlass-dsl packages)
+
+    python -m mosaicist_b200.bench_configs [--reps 20] [--vs-flashinfer]
 
 Inputs are seeded synthetic data of those shapes; every timed launch is preceded by an L2
 flush (a 256 MB memset) outside the CUDA-event window.  One JSON line per configuration.
@@ -39,6 +42,46 @@ def _time(fn, reps, flush):
     return ts[len(ts) // 2]
 
 
+def _time_graph(fn, launches=20, reps=15):
+    """us per launch of `launches` back-to-back calls replayed from one CUDA graph (operands
+    stay L2-resident: the warm figure, free of host launch cost for either implementation)."""
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for _ in range(3):
+            fn()
+        st.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            for _ in range(launches):
+                fn()
+        ts = []
+        for _ in range(reps):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(st)
+            graph.replay()
+            e.record(st)
+            st.synchronize()
+            ts.append(s.elapsed_time(e) * 1e3 / launches)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def headline_vs_flashinfer(reps):
+    from .candidates import cand_cuda_gemm as cand, ref_flashinfer_gemm as ref
+
+    ours, a1 = cand.build()
+    theirs, a2 = ref.build()
+    y_ref = theirs(*a2).clone()
+    y = ours(*a1)
+    torch.cuda.synchronize()
+    fl = 2.0 * cand.L * cand.M * cand.N * cand.K
+    us_ours, us_ref = _time_graph(lambda: ours(*a1), reps=reps), _time_graph(lambda: theirs(*a2), reps=reps)
+    return {"config": "C1 NVFP4 masked grouped GEMM l=8 m=512 n=2048 k=2048, same operand bytes, warm, graph of 20",
+            "us": us_ours, "tflops": fl / us_ours / 1e6, "flashinfer_us": us_ref,
+            "flashinfer_tflops": fl / us_ref / 1e6,
+            "bitwise_equal_fraction": float((y == y_ref).float().mean())}
+
+
 def _layout(rows):
     offs, tot = [], 0
     for r in rows:
@@ -58,6 +101,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--vs-flashinfer", action="store_true")
     args = ap.parse_args()
     from . import _lib, ops
 
@@ -70,6 +114,8 @@ def main():
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     g = torch.Generator(device=dev).manual_seed(rank)
     out = []
+    if args.vs_flashinfer and rank == 0:
+        out.append(headline_vs_flashinfer(args.reps))
 
     # C2: dense fp16, this rank's column shard
     n = 8192

@@ -126,9 +126,16 @@ def main():
                                                             L.group_rows, L.alpha1, None, L.config, out=L.gateup),
             "silu_mul_quantize": lambda: ops.quantize_nvfp4_ragged(L.gateup, L.a2_gs, L.group_offsets,
                                                                     L.group_rows, silu=True, out=(L.d_q, L.d_sf)),
+            "gemm1_swiglu_quantize_fused": lambda: ops.ragged_gemm1_swiglu_quantize(
+                L.a_q, L.a_sf, L.w1_q, L.w1_sf, L.group_offsets, L.group_rows, L.alpha1, L.a2_gs,
+                out=(L.d_q, L.d_sf)),
             "gemm2": lambda: ops.ragged_grouped_gemm_nvfp4(L.d_q, L.d_sf, L.w2_q, L.w2_sf, L.group_offsets,
                                                             L.group_rows, L.alpha2, L.row_weight, L.config, out=L.y),
+            "combine": lambda: _lib.check(lib.msc_moe_unpermute(
+                L.y.data_ptr(), L.ids.data_ptr(), L.rank.data_ptr(), L.group_offsets.data_ptr(),
+                combined.data_ptr(), T_loc, h, k, 0, E_loc, st)),
         }
+        combined = torch.empty((T_loc, h), dtype=torch.bfloat16, device=dev)
         per = {}
         for name, fn in stages.items():
             fn(); torch.cuda.synchronize()

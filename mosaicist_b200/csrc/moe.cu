@@ -96,28 +96,50 @@ __global__ void __launch_bounds__(256)
 moe_plan_kernel(const int* __restrict__ ids, int entries, int expert_first, int experts_local,
                 int* __restrict__ rank, int* __restrict__ group_rows, int* __restrict__ group_offsets,
                 int* __restrict__ total_rows, int* __restrict__ scratch) {
-  __shared__ int warp_tot[8];
+  __shared__ int warp_tot[2][8];
   __shared__ int is_last;
   const int e = blockIdx.x;
   const int want = expert_first + e;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned below = (1u << lane) - 1u;
+  const bool vec = (reinterpret_cast<uintptr_t>(ids) & 15) == 0;
   int running = 0;
-  for (int base = 0; base < entries; base += 256) {
-    const int i = base + threadIdx.x;
-    const bool hit = i < entries && __ldg(ids + i) == want;
-    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-    if (lane == 0) warp_tot[warp] = __popc(ballot);
+  // Each thread owns four consecutive pairs per round (one 16-byte load when the round is
+  // full); the per-warp totals are double-buffered so a round costs one block barrier.
+  for (int base = 0, round = 0; base < entries; base += 1024, ++round) {
+    const int i0 = base + threadIdx.x * 4;
+    int4 v = make_int4(-1, -1, -1, -1);
+    if (vec && i0 + 3 < entries) {
+      v = __ldg(reinterpret_cast<const int4*>(ids + i0));
+    } else {
+      if (i0 < entries) v.x = __ldg(ids + i0);
+      if (i0 + 1 < entries) v.y = __ldg(ids + i0 + 1);
+      if (i0 + 2 < entries) v.z = __ldg(ids + i0 + 2);
+      if (i0 + 3 < entries) v.w = __ldg(ids + i0 + 3);
+    }
+    const bool h0 = v.x == want, h1 = v.y == want, h2 = v.z == want, h3 = v.w == want;
+    const unsigned b0 = __ballot_sync(0xffffffffu, h0), b1 = __ballot_sync(0xffffffffu, h1);
+    const unsigned b2 = __ballot_sync(0xffffffffu, h2), b3 = __ballot_sync(0xffffffffu, h3);
+    int* tot = warp_tot[round & 1];
+    if (lane == 0) tot[warp] = __popc(b0) + __popc(b1) + __popc(b2) + __popc(b3);
     __syncthreads();
     int before = 0, total = 0;
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
-      const int c = warp_tot[w];
+      const int c = tot[w];
       if (w < warp) before += c;
       total += c;
     }
-    if (hit) rank[i] = running + before + __popc(ballot & ((1u << lane) - 1u));
+    int r = running + before + __popc(b0 & below) + __popc(b1 & below) + __popc(b2 & below) +
+            __popc(b3 & below);
+    if (h0) rank[i0] = r;
+    r += h0;
+    if (h1) rank[i0 + 1] = r;
+    r += h1;
+    if (h2) rank[i0 + 2] = r;
+    r += h2;
+    if (h3) rank[i0 + 3] = r;
     running += total;
-    __syncthreads();
   }
   if (threadIdx.x == 0) {
     group_rows[e] = running;
@@ -126,15 +148,37 @@ moe_plan_kernel(const int* __restrict__ ids, int entries, int expert_first, int 
     is_last = (ticket == experts_local - 1);
   }
   __syncthreads();
-  if (is_last && threadIdx.x == 0) {
+  if (is_last) {
+    // exclusive scan of the 128-aligned counts, 256 groups per round, by the whole block
     __threadfence();
-    int off = 0;
-    for (int g = 0; g < experts_local; ++g) {
-      group_offsets[g] = off;
-      off += (__ldcg(group_rows + g) + 127) & ~127;
+    __shared__ int scan_tot[8];
+    int carry = 0;
+    for (int base = 0; base < experts_local; base += 256) {
+      const int g = base + threadIdx.x;
+      const int c = g < experts_local ? ((__ldcg(group_rows + g) + 127) & ~127) : 0;
+      int incl = c;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+      }
+      if (lane == 31) scan_tot[warp] = incl;
+      __syncthreads();
+      int before = 0, total = 0;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const int t = scan_tot[w];
+        if (w < warp) before += t;
+        total += t;
+      }
+      if (g < experts_local) group_offsets[g] = carry + before + incl - c;
+      carry += total;
+      __syncthreads();
     }
-    *total_rows = off;
-    *scratch = 0;  // ready for the next call
+    if (threadIdx.x == 0) {
+      *total_rows = carry;
+      *scratch = 0;  // ready for the next call
+    }
   }
 }
 
@@ -153,32 +197,44 @@ struct PermuteParams {
   int entries, hidden, topk, expert_first, experts_local;
 };
 
+// One thread per (token, 16-value block): the block is loaded once and written to the row of
+// every expert the token is routed to.  The quantised bytes depend on the expert only through
+// its global scale, so they are recomputed only when that scale differs from the previous
+// expert's (with one shared input scale a block is quantised once instead of topk times).
 __global__ void __launch_bounds__(256) moe_permute_quantize_kernel(const PermuteParams p) {
   const int kblocks = p.hidden >> 4;
   const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long entry = unit / kblocks;
-  const int kb = (int)(unit - entry * kblocks);
-  int e = -1;
-  if (entry < p.entries) e = __ldg(p.ids + entry) - p.expert_first;
-  const bool valid = e >= 0 && e < p.experts_local;   // uniform over the 4 lanes of a unit
+  const long long token = unit / kblocks;
+  const int kb = (int)(unit - token * kblocks);
+  const bool live = token * p.topk < p.entries;
+  float v[16];
+  if (live) load16_bf16(p.tokens + (size_t)token * p.hidden + kb * 16, v);
+  uint2 q8 = make_uint2(0u, 0u);
   uint32_t sfb = 0;
-  int dest = 0;
-  if (valid) {
-    dest = __ldg(p.group_offsets + e) + __ldg(p.rank + entry);
-    const int token = (int)(entry / p.topk);
-    float v[16];
-    load16_bf16(p.tokens + (size_t)token * p.hidden + kb * 16, v);
-    uint2 q8;
-    quantize_16(v, __ldg(p.gs + e), q8, sfb);
-    *reinterpret_cast<uint2*>(p.q + (size_t)dest * (p.hidden >> 1) + kb * 8) = q8;
-    if (kb == 0) {
-      p.row_weight[dest] = __ldg(p.weights + entry);
-      p.row_token[dest] = token;
+  float have_gs = -1.0f;   // global scales are positive: nothing is cached yet
+  for (int k = 0; k < p.topk; ++k) {   // trip count uniform over the warp: the shuffles converge
+    const long long entry = token * p.topk + k;
+    int e = -1;
+    if (live) e = __ldg(p.ids + entry) - p.expert_first;
+    const bool valid = e >= 0 && e < p.experts_local;   // uniform over the 4 lanes of a unit
+    int dest = 0;
+    if (valid) {
+      const float gs = __ldg(p.gs + e);
+      if (gs != have_gs) {
+        quantize_16(v, gs, q8, sfb);
+        have_gs = gs;
+      }
+      dest = __ldg(p.group_offsets + e) + __ldg(p.rank + entry);
+      *reinterpret_cast<uint2*>(p.q + (size_t)dest * (p.hidden >> 1) + kb * 8) = q8;
+      if (kb == 0) {
+        p.row_weight[dest] = __ldg(p.weights + entry);
+        p.row_token[dest] = (int)token;
+      }
     }
+    const uint32_t word = gather_scale_word(sfb);
+    if (valid && (kb & 3) == 0)
+      *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word(dest, kb >> 2, kblocks >> 2)) = word;
   }
-  const uint32_t word = gather_scale_word(sfb);
-  if (valid && (kb & 3) == 0)
-    *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word(dest, kb >> 2, kblocks >> 2)) = word;
 }
 
 // ---- combine -----------------------------------------------------------------------------
@@ -321,7 +377,7 @@ int msc_moe_permute_quantize(const void* tokens_bf16, const int32_t* ids, const 
   p.row_weight = row_weight; p.row_token = row_token;
   p.entries = tokens * topk; p.hidden = hidden; p.topk = topk;
   p.expert_first = expert_first; p.experts_local = experts_local;
-  const long long units = (long long)p.entries * (hidden / 16);
+  const long long units = (long long)tokens * (hidden / 16);
   const long long blocks = (units + 255) / 256;
   if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
   msc::moe_permute_quantize_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
