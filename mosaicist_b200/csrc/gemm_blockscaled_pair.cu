@@ -505,9 +505,9 @@ template <int KIND, int STAGES>
 static int launch_pair_v(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStream_t stream,
                          bool sf_by_warps) {
   if (p.out_q) {
-    if (KIND != KIND_NVFP4 || STAGES != 4)
-      return fail(MSC_ERR_UNSUPPORTED, "the fused SwiGLU epilogue is built for NVFP4 with 4 stages");
-    return launch_pair<KIND_NVFP4, 4, false, true>(maps, p, grid, stream);
+    if (KIND != KIND_NVFP4 || STAGES != 5)
+      return fail(MSC_ERR_UNSUPPORTED, "the fused SwiGLU epilogue is built for NVFP4 with 5 stages");
+    return launch_pair<KIND_NVFP4, 5, false, true>(maps, p, grid, stream);
   }
   if (sf_by_warps) {
     if (STAGES != 4) return fail(MSC_ERR_UNSUPPORTED, "scale-writer warps are built for 4 stages");
@@ -534,7 +534,7 @@ int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_
   if (rc) return rc;
   if (p.out_q) {
     maps[4] = maps[0];  // the fused epilogue stores with plain writes: no store map needed
-    if (stages <= 0) stages = 4;
+    stages = 5;
   } else {
     rc = make_tmap_bf16_2d(&maps[4], p.out, (uint64_t)rows_total, (uint64_t)p.n, 32);
     if (rc) return rc;
@@ -545,7 +545,9 @@ int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_
   if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
   if (pairs > max_tiles) pairs = (int)max_tiles;
   const int grid = 2 * pairs;
-  if (stages <= 0) stages = 4;
+  // the ring is latency-bound: every extra stage in flight pays (8192^3 NVFP4: 307 / 224 / 196 /
+  // 189 us with 2 / 3 / 4 / 5 stages), and five is what fits beside the store staging
+  if (stages <= 0) stages = sf_by_warps ? 4 : 5;
   if (stages > 5) stages = 5;
   if (stages < 2) stages = 2;
   if (kind == KIND_NVFP4) {
