@@ -19,6 +19,7 @@
 #ifndef MOSAICIST_SM100A_H
 #define MOSAICIST_SM100A_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -233,6 +234,53 @@ int msc_moe_permute_quantize(const void* tokens_bf16, const int32_t* ids, const 
 int msc_moe_unpermute(const void* y, const int32_t* ids, const int32_t* rank,
                       const int32_t* group_offsets, void* out, int tokens, int hidden, int topk,
                       int expert_first, int experts_local, void* stream);
+
+/* ---- expert-parallel exchange over peer memory --------------------------------------------
+ * No counterpart in the reference, which runs on one GPU; the partitioning is the one its
+ * benchmark configuration names (experts split over the GPUs of one box, token dispatch and
+ * combine between them).  Rank r owns the experts [r * E / world, (r + 1) * E / world) and the
+ * buffers a_q / sf_rows / row_weight / y of `rows_cap` rows (a multiple of 128): packed
+ * values and result rows as its grouped GEMMs read and write them, scale bytes row-major
+ * (rows_cap, hidden/16).  Every rank maps every other rank's buffers (msc_peer_*).  Per layer:
+ * msc_moe_plan over all E experts (counts + position of each pair), an all-gather of the
+ * counts, msc_ep_offsets, msc_ep_dispatch_quantize, a barrier, msc_sf_swizzle of the received
+ * scale rows into the MMA tiling, the local GEMMs, a barrier, msc_ep_combine.  The barriers and the all-gather are the caller's (NCCL, stream-ordered);
+ * no kernel of this library waits on another GPU.  A destination row at or beyond rows_cap is
+ * never stored: the pair is dropped, its pair_row set to -1 and bit 0x00E00000 raised in the
+ * status word (msc_status_word_read). */
+
+/* cudaMalloc + cudaIpcGetMemHandle: *ptr is this process's pointer, handle64 receives the 64
+ * bytes another process of the same box passes to msc_peer_open.  msc_peer_close unmaps an
+ * opened pointer, msc_peer_free releases an allocated one (after every peer closed it). */
+int msc_peer_alloc(size_t bytes, void** ptr, void* handle64);
+int msc_peer_open(const void* handle64, void** ptr);
+int msc_peer_close(void* ptr);
+int msc_peer_free(void* ptr);
+
+/* counts_all (world, experts_total) i32: pairs each rank routes to each expert.  Writes
+ * send_base (experts_total): the first row of this rank's pairs of expert e in the owner's
+ * buffers (owner's 128-aligned group offset + the pairs of lower ranks), and this rank's own
+ * group table group_rows / group_offsets (experts_total / world), total_rows (1). */
+int msc_ep_offsets(const int32_t* counts_all, int world, int rank, int experts_total, int rows_cap,
+                   int32_t* send_base, int32_t* group_rows, int32_t* group_offsets,
+                   int32_t* total_rows, void* stream);
+
+/* msc_moe_permute_quantize across ranks: pair (token, k) with global expert e is quantised with
+ * input_gs[e] (experts_total) and stored at row send_base[e] + rank_in_group[pair] of rank
+ * e / (experts_total / world)'s a_q / sf_rows / row_weight, given as host arrays of `world`
+ * device pointers.  pair_row (tokens, topk) i32 receives that row for msc_ep_combine. */
+int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const float* weights,
+                             const int32_t* rank_in_group, const int32_t* send_base,
+                             const float* input_gs, int tokens, int hidden, int topk,
+                             int experts_total, int world, void* const* peer_a_q,
+                             void* const* peer_sf_rows, float* const* peer_row_weight, int rows_cap,
+                             int32_t* pair_row, void* stream);
+
+/* out[token] = bf16( sum over k (ascending, fp32) of y_owner[pair_row] ), reading each owner's
+ * y (rows_cap, hidden) bf16 through `peer_y` (host array of `world` device pointers). */
+int msc_ep_combine(const void* const* peer_y, const int32_t* ids, const int32_t* pair_row, void* out,
+                   int tokens, int hidden, int topk, int experts_total, int world, int rows_cap,
+                   void* stream);
 
 #ifdef __cplusplus
 }

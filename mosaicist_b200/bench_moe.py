@@ -6,7 +6,8 @@ activations.
     python -m torch.distributed.run --nproc-per-node N -m mosaicist_b200.bench_moe --gpus N
 
 One GPU runs all 256 experts; N GPUs run expert-parallel (256/N experts and 8192/N tokens per
-rank, NCCL all-to-all dispatch and combine).  Weights are random bytes in the NVFP4 layout
+rank).  `--exchange peer` (default) dispatches NVFP4 rows into, and combines from, the other
+ranks' buffers through peer memory; `--exchange nccl` uses all-to-all collectives on bf16 rows.  Weights are random bytes in the NVFP4 layout
 (values uniform over the e2m1 codes, block scales in a narrow e4m3 range): the timing does not
 depend on their values, and quantising 6 GB of weights from fp32 would dominate set-up.
 Prints one JSON line: layer TFLOP/s (2 * routed rows * (hidden * 2n + n * hidden)), time per
@@ -45,13 +46,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--cta-pair", type=int, default=0)
     ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer")
     args = ap.parse_args()
 
     import torch.distributed as dist
 
     from . import _lib, ops
     from .moe import MegaMoE
-    from .parallel import ExpertParallelMoE
+    from .parallel import ExpertParallelMoE, PeerBuffers, PeerExpertParallelMoE
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -75,11 +77,19 @@ def main():
     if world == 1:
         layer = MegaMoE(*w, gs_in, gs_a2, topk=k, max_tokens=T_loc, config=cfg)
         run = lambda: layer.forward(tokens, logits)
-    else:
+    elif args.exchange == "nccl":
         # a rank can receive up to 2x its even share before the workspace is exceeded
         inner = MegaMoE(*w, gs_in, gs_a2, topk=1, max_tokens=2 * T_loc * k, expert_first=rank * E_loc,
                         config=cfg)
         layer = ExpertParallelMoE(inner, E, k)
+        run = lambda: layer.forward(tokens, logits)
+    else:
+        rows_cap = (2 * T_loc * k + 127 * E_loc + 127) // 128 * 128
+        bufs = PeerBuffers(rows_cap, h)
+        inner = MegaMoE(*w, gs_in, gs_a2, topk=1, max_tokens=1, expert_first=rank * E_loc, config=cfg,
+                        rows_cap=rows_cap, workspace=bufs.tensors)
+        gs_all = torch.full((E,), 2688.0 / 5.0, dtype=torch.float32, device=dev)
+        layer = PeerExpertParallelMoE(inner, bufs.pointers, bufs.tensors["sf_rows"], gs_all, E, k, T_loc, rank, world)
         run = lambda: layer.forward(tokens, logits)
 
     def barrier():
@@ -106,7 +116,9 @@ def main():
     out = {"metric": "megamoe_layer_tflops", "value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
            "n_gpus": world, "ms_per_layer": ms, "steps": args.steps,
            "config": {"workload": f"MegaMoE tokens={args.tokens} hidden={h} experts={E} top{k} inter={n}",
-                      "parallelism": "single GPU" if world == 1 else f"ep{world}, all-to-all bf16 dispatch + combine"}}
+                      "parallelism": "single GPU" if world == 1 else
+                      (f"ep{world}, all-to-all bf16 dispatch + combine" if args.exchange == "nccl" else
+                       f"ep{world}, NVFP4 dispatch into and bf16 combine from peer memory")}}
 
     if world == 1:
         # per-stage device times on one GPU
@@ -146,9 +158,36 @@ def main():
             per[name] = s.elapsed_time(e) * 1e3 / 5
         out["stage_us"] = per
         out["rows"] = int(L.total_rows[0])
+    if world > 1 and args.exchange == "peer":
+        # device time of each phase on this rank (waiting for slower ranks shows up in the barriers)
+        L = layer
+        phases = [("route_count", lambda: L.count(logits)),
+                  ("allgather_counts", lambda: dist.all_gather_into_tensor(L.counts_all, L.counts)),
+                  ("place", lambda: L.place(L.counts_all)),
+                  ("dispatch", lambda: L.dispatch(tokens)),
+                  ("barrier_rows_landed", lambda: dist.all_reduce(L._flag)),
+                  ("experts", L.experts),
+                  ("barrier_results_ready", lambda: dist.all_reduce(L._flag)),
+                  ("combine", L.combine)]
+        acc = {name: 0.0 for name, _ in phases}
+        reps = 5
+        for _ in range(reps):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(phases) + 1)]
+            ev[0].record()
+            for i, (_, fn) in enumerate(phases):
+                fn()
+                ev[i + 1].record()
+            torch.cuda.synchronize()
+            for i, (name, _) in enumerate(phases):
+                acc[name] += ev[i].elapsed_time(ev[i + 1]) * 1e3 / reps
+        out["phase_us_rank0"] = acc
+        out["rows_rank0"] = int(inner.total_rows[0])
+        assert _lib.status_word() == 0
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
+        if args.exchange == "peer":
+            bufs.close()
         dist.destroy_process_group()
 
 

@@ -1,0 +1,303 @@
+// Expert-parallel token exchange over peer memory: every rank owns a contiguous block of the
+// experts and a slice of the tokens, and the GPUs of one box see each other's receive buffers
+// (CUDA IPC mappings over NVLink).  Instead of sorting rows by destination and calling a
+// library all-to-all, the dispatch kernel quantises a token block once and stores the packed
+// row and its routing weight straight into the owning rank's GEMM operand buffers, at the row
+// the exchanged counts assign to it (the scale bytes go into a row-major buffer, 32-byte
+// pieces over NVLink instead of scattered words, and the owner tiles them locally with
+// msc_sf_swizzle); the combine kernel reads each
+// token's expert outputs from the owners' result buffers and sums them.  The only collective
+// left is the all-gather of the per-expert counts, plus two stream-ordered barriers the host
+// places between the phases (pushes visible before the GEMMs, results complete before the
+// pull).  No kernel here waits on another GPU.
+//
+// The reference has no multi-GPU code; the partitioning is the one its benchmark
+// configuration names (expert-parallel across the GPUs of one box, dispatch and combine).
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "../../include/mosaicist_sm100a.h"
+#include "host_common.h"
+#include "quantize_common.cuh"
+
+namespace msc {
+
+constexpr int kMaxPeers = 16;
+constexpr uint32_t kStatusEpOverflow = 0x00E00000u;   // a destination row beyond rows_cap
+
+// ---- offsets ---------------------------------------------------------------------------------
+// counts_all[s][e]: pairs rank s routes to global expert e.  One block computes, for every
+// expert, the first row this rank's pairs take in the owner's buffers (the owner's 128-aligned
+// group offset plus the pairs of lower ranks), and this rank's own group table.
+__global__ void __launch_bounds__(256)
+ep_offsets_kernel(const int* __restrict__ counts_all, int world, int rank, int experts_total,
+                  int experts_local, int rows_cap, int* __restrict__ send_base,
+                  int* __restrict__ group_rows, int* __restrict__ group_offsets,
+                  int* __restrict__ total_rows, uint32_t* __restrict__ status) {
+  extern __shared__ int aligned_total[];   // experts_total entries
+  for (int e = threadIdx.x; e < experts_total; e += blockDim.x) {
+    int total = 0;
+    for (int s = 0; s < world; ++s) total += __ldg(counts_all + (size_t)s * experts_total + e);
+    aligned_total[e] = (total + 127) & ~127;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts_total; e += blockDim.x) {
+    const int owner = e / experts_local;
+    int off = 0;
+    for (int j = owner * experts_local; j < e; ++j) off += aligned_total[j];
+    int before = 0, total = 0;
+    for (int s = 0; s < world; ++s) {
+      const int c = __ldg(counts_all + (size_t)s * experts_total + e);
+      if (s < rank) before += c;
+      total += c;
+    }
+    send_base[e] = off + before;
+    if (owner == rank) {
+      const int el = e - owner * experts_local;
+      group_rows[el] = total;
+      group_offsets[el] = off;
+      if (el == experts_local - 1) *total_rows = off + aligned_total[e];
+    }
+    if (e == (owner + 1) * experts_local - 1 && off + aligned_total[e] > rows_cap)
+      atomicOr(status, kStatusEpOverflow);
+  }
+}
+
+// ---- dispatch --------------------------------------------------------------------------------
+struct EpDispatchParams {
+  const __nv_bfloat16* tokens;   // (tokens, hidden)
+  const int* ids;                // (tokens, topk) global expert ids
+  const float* weights;          // (tokens, topk)
+  const int* rank_in_group;      // (tokens, topk) position among this rank's pairs of the expert
+  const int* send_base;          // (experts_total)
+  const float* gs;               // (experts_total) input global scale of every expert
+  int* pair_row;                 // (tokens, topk) out: row in the owner's buffers
+  uint32_t* status;
+  uint8_t* q[kMaxPeers];         // per rank: (rows_cap, hidden/2)
+  uint8_t* sf[kMaxPeers];        // per rank: row-major (rows_cap, hidden/16)
+  float* row_weight[kMaxPeers];  // per rank: (rows_cap)
+  int entries, hidden, topk, experts_total, experts_local, rows_cap;
+};
+
+// One thread per (token, 16-value block), as in the single-GPU dispatch: the block is loaded
+// once, quantised once per distinct global scale, and stored into every owner's buffers.
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchParams p) {
+  const int kblocks = p.hidden >> 4;
+  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long token = unit / kblocks;
+  const int kb = (int)(unit - token * kblocks);
+  const bool live = token * p.topk < p.entries;
+  float v[16];
+  if (live) load16_bf16(p.tokens + (size_t)token * p.hidden + kb * 16, v);
+  uint2 q8 = make_uint2(0u, 0u);
+  uint32_t sfb = 0;
+  float have_gs = -1.0f;
+  for (int k = 0; k < p.topk; ++k) {
+    const long long entry = token * p.topk + k;
+    int e = -1;
+    if (live) e = __ldg(p.ids + entry);
+    bool valid = e >= 0 && e < p.experts_total;
+    int dest = 0, owner = 0;
+    if (valid) {
+      owner = e / p.experts_local;
+      dest = __ldg(p.send_base + e) + __ldg(p.rank_in_group + entry);
+      if (dest < 0 || dest >= p.rows_cap) {   // never store outside the owner's buffers
+        valid = false;
+        if (kb == 0) {
+          atomicOr(p.status, kStatusEpOverflow);
+          p.pair_row[entry] = -1;   // the combine skips it
+        }
+      }
+    }
+    if (valid) {
+      const float gs = __ldg(p.gs + e);
+      if (gs != have_gs) {
+        quantize_16(v, gs, q8, sfb);
+        have_gs = gs;
+      }
+      *reinterpret_cast<uint2*>(p.q[owner] + (size_t)dest * (p.hidden >> 1) + kb * 8) = q8;
+      if (kb == 0) {
+        p.row_weight[owner][dest] = __ldg(p.weights + entry);
+        p.pair_row[entry] = dest;
+      }
+    }
+    const uint32_t word = gather_scale_word(sfb);
+    if (valid && (kb & 3) == 0)
+      *reinterpret_cast<uint32_t*>(p.sf[owner] + (size_t)dest * kblocks + kb) = word;
+  }
+  __threadfence_system();   // the stores went to other GPUs: order them before the kernel ends
+}
+
+// ---- combine ---------------------------------------------------------------------------------
+struct EpCombineParams {
+  const __nv_bfloat16* y[kMaxPeers];   // per rank: (rows_cap, hidden), routing weight applied
+  const int* ids;                      // (tokens, topk)
+  const int* pair_row;                 // (tokens, topk)
+  __nv_bfloat16* out;                  // (tokens, hidden)
+  int tokens, hidden, topk, experts_total, experts_local, rows_cap;
+};
+
+__global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p) {
+  const int vecs = p.hidden >> 3;
+  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long token = unit / vecs;
+  const int vc = (int)(unit - token * vecs);
+  if (token >= p.tokens) return;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int k = 0; k < p.topk; ++k) {
+    const long long entry = token * p.topk + k;
+    const int e = __ldg(p.ids + entry);
+    const int row = __ldg(p.pair_row + entry);
+    if (e < 0 || e >= p.experts_total || row < 0 || row >= p.rows_cap) continue;
+    const __nv_bfloat16* src = p.y[e / p.experts_local] + (size_t)row * p.hidden;
+    const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(src) + vc);   // peer memory: L2 only
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      acc[2 * j] = __fadd_rn(acc[2 * j], f.x);
+      acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], f.y);
+    }
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 pr = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    w[j] = *reinterpret_cast<uint32_t*>(&pr);
+  }
+  reinterpret_cast<uint4*>(p.out + (size_t)token * p.hidden)[vc] = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+static int check_world(int world, int experts_total) {
+  if (world < 1 || world > kMaxPeers)
+    return fail(MSC_ERR_UNSUPPORTED, "world=%d must be in [1, %d]", world, kMaxPeers);
+  if (experts_total <= 0 || experts_total % world)
+    return fail(MSC_ERR_BAD_ARG, "%d experts do not split over %d ranks", experts_total, world);
+  return MSC_OK;
+}
+
+}  // namespace msc
+
+extern "C" {
+
+int msc_peer_alloc(size_t bytes, void** ptr, void* handle64) {
+  if (!ptr || !handle64 || bytes == 0) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer or zero size");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  void* d = nullptr;
+  MSC_CUDA_OK(cudaMalloc(&d, bytes));
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, d);
+  if (e != cudaSuccess) {
+    cudaFree(d);
+    return msc::fail(MSC_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+  }
+  memcpy(handle64, &h, 64);
+  *ptr = d;
+  return MSC_OK;
+}
+
+int msc_peer_open(const void* handle64, void** ptr) {
+  if (!handle64 || !ptr) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* d = nullptr;
+  MSC_CUDA_OK(cudaIpcOpenMemHandle(&d, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr = d;
+  return MSC_OK;
+}
+
+int msc_peer_close(void* ptr) {
+  if (!ptr) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  MSC_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+  return MSC_OK;
+}
+
+int msc_peer_free(void* ptr) {
+  if (!ptr) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  MSC_CUDA_OK(cudaFree(ptr));
+  return MSC_OK;
+}
+
+int msc_ep_offsets(const int32_t* counts_all, int world, int rank, int experts_total, int rows_cap,
+                   int32_t* send_base, int32_t* group_rows, int32_t* group_offsets,
+                   int32_t* total_rows, void* stream) {
+  if (!counts_all || !send_base || !group_rows || !group_offsets || !total_rows)
+    return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  int rc = msc::check_world(world, experts_total);
+  if (rc) return rc;
+  if (rank < 0 || rank >= world) return msc::fail(MSC_ERR_BAD_ARG, "rank=%d outside [0, %d)", rank, world);
+  if (experts_total > 8192) return msc::fail(MSC_ERR_UNSUPPORTED, "experts_total=%d exceeds 8192", experts_total);
+  if (rows_cap <= 0 || rows_cap % 128) return msc::fail(MSC_ERR_BAD_ARG, "rows_cap=%d must be a positive multiple of 128", rows_cap);
+  uint32_t* status = reinterpret_cast<uint32_t*>(msc::status_word());
+  if (!status) return MSC_ERR_CUDA;
+  msc::ep_offsets_kernel<<<1, 256, experts_total * sizeof(int), static_cast<cudaStream_t>(stream)>>>(
+      counts_all, world, rank, experts_total, experts_total / world, rows_cap, send_base, group_rows,
+      group_offsets, total_rows, status);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const float* weights,
+                             const int32_t* rank_in_group, const int32_t* send_base,
+                             const float* input_gs, int tokens, int hidden, int topk,
+                             int experts_total, int world, void* const* peer_a_q,
+                             void* const* peer_sf_rows, float* const* peer_row_weight, int rows_cap,
+                             int32_t* pair_row, void* stream) {
+  if (!tokens_bf16 || !ids || !weights || !rank_in_group || !send_base || !input_gs || !peer_a_q ||
+      !peer_sf_rows || !peer_row_weight || !pair_row)
+    return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  int rc = msc::check_world(world, experts_total);
+  if (rc) return rc;
+  if (tokens <= 0 || topk <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (hidden <= 0 || hidden % 64) return msc::fail(MSC_ERR_BAD_ARG, "hidden=%d must be a multiple of 64", hidden);
+  if (rows_cap <= 0 || rows_cap % 128) return msc::fail(MSC_ERR_BAD_ARG, "rows_cap=%d must be a positive multiple of 128", rows_cap);
+  msc::EpDispatchParams p;
+  p.tokens = static_cast<const __nv_bfloat16*>(tokens_bf16);
+  p.ids = ids; p.weights = weights; p.rank_in_group = rank_in_group; p.send_base = send_base;
+  p.gs = input_gs; p.pair_row = pair_row;
+  p.status = reinterpret_cast<uint32_t*>(msc::status_word());
+  if (!p.status) return MSC_ERR_CUDA;
+  for (int r = 0; r < msc::kMaxPeers; ++r) {
+    const bool in = r < world;
+    if (in && (!peer_a_q[r] || !peer_sf_rows[r] || !peer_row_weight[r]))
+      return msc::fail(MSC_ERR_BAD_ARG, "NULL buffer for rank %d", r);
+    p.q[r] = in ? static_cast<uint8_t*>(peer_a_q[r]) : nullptr;
+    p.sf[r] = in ? static_cast<uint8_t*>(peer_sf_rows[r]) : nullptr;
+    p.row_weight[r] = in ? peer_row_weight[r] : nullptr;
+  }
+  p.entries = tokens * topk; p.hidden = hidden; p.topk = topk;
+  p.experts_total = experts_total; p.experts_local = experts_total / world; p.rows_cap = rows_cap;
+  const long long units = (long long)tokens * (hidden / 16);
+  const long long blocks = (units + 255) / 256;
+  if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
+  msc::ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+int msc_ep_combine(const void* const* peer_y, const int32_t* ids, const int32_t* pair_row, void* out,
+                   int tokens, int hidden, int topk, int experts_total, int world, int rows_cap,
+                   void* stream) {
+  if (!peer_y || !ids || !pair_row || !out) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  int rc = msc::check_world(world, experts_total);
+  if (rc) return rc;
+  if (tokens <= 0 || topk <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (hidden <= 0 || hidden % 8) return msc::fail(MSC_ERR_BAD_ARG, "hidden=%d must be a multiple of 8", hidden);
+  msc::EpCombineParams p;
+  for (int r = 0; r < msc::kMaxPeers; ++r) {
+    if (r < world && !peer_y[r]) return msc::fail(MSC_ERR_BAD_ARG, "NULL buffer for rank %d", r);
+    p.y[r] = r < world ? static_cast<const __nv_bfloat16*>(peer_y[r]) : nullptr;
+  }
+  p.ids = ids; p.pair_row = pair_row; p.out = static_cast<__nv_bfloat16*>(out);
+  p.tokens = tokens; p.hidden = hidden; p.topk = topk; p.experts_total = experts_total;
+  p.experts_local = experts_total / world; p.rows_cap = rows_cap;
+  const long long units = (long long)tokens * (hidden / 8);
+  const long long blocks = (units + 255) / 256;
+  if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
+  msc::ep_combine_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+}  // extern "C"

@@ -42,7 +42,11 @@ class MegaMoE:
 
     def __init__(self, w1_q, w1_sf, w1_gs, w1_alpha, w2_q, w2_sf, w2_gs, w2_alpha, input_gs, a2_gs,
                  topk: int, max_tokens: int, expert_first: int = 0,
-                 config: ops.GemmConfig = ops.GemmConfig(), fuse_gemm1: bool = True):
+                 config: ops.GemmConfig = ops.GemmConfig(), fuse_gemm1: bool = True,
+                 rows_cap: int | None = None, workspace: dict | None = None):
+        """`rows_cap` overrides the row capacity of the grouped buffers (default: room for
+        max_tokens * topk rows plus 127 padding rows per expert); `workspace` may provide the
+        buffers other GPUs access under expert parallelism (a_q, a_sf, row_weight, y)."""
         self.E, n2, hh = w1_q.shape
         self.h, self.n, self.topk = hh * 2, n2 // 2, topk
         self.expert_first, self.config = expert_first, config
@@ -56,8 +60,11 @@ class MegaMoE:
         dev = w1_q.device
         T, K, E = max_tokens, topk, self.E
         self.max_tokens = T
-        cap = (T * K + 127 * E + 127) // 128 * 128
+        cap = rows_cap if rows_cap is not None else (T * K + 127 * E + 127) // 128 * 128
+        if cap <= 0 or cap % 128:
+            raise ValueError(f"rows_cap={cap} must be a positive multiple of 128")
         self.rows_cap = cap
+        ws = workspace or {}
         i32 = dict(dtype=torch.int32, device=dev)
         self.ids = torch.empty((T, K), **i32)
         self.weights = torch.empty((T, K), dtype=torch.float32, device=dev)
@@ -66,14 +73,23 @@ class MegaMoE:
         self.group_offsets = torch.zeros((E,), **i32)
         self.total_rows = torch.zeros((1,), **i32)
         self.scratch = torch.zeros((4,), **i32)
-        self.a_q = torch.empty((cap, self.h // 2), dtype=torch.uint8, device=dev)
-        self.a_sf = torch.zeros((cap // 128, self.h // 64, 32, 16), dtype=torch.uint8, device=dev)
-        self.row_weight = torch.zeros((cap,), dtype=torch.float32, device=dev)
+
+        def buf(name, shape, dtype, zero):
+            t = ws.get(name)
+            if t is None:
+                return (torch.zeros if zero else torch.empty)(shape, dtype=dtype, device=dev)
+            if tuple(t.shape) != tuple(shape) or t.dtype != dtype or not t.is_contiguous():
+                raise ValueError(f"workspace[{name!r}] must be a contiguous {dtype} tensor of shape {shape}")
+            return t
+
+        self.a_q = buf("a_q", (cap, self.h // 2), torch.uint8, False)
+        self.a_sf = buf("a_sf", (cap // 128, self.h // 64, 32, 16), torch.uint8, True)
+        self.row_weight = buf("row_weight", (cap,), torch.float32, True)
         self.row_token = torch.zeros((cap,), **i32)
         self.gateup = torch.empty((cap, 2 * self.n), dtype=torch.bfloat16, device=dev)
         self.d_q = torch.empty((cap, self.n // 2), dtype=torch.uint8, device=dev)
         self.d_sf = torch.zeros((cap // 128, self.n // 64, 32, 16), dtype=torch.uint8, device=dev)
-        self.y = torch.empty((cap, self.h), dtype=torch.bfloat16, device=dev)
+        self.y = buf("y", (cap, self.h), torch.bfloat16, False)
 
     def route(self, logits):
         """logits (T, experts_total) f32 -> fills ids / weights; returns them."""
@@ -104,6 +120,17 @@ class MegaMoE:
             self.group_offsets.data_ptr(), self.input_gs.data_ptr(), T, self.h, K,
             self.expert_first, E, self.a_q.data_ptr(), self.a_sf.data_ptr(),
             self.row_weight.data_ptr(), self.row_token.data_ptr(), st))
+        self.run_experts()
+        if out is None:
+            out = torch.empty((T, self.h), dtype=torch.bfloat16, device=tokens.device)
+        _lib.check(lib.msc_moe_unpermute(self.y.data_ptr(), self.ids.data_ptr(), self.rank.data_ptr(),
+                                         self.group_offsets.data_ptr(), out.data_ptr(), T, self.h, K,
+                                         self.expert_first, E, st))
+        return out
+
+    def run_experts(self):
+        """GEMM1 -> SiLU*up + quantise -> GEMM2 over the grouped rows in a_q / a_sf (layout in
+        group_offsets / group_rows), result rows times row_weight into y."""
         if self.fuse_gemm1:
             ops.ragged_gemm1_swiglu_quantize(self.a_q, self.a_sf, self.w1_q, self.w1_sf,
                                              self.group_offsets, self.group_rows, self.alpha1,
@@ -116,9 +143,3 @@ class MegaMoE:
         ops.ragged_grouped_gemm_nvfp4(self.d_q, self.d_sf, self.w2_q, self.w2_sf, self.group_offsets,
                                       self.group_rows, self.alpha2, self.row_weight, self.config,
                                       out=self.y)
-        if out is None:
-            out = torch.empty((T, self.h), dtype=torch.bfloat16, device=tokens.device)
-        _lib.check(lib.msc_moe_unpermute(self.y.data_ptr(), self.ids.data_ptr(), self.rank.data_ptr(),
-                                         self.group_offsets.data_ptr(), out.data_ptr(), T, self.h, K,
-                                         self.expert_first, E, st))
-        return out

@@ -4,11 +4,16 @@ step of the path that really exchanges data — MoE token dispatch and combine.
 * Grouped GEMMs shard by group and dense GEMMs along N; neither needs a collective
   (`group_range`, `column_range`).
 * The MoE layer is expert-parallel: rank r owns experts [r*E/N, (r+1)*E/N) and a slice of the
-  tokens.  `ExpertParallelMoE.forward` routes its tokens, sends every (token, k) pair to the
-  rank that owns its expert with `all_to_all_single` (counts first, then rows, expert ids and
-  routing weights), runs the local expert layer on what arrived, returns the expert outputs
-  with a second all-to-all and sums each token's k contributions.  Received rows always land
-  in this GPU's own memory before any kernel reads them.
+  tokens.  `PeerExpertParallelMoE` is the fast path: the ranks map each other's GEMM operand
+  and result buffers (CUDA IPC over NVLink); after an all-gather of the per-expert counts the
+  dispatch kernel quantises every token once and stores the NVFP4 row straight into the owning
+  rank's buffers, and the combine kernel reads the expert outputs from the owners and sums
+  them.  Two stream-ordered barriers separate the phases; there is no host synchronisation
+  and no row ever crosses NVLink in bf16 on the way in.
+* `ExpertParallelMoE` is the plain version on library collectives: it sends every
+  (token, k) pair to the rank that owns its expert with `all_to_all_single` (counts first,
+  then bf16 rows, expert ids and routing weights), runs the local expert layer on what
+  arrived, and returns the outputs with a second all-to-all.  It also runs on gloo.
 
 The reference has no multi-GPU code; this follows the partitioning the benchmark
 configuration names (expert-parallel across the GPUs of one box, all-to-all dispatch/combine).
@@ -129,3 +134,215 @@ class ExpertParallelMoE:
         _lib.check(lib.msc_moe_unpermute(back.data_ptr(), zeros.data_ptr(), position.data_ptr(),
                                          self._zero.data_ptr(), out.data_ptr(), T, h, k, 0, 1, st))
         return out
+
+
+class _DeviceBytes:
+    """Adapter that lets torch view raw device memory (the CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def exchange_layout(rows_cap: int, hidden: int):
+    """Byte offsets of (a_q, sf_rows, row_weight, y) inside one rank's exchange allocation, and
+    its total size.  Sections start on 1 KB boundaries (TMA maps need 16 bytes)."""
+    sizes = (rows_cap * (hidden // 2), rows_cap * (hidden // 16), rows_cap * 4, rows_cap * hidden * 2)
+    offs, at = [], 0
+    for n in sizes:
+        offs.append(at)
+        at = (at + n + 1023) // 1024 * 1024
+    return offs, at
+
+
+def exchange_views(base: torch.Tensor, rows_cap: int, hidden: int) -> dict:
+    """The four buffers as tensors over a flat uint8 allocation laid out by exchange_layout."""
+    offs, total = exchange_layout(rows_cap, hidden)
+    if base.dtype != torch.uint8 or base.numel() < total:
+        raise ValueError(f"need a uint8 allocation of at least {total} bytes")
+
+    def cut(i, nbytes):
+        return base[offs[i]:offs[i] + nbytes]
+
+    return {
+        "a_q": cut(0, rows_cap * (hidden // 2)).view(rows_cap, hidden // 2),
+        "sf_rows": cut(1, rows_cap * (hidden // 16)).view(rows_cap, hidden // 16),
+        "row_weight": cut(2, rows_cap * 4).view(torch.float32),
+        "y": cut(3, rows_cap * hidden * 2).view(torch.bfloat16).view(rows_cap, hidden),
+    }
+
+
+class PeerBuffers:
+    """One rank's exchange allocation, mapped into every rank of `group` on the same box.
+
+    `tensors` are this rank's a_q / sf_rows / row_weight / y (a_q, row_weight and y double as
+    the MegaMoE workspace; sf_rows receives scale bytes row-major),
+    `pointers[name][r]` is rank r's buffer as seen from this process."""
+
+    def __init__(self, rows_cap: int, hidden: int, group=None):
+        import ctypes
+
+        from . import _lib
+
+        lib = _lib.load()
+        self.group, self.rows_cap, self.hidden = group, rows_cap, hidden
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        offs, total = exchange_layout(rows_cap, hidden)
+        ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        _lib.check(lib.msc_peer_alloc(total, ctypes.byref(ptr), handle))
+        self._own, self._opened = ptr.value, []
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        bases = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                bases.append(self._own)
+                continue
+            q = ctypes.c_void_p()
+            _lib.check(lib.msc_peer_open(ctypes.create_string_buffer(h, 64), ctypes.byref(q)))
+            self._opened.append(q.value)
+            bases.append(q.value)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        flat = torch.as_tensor(_DeviceBytes(self._own, total), device=dev)
+        flat.zero_()
+        self.tensors = exchange_views(flat, rows_cap, hidden)
+        self.pointers = {name: [b + offs[i] for b in bases]
+                         for i, name in enumerate(("a_q", "sf_rows", "row_weight", "y"))}
+        dist.barrier(group=group)   # every rank has zeroed its buffers before anyone writes
+
+    def close(self):
+        """Unmaps the peers' buffers and frees this rank's (collective: all ranks call it)."""
+        from . import _lib
+
+        lib = _lib.load()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for q in self._opened:
+            _lib.check(lib.msc_peer_close(q))
+        self._opened = []
+        dist.barrier(group=self.group)
+        if self._own:
+            self.tensors = {}
+            _lib.check(lib.msc_peer_free(self._own))
+            self._own = None
+
+
+class PeerExpertParallelMoE:
+    """MegaMoE over expert-parallel ranks with dispatch and combine through peer memory.
+
+    `layer` is this rank's `moe.MegaMoE` over its local experts, built with topk=1,
+    expert_first=rank * E_local, rows_cap=`rows_cap` and workspace=this rank's exchange buffers;
+    `pointers[name][r]` are the device addresses of rank r's a_q / sf_rows / row_weight / y
+    (`PeerBuffers.pointers`), `sf_rows` this rank's own (rows_cap, h/16) scale rows; `input_gs_all` (experts_total,) f32 holds every expert's input
+    global scale, since the sender quantises.  The phases `count`, `place`, `dispatch`,
+    `experts`, `combine` are public so one process can drive several ranks' layers in lockstep
+    on one device (each phase for every rank before the next phase)."""
+
+    def __init__(self, layer, pointers: dict, sf_rows, input_gs_all, experts_total: int, topk: int,
+                 max_tokens: int, rank: int, world: int, group=None):
+        import ctypes
+
+        if experts_total % world:
+            raise ValueError(f"{experts_total} experts do not split over {world} ranks")
+        if layer.topk != 1 or layer.expert_first != rank * (experts_total // world):
+            raise ValueError("the local layer must be built with topk=1 and this rank's expert_first")
+        self.layer, self.topk, self.E, self.group = layer, topk, experts_total, group
+        self.rank, self.world, self.rows_cap, self.max_tokens = rank, world, layer.rows_cap, max_tokens
+        self.input_gs_all = input_gs_all.float().contiguous()
+        arr = ctypes.c_void_p * world
+        if tuple(sf_rows.shape) != (layer.rows_cap, layer.h // 16) or sf_rows.dtype != torch.uint8:
+            raise ValueError("sf_rows must be (rows_cap, h/16) uint8")
+        if sf_rows.data_ptr() != pointers["sf_rows"][rank]:
+            raise ValueError("sf_rows is not the buffer the other ranks were given for this rank")
+        self.sf_rows = sf_rows
+        self._q, self._sf = arr(*pointers["a_q"]), arr(*pointers["sf_rows"])
+        self._rw, self._y = arr(*pointers["row_weight"]), arr(*pointers["y"])
+        dev = layer.a_q.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        T, K = max_tokens, topk
+        self.ids = torch.zeros((T, K), **i32)
+        self.weights = torch.zeros((T, K), dtype=torch.float32, device=dev)
+        self.rank_in_group = torch.zeros((T, K), **i32)
+        self.pair_row = torch.full((T, K), -1, **i32)
+        self.counts = torch.zeros((experts_total,), **i32)
+        self.counts_all = torch.zeros((world, experts_total), **i32)
+        self.send_base = torch.zeros((experts_total,), **i32)
+        self._tmp = torch.zeros((experts_total + 8,), **i32)
+        self._scratch = torch.zeros((4,), **i32)
+        self._flag = torch.zeros((1,), **i32)
+        self._T = 0
+
+    @staticmethod
+    def _stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    def count(self, logits):
+        """Routes this rank's tokens and counts its pairs per global expert (`counts`)."""
+        from . import _lib
+
+        lib = _lib.load()
+        T = logits.shape[0]
+        if T > self.max_tokens:
+            raise ValueError(f"{T} tokens exceed the workspace built for {self.max_tokens}")
+        self._T = T
+        st = self._stream()
+        _lib.check(lib.msc_moe_route_topk(logits.data_ptr(), self.ids.data_ptr(), self.weights.data_ptr(),
+                                          T, logits.shape[1], self.topk, st))
+        _lib.check(lib.msc_moe_plan(self.ids.data_ptr(), T * self.topk, 0, self.E,
+                                    self.rank_in_group.data_ptr(), self.counts.data_ptr(),
+                                    self._tmp.data_ptr(), self._tmp[self.E:].data_ptr(),
+                                    self._scratch.data_ptr(), st))
+        return self.counts
+
+    def place(self, counts_all):
+        """From all ranks' counts: where this rank's pairs go, and this rank's group table."""
+        from . import _lib
+
+        L = self.layer
+        _lib.check(_lib.load().msc_ep_offsets(counts_all.data_ptr(), self.world, self.rank, self.E,
+                                              self.rows_cap, self.send_base.data_ptr(),
+                                              L.group_rows.data_ptr(), L.group_offsets.data_ptr(),
+                                              L.total_rows.data_ptr(), self._stream()))
+
+    def dispatch(self, tokens):
+        from . import _lib
+
+        T = self._T
+        if tokens.shape[0] != T or tokens.dtype != torch.bfloat16 or not tokens.is_contiguous():
+            raise ValueError("tokens must be the contiguous bf16 rows the logits were routed for")
+        _lib.check(_lib.load().msc_ep_dispatch_quantize(
+            tokens.data_ptr(), self.ids.data_ptr(), self.weights.data_ptr(), self.rank_in_group.data_ptr(),
+            self.send_base.data_ptr(), self.input_gs_all.data_ptr(), T, self.layer.h, self.topk, self.E,
+            self.world, self._q, self._sf, self._rw, self.rows_cap, self.pair_row.data_ptr(),
+            self._stream()))
+
+    def experts(self):
+        """Tiles the received scale rows for the MMA, then the two grouped GEMMs."""
+        from . import _lib
+
+        L = self.layer
+        _lib.check(_lib.load().msc_sf_swizzle(self.sf_rows.data_ptr(), L.a_sf.data_ptr(), 1, self.rows_cap,
+                                              L.h // 16, self._stream()))
+        L.run_experts()
+
+    def combine(self, out=None):
+        from . import _lib
+
+        T = self._T
+        if out is None:
+            out = torch.empty((T, self.layer.h), dtype=torch.bfloat16, device=self.ids.device)
+        _lib.check(_lib.load().msc_ep_combine(self._y, self.ids.data_ptr(), self.pair_row.data_ptr(),
+                                              out.data_ptr(), T, self.layer.h, self.topk, self.E,
+                                              self.world, self.rows_cap, self._stream()))
+        return out
+
+    def forward(self, tokens, logits, out=None):
+        """tokens (T_local, h) bf16, logits (T_local, experts_total) f32 -> (T_local, h) bf16."""
+        self.count(logits)
+        dist.all_gather_into_tensor(self.counts_all, self.counts, group=self.group)
+        self.place(self.counts_all)
+        self.dispatch(tokens)
+        dist.all_reduce(self._flag, group=self.group)   # every rank's rows have landed
+        self.experts()
+        dist.all_reduce(self._flag, group=self.group)   # every rank's results are complete
+        return self.combine(out)

@@ -45,6 +45,26 @@ def plan(ids: np.ndarray, expert_first: int, experts_local: int):
     return rank.reshape(ids.shape), rows, offs, tot
 
 
+def ep_placement(counts_all: np.ndarray, rank: int):
+    """Expert-parallel placement from all ranks' per-expert pair counts (world, experts): the
+    first row this rank's pairs of every expert take in the owner's buffers (owner's 128-aligned
+    group offset + the pairs of lower ranks), and this rank's own rows per expert, group
+    offsets and padded total.  The reference is single-GPU; this states the layout the
+    expert-parallel kernels agree on so that a rank's rows of one expert are ordered by source
+    rank, then token."""
+    world, experts = counts_all.shape
+    el = experts // world
+    total = counts_all.sum(axis=0)
+    aligned = (total + 127) // 128 * 128
+    send_base = np.zeros(experts, np.int32)
+    for e in range(experts):
+        first = e // el * el
+        send_base[e] = aligned[first:e].sum() + counts_all[:rank, e].sum()
+    mine = slice(rank * el, (rank + 1) * el)
+    offs = np.concatenate([[0], np.cumsum(aligned[mine])[:-1]]).astype(np.int32)
+    return send_base, total[mine].astype(np.int32), offs, int(aligned[mine].sum())
+
+
 def routed_moe(tokens_bf16, ids, weights, w1_q, w1_sf, w1_gs, w1_alpha, w2_q, w2_sf, w2_gs, w2_alpha,
                input_gs, a2_gs, expert_first: int = 0):
     """out[t] = bf16( sum_k bf16( w_tk * expert_e(t) ) ) over the local experts, each expert

@@ -1,0 +1,119 @@
+"""The peer-memory expert-parallel exchange on ONE device: several ranks' layers live in one
+process, every phase runs for all of them before the next phase starts (which is what the
+barriers guarantee between real ranks), and the buffers a rank would reach over NVLink are
+plain tensors of the same device.  Each rank's output must equal, bit for bit, what the
+single-GPU layer computes for the same tokens; the placement kernel must equal its oracle."""
+
+import ml_dtypes
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe as M
+from tests.test_moe_gpu import T, _dev_weights, _weights
+
+pytestmark = pytest.mark.gpu
+
+
+def _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs):
+    from mosaicist_b200.moe import MegaMoE
+    from mosaicist_b200.parallel import PeerExpertParallelMoE, exchange_layout, exchange_views
+
+    el = E // world
+    d = _dev_weights(w)
+    _, total = exchange_layout(rows_cap, h)
+    spaces = [exchange_views(torch.zeros(total, dtype=torch.uint8, device="cuda"), rows_cap, h)
+              for _ in range(world)]
+    pointers = {name: [s[name].data_ptr() for s in spaces] for name in ("a_q", "sf_rows", "row_weight", "y")}
+    ranks = []
+    for r in range(world):
+        sl = slice(r * el, (r + 1) * el)
+        layer = MegaMoE(d["w1_q"][sl], d["w1_sf"][sl], d["w1_gs"][sl], d["w1_alpha"][sl], d["w2_q"][sl],
+                        d["w2_sf"][sl], d["w2_gs"][sl], d["w2_alpha"][sl], T(input_gs[sl]), T(a2_gs[sl]),
+                        topk=1, max_tokens=1, expert_first=r * el, rows_cap=rows_cap, workspace=spaces[r])
+        ranks.append(PeerExpertParallelMoE(layer, pointers, spaces[r]["sf_rows"], T(input_gs), E, k, T_loc, r, world))
+    return ranks
+
+
+def _lockstep(ranks, tokens, logits):
+    for ep, lg in zip(ranks, logits):
+        ep.count(lg)
+    counts_all = torch.stack([ep.counts for ep in ranks]).contiguous()
+    for ep in ranks:
+        ep.place(counts_all)
+    for ep, tk in zip(ranks, tokens):
+        ep.dispatch(tk)
+    for ep in ranks:
+        ep.experts()
+    return [ep.combine() for ep in ranks], counts_all
+
+
+@pytest.mark.parametrize("world,E,k,h,n,T_loc", [(2, 32, 2, 256, 128, 160), (4, 32, 4, 512, 256, 96),
+                                                  (8, 64, 8, 256, 128, 40)])
+def test_emulated_ranks_equal_single_gpu_layer(world, E, k, h, n, T_loc):
+    from mosaicist_b200 import _lib
+    from mosaicist_b200.moe import MegaMoE
+
+    w = _weights(E, h, n, seed=world)
+    rng = np.random.default_rng([world, 9])
+    tokens = [rng.standard_normal((T_loc, h)).astype(np.float32).astype(ml_dtypes.bfloat16) for _ in range(world)]
+    logits = [rng.standard_normal((T_loc, E)).astype(np.float32) for _ in range(world)]
+    # two distinct input scales, so that a token block is requantised between its experts
+    input_gs = np.where(np.arange(E) % 3 == 0, 2688.0 / 4.0, 2688.0 / 5.0).astype(np.float32)
+    a2_gs = np.full(E, 2688.0 / 4.0, np.float32)
+    rows_cap = (world * T_loc * k + 127 * (E // world) + 127) // 128 * 128
+    ranks = _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs)
+    tk = [T(np.asarray(t, np.float32)).to(torch.bfloat16) for t in tokens]
+    lg = [T(l) for l in logits]
+    for _ in range(2):                                     # buffers are reusable as they are
+        outs, counts_all = _lockstep(ranks, tk, lg)
+    assert _lib.status_word() == 0
+
+    # placement kernel == oracle
+    ca = counts_all.cpu().numpy()
+    for r, ep in enumerate(ranks):
+        ids, _ = M.route_topk(logits[r], k)
+        _, counts, _, _ = M.plan(ids, 0, E)
+        assert np.array_equal(ca[r], counts)
+        send_base, rows, offs, total = M.ep_placement(ca, r)
+        assert np.array_equal(ep.send_base.cpu().numpy(), send_base)
+        assert np.array_equal(ep.layer.group_rows.cpu().numpy(), rows)
+        assert np.array_equal(ep.layer.group_offsets.cpu().numpy(), offs)
+        assert int(ep.layer.total_rows[0]) == total
+
+    # every rank's output == the single-GPU layer over all experts on that rank's tokens
+    d = _dev_weights(w)
+    single = MegaMoE(d["w1_q"], d["w1_sf"], d["w1_gs"], d["w1_alpha"], d["w2_q"], d["w2_sf"], d["w2_gs"],
+                     d["w2_alpha"], T(input_gs), T(a2_gs), topk=k, max_tokens=T_loc)
+    for r in range(world):
+        want = single.forward(tk[r], lg[r])
+        assert torch.equal(outs[r], want), (r, (outs[r].float() - want.float()).abs().max())
+        assert np.count_nonzero(want.float().cpu().numpy()) > 0.9 * want.numel()
+    assert _lib.status_word() == 0
+
+
+def test_overflowing_rank_drops_rows_and_raises_the_status_bit():
+    """More rows than rows_cap: nothing is stored out of bounds, the status word reports it."""
+    from mosaicist_b200 import _lib
+
+    world, E, k, h, n, T_loc = 2, 32, 2, 256, 128, 160
+    w = _weights(E, h, n, seed=1)
+    rng = np.random.default_rng(3)
+    tokens = [T(rng.standard_normal((T_loc, h)).astype(np.float32)).to(torch.bfloat16) for _ in range(world)]
+    logits = [T(rng.standard_normal((T_loc, E)).astype(np.float32)) for _ in range(world)]
+    gs = np.full(E, 2688.0 / 5.0, np.float32)
+    ranks = _layers(world, E, k, h, n, T_loc, 128, w, gs, gs)        # far too small
+    for ep, lg in zip(ranks, logits):
+        ep.count(lg)
+    counts_all = torch.stack([ep.counts for ep in ranks]).contiguous()
+    for ep, tk in zip(ranks, tokens):
+        ep.place(counts_all)
+        ep.dispatch(tk)
+    assert _lib.status_word() & 0x00E00000
+    ca = counts_all.cpu().numpy()
+    for r, ep in enumerate(ranks):
+        rows = ep.pair_row[:T_loc].cpu().numpy()
+        ids = ep.ids[:T_loc].cpu().numpy()
+        dest = M.ep_placement(ca, r)[0][ids] + ep.rank_in_group[:T_loc].cpu().numpy()
+        assert np.array_equal(rows, np.where(dest < 128, dest, -1))     # dropped pairs are marked
+        assert (rows == -1).any()

@@ -66,3 +66,56 @@ def _worker(rank, world, port, experts, skew):
 @pytest.mark.parametrize("skew", [False, True])
 def test_token_exchange_world2(skew):
     mp.spawn(_worker, args=(2, _free_port(), 8, skew), nprocs=2, join=True)
+
+
+def _placement_worker(rank, world, port, experts):
+    """The peer-memory exchange's placement arithmetic, with the counts really all-gathered
+    between two processes: every pair gets a distinct row inside its owner's capacity, rows of
+    one expert are contiguous and ordered by source rank, then by token."""
+    import numpy as np
+
+    from oracle import moe as M
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(50 + rank)
+        T, k = 300 + 17 * rank, 4
+        ids = np.stack([rng.choice(experts, k, replace=False) for _ in range(T)]).astype(np.int32)
+        pos, counts, _, _ = M.plan(ids, 0, experts)
+        gathered = [torch.zeros(experts, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(counts))
+        counts_all = torch.stack(gathered).numpy()
+        send_base, rows, offs, total = M.ep_placement(counts_all, rank)
+        el = experts // world
+        dest_rank = ids // el
+        dest_row = send_base[ids] + pos
+        # publish (owner, row, source, expert, token) of every pair and check globally on rank 0
+        mine = np.stack([dest_rank.ravel(), dest_row.ravel(), np.full(T * k, rank), ids.ravel(),
+                         np.repeat(np.arange(T), k)], axis=1)
+        everything = [None] * world
+        dist.all_gather_object(everything, mine)
+        tables = [None] * world
+        dist.all_gather_object(tables, (rows, offs, total))
+        if rank == 0:
+            allp = np.concatenate(everything)
+            for owner in range(world):
+                rws, ofs, tot = tables[owner]
+                sel = allp[allp[:, 0] == owner]
+                assert len(np.unique(sel[:, 1])) == len(sel)            # no two pairs share a row
+                assert sel[:, 1].max(initial=-1) < tot
+                for le in range(el):
+                    e = owner * el + le
+                    grp = sel[sel[:, 3] == e]
+                    grp = grp[np.argsort(grp[:, 1])]
+                    assert len(grp) == rws[le]
+                    assert (grp[:, 1] == ofs[le] + np.arange(len(grp))).all()   # contiguous from the offset
+                    key = grp[:, 2] * 10 ** 6 + grp[:, 4]
+                    assert (np.diff(key) > 0).all()                           # by source rank, then token
+                assert (ofs % 128 == 0).all() and tot % 128 == 0
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_exchange_placement_world2():
+    mp.spawn(_placement_worker, args=(2, _free_port(), 8), nprocs=2, join=True)
