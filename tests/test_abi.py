@@ -131,3 +131,22 @@ def test_byte_decoders_match_ml_dtypes():
     got = F.dequant_nvfp4(O.pack_e2m1(q[0]), O.e4m3_bytes(O.to_mma_scale_layout(sf[0])))
     want = q[0].astype(np.float64) * np.repeat(sf[0].astype(np.float64), 16, axis=-1)
     assert np.array_equal(got, want)
+
+
+def test_profile_stage_summary_table():
+    """The profiling stage's CSV folding: per kernel launches, average duration, DRAM GB/s."""
+    from mosaicist_b200.profile_stage import METRICS, summarise
+
+    head = '"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size","Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"'
+    rows = ["==PROF== Connected to process 1", head]
+    vals = {0: [10000, 4_000_000, 1_000_000, 50.0, 30.0, 153, 15.0], 1: [30000, 8_000_000, 2_000_000, 60.0, 40.0, 153, 17.0],
+            2: [5000, 1_000_000, 0, 10.0, 0.0, 32, 80.0]}
+    names = {0: "gemm_pair_kernel<0, 5, 0, 0>(CUtensorMap)", 1: "gemm_pair_kernel<0, 5, 0, 0>(CUtensorMap)",
+             2: "moe_plan_kernel(const int *)"}
+    units = ["ns", "byte", "byte", "%", "%", "register/thread", "%"]
+    for i, v in vals.items():
+        for m, u, x in zip(METRICS, units, v):
+            rows.append(f'"{i}","1","python","host","{names[i]}","1","7","(320, 1, 1)","(148, 1, 1)","0","10.0","Command line profiler metrics","{m}","{u}","{x}"')
+    table = summarise("\n".join(rows)).splitlines()
+    assert table[2].startswith("| gemm_pair_kernel<0, 5, 0, 0> | 2 | 20.0 | 6.00 | 1.50 | 375 | 55.0 | 35.0 | 153 | 16.0 |")
+    assert table[3].startswith("| moe_plan_kernel | 1 | 5.0 | 1.00 | 0.00 | 200 |")
