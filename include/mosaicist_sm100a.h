@@ -235,6 +235,22 @@ int msc_moe_unpermute(const void* y, const int32_t* ids, const int32_t* rank,
                       const int32_t* group_offsets, void* out, int tokens, int hidden, int topk,
                       int expert_first, int experts_local, void* stream);
 
+/* msc_grouped_gemm_nvfp4_ragged whose result rows are scattered instead of stored in place:
+ * row r (times alpha and, if given, row_scale[r]) goes to
+ * dest_bases[code >> 26] + (code & 0x3ffffff) * n bf16 with code = row_dest[r] (rows_total) i32;
+ * rows with a negative code are skipped.  dest_bases is a host array of dest_count (<= 16)
+ * device pointers, which may be other GPUs' mapped memory: each row leaves as untiled 256-byte
+ * bulk copies (cp.async.bulk shared -> global), never as a tiled or multicast operation.  The
+ * MoE's second GEMM uses it to deliver every result row to the token's home rank while the
+ * GEMM is still running.  No counterpart in the reference.  n % 256 == 0, k % 64 == 0. */
+int msc_grouped_gemm_nvfp4_scatter_ragged(const void* a_q, const void* a_sf, const void* b_q,
+                                          const void* b_sf, const float* alpha,
+                                          const int32_t* group_offsets, const int32_t* group_rows,
+                                          const float* row_scale, const int32_t* row_dest,
+                                          void* const* dest_bases, int dest_count, int l,
+                                          int rows_total, int n, int k, const msc_gemm_cfg* cfg,
+                                          void* stream);
+
 /* ---- expert-parallel exchange over peer memory --------------------------------------------
  * No counterpart in the reference, which runs on one GPU; the partitioning is the one its
  * benchmark configuration names (experts split over the GPUs of one box, token dispatch and
@@ -268,12 +284,16 @@ int msc_ep_offsets(const int32_t* counts_all, int world, int rank, int experts_t
 /* msc_moe_permute_quantize across ranks: pair (token, k) with global expert e is quantised with
  * input_gs[e] (experts_total) and stored at row send_base[e] + rank_in_group[pair] of rank
  * e / (experts_total / world)'s a_q / sf_rows / row_weight, given as host arrays of `world`
- * device pointers.  pair_row (tokens, topk) i32 receives that row for msc_ep_combine. */
+ * device pointers.  pair_row (tokens, topk) i32 receives that row for msc_ep_combine.  With
+ * peer_row_dest (host array of `world` pointers to (rows_cap) i32, or NULL) the owner also
+ * learns where the row's result belongs: code (rank << 26) | (token * topk + k), the form
+ * msc_grouped_gemm_nvfp4_scatter_ragged takes. */
 int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const float* weights,
                              const int32_t* rank_in_group, const int32_t* send_base,
                              const float* input_gs, int tokens, int hidden, int topk,
                              int experts_total, int world, void* const* peer_a_q,
-                             void* const* peer_sf_rows, float* const* peer_row_weight, int rows_cap,
+                             void* const* peer_sf_rows, float* const* peer_row_weight,
+                             int32_t* const* peer_row_dest, int rank, int rows_cap,
                              int32_t* pair_row, void* stream);
 
 /* out[token] = bf16( sum over k (ascending, fp32) of y_owner[pair_row] ), reading each owner's
@@ -281,6 +301,11 @@ int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const 
 int msc_ep_combine(const void* const* peer_y, const int32_t* ids, const int32_t* pair_row, void* out,
                    int tokens, int hidden, int topk, int experts_total, int world, int rows_cap,
                    void* stream);
+
+/* out[token] = bf16( sum over k (ascending, fp32) of y_pairs[token * topk + k] ): the last step
+ * when the second GEMM scattered every pair's result row to the token's home rank.
+ * y_pairs (tokens * topk, hidden) bf16, out (tokens, hidden) bf16. */
+int msc_ep_sum_pairs(const void* y_pairs, void* out, int tokens, int hidden, int topk, void* stream);
 
 #ifdef __cplusplus
 }

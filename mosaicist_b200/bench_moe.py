@@ -47,6 +47,8 @@ def main():
     ap.add_argument("--cta-pair", type=int, default=0)
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer")
+    ap.add_argument("--combine", choices=["push", "pull"], default="push",
+                    help="peer exchange: GEMM2 scatters result rows to the home ranks / the home rank pulls them")
     args = ap.parse_args()
 
     import torch.distributed as dist
@@ -85,11 +87,14 @@ def main():
         run = lambda: layer.forward(tokens, logits)
     else:
         rows_cap = (2 * T_loc * k + 127 * E_loc + 127) // 128 * 128
-        bufs = PeerBuffers(rows_cap, h)
+        push = args.combine == "push"
+        bufs = PeerBuffers(rows_cap, h, T_loc * k if push else 0)
+        extra = dict(row_dest=bufs.tensors["row_dest"], recv_y=bufs.tensors["recv_y"]) if push else {}
         inner = MegaMoE(*w, gs_in, gs_a2, topk=1, max_tokens=1, expert_first=rank * E_loc, config=cfg,
                         rows_cap=rows_cap, workspace=bufs.tensors)
         gs_all = torch.full((E,), 2688.0 / 5.0, dtype=torch.float32, device=dev)
-        layer = PeerExpertParallelMoE(inner, bufs.pointers, bufs.tensors["sf_rows"], gs_all, E, k, T_loc, rank, world)
+        layer = PeerExpertParallelMoE(inner, bufs.pointers, bufs.tensors["sf_rows"], gs_all, E, k, T_loc, rank, world,
+                                      **extra)
         run = lambda: layer.forward(tokens, logits)
 
     def barrier():
@@ -118,7 +123,9 @@ def main():
            "config": {"workload": f"MegaMoE tokens={args.tokens} hidden={h} experts={E} top{k} inter={n}",
                       "parallelism": "single GPU" if world == 1 else
                       (f"ep{world}, all-to-all bf16 dispatch + combine" if args.exchange == "nccl" else
-                       f"ep{world}, NVFP4 dispatch into and bf16 combine from peer memory")}}
+                       f"ep{world}, NVFP4 dispatch into peer memory, bf16 results " +
+                       ("scattered to the home rank by the GEMM2 epilogue" if args.combine == "push" else
+                        "pulled from peer memory"))}}
 
     if world == 1:
         # per-stage device times on one GPU

@@ -77,7 +77,8 @@ struct EpDispatchParams {
   uint8_t* q[kMaxPeers];         // per rank: (rows_cap, hidden/2)
   uint8_t* sf[kMaxPeers];        // per rank: row-major (rows_cap, hidden/16)
   float* row_weight[kMaxPeers];  // per rank: (rows_cap)
-  int entries, hidden, topk, experts_total, experts_local, rows_cap;
+  int* row_dest[kMaxPeers];      // per rank: (rows_cap) where the row's result goes, or all null
+  int entries, hidden, topk, experts_total, experts_local, rows_cap, rank;
 };
 
 // One thread per (token, 16-value block), as in the single-GPU dispatch: the block is loaded
@@ -119,6 +120,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchParams
       *reinterpret_cast<uint2*>(p.q[owner] + (size_t)dest * (p.hidden >> 1) + kb * 8) = q8;
       if (kb == 0) {
         p.row_weight[owner][dest] = __ldg(p.weights + entry);
+        if (p.row_dest[owner]) p.row_dest[owner][dest] = (p.rank << 26) | (int)entry;
         p.pair_row[entry] = dest;
       }
     }
@@ -167,6 +169,36 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p
     w[j] = *reinterpret_cast<uint32_t*>(&pr);
   }
   reinterpret_cast<uint4*>(p.out + (size_t)token * p.hidden)[vc] = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// out[token] = bf16(sum over k, ascending, fp32) of y_pairs[token * topk + k]: the last step when
+// the second GEMM has already delivered every pair's result row to the token's home rank.
+__global__ void __launch_bounds__(256)
+ep_sum_pairs_kernel(const __nv_bfloat16* __restrict__ y_pairs, __nv_bfloat16* __restrict__ out,
+                    int tokens, int hidden, int topk) {
+  const int vecs = hidden >> 3;
+  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long token = unit / vecs;
+  const int vc = (int)(unit - token * vecs);
+  if (token >= tokens) return;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int k = 0; k < topk; ++k) {
+    const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(y_pairs + ((size_t)token * topk + k) * hidden) + vc);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      acc[2 * j] = __fadd_rn(acc[2 * j], f.x);
+      acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], f.y);
+    }
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 pr = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    w[j] = *reinterpret_cast<uint32_t*>(&pr);
+  }
+  reinterpret_cast<uint4*>(out + (size_t)token * hidden)[vc] = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 static int check_world(int world, int experts_total) {
@@ -242,7 +274,8 @@ int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const 
                              const int32_t* rank_in_group, const int32_t* send_base,
                              const float* input_gs, int tokens, int hidden, int topk,
                              int experts_total, int world, void* const* peer_a_q,
-                             void* const* peer_sf_rows, float* const* peer_row_weight, int rows_cap,
+                             void* const* peer_sf_rows, float* const* peer_row_weight,
+                             int32_t* const* peer_row_dest, int rank, int rows_cap,
                              int32_t* pair_row, void* stream) {
   if (!tokens_bf16 || !ids || !weights || !rank_in_group || !send_base || !input_gs || !peer_a_q ||
       !peer_sf_rows || !peer_row_weight || !pair_row)
@@ -252,6 +285,9 @@ int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const 
   if (tokens <= 0 || topk <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
   if (hidden <= 0 || hidden % 64) return msc::fail(MSC_ERR_BAD_ARG, "hidden=%d must be a multiple of 64", hidden);
   if (rows_cap <= 0 || rows_cap % 128) return msc::fail(MSC_ERR_BAD_ARG, "rows_cap=%d must be a positive multiple of 128", rows_cap);
+  if (rank < 0 || rank >= world) return msc::fail(MSC_ERR_BAD_ARG, "rank=%d outside [0, %d)", rank, world);
+  if ((long long)tokens * topk > 0x03ffffffLL)
+    return msc::fail(MSC_ERR_UNSUPPORTED, "tokens * topk exceeds the 26 bits of a row destination code");
   msc::EpDispatchParams p;
   p.tokens = static_cast<const __nv_bfloat16*>(tokens_bf16);
   p.ids = ids; p.weights = weights; p.rank_in_group = rank_in_group; p.send_base = send_base;
@@ -265,7 +301,10 @@ int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const 
     p.q[r] = in ? static_cast<uint8_t*>(peer_a_q[r]) : nullptr;
     p.sf[r] = in ? static_cast<uint8_t*>(peer_sf_rows[r]) : nullptr;
     p.row_weight[r] = in ? peer_row_weight[r] : nullptr;
+    p.row_dest[r] = (in && peer_row_dest) ? peer_row_dest[r] : nullptr;
+    if (in && peer_row_dest && !peer_row_dest[r]) return msc::fail(MSC_ERR_BAD_ARG, "NULL row_dest for rank %d", r);
   }
+  p.rank = rank;
   p.entries = tokens * topk; p.hidden = hidden; p.topk = topk;
   p.experts_total = experts_total; p.experts_local = experts_total / world; p.rows_cap = rows_cap;
   const long long units = (long long)tokens * (hidden / 16);
@@ -296,6 +335,19 @@ int msc_ep_combine(const void* const* peer_y, const int32_t* ids, const int32_t*
   const long long blocks = (units + 255) / 256;
   if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
   msc::ep_combine_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+int msc_ep_sum_pairs(const void* y_pairs, void* out, int tokens, int hidden, int topk, void* stream) {
+  if (!y_pairs || !out) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (tokens <= 0 || topk <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (hidden <= 0 || hidden % 8) return msc::fail(MSC_ERR_BAD_ARG, "hidden=%d must be a multiple of 8", hidden);
+  const long long units = (long long)tokens * (hidden / 8);
+  const long long blocks = (units + 255) / 256;
+  if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
+  msc::ep_sum_pairs_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y_pairs), static_cast<__nv_bfloat16*>(out), tokens, hidden, topk);
   MSC_CUDA_OK(cudaGetLastError());
   return MSC_OK;
 }

@@ -519,6 +519,8 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   p.out_q = nullptr;
   p.out_sf = nullptr;
   p.out_gs = nullptr;
+  p.row_dest = nullptr;
+  for (auto& b : p.scatter_base) b = nullptr;
 #ifdef MSC_DEBUG
   p.trace = g_trace;
   p.debug_flags = g_debug_flags;
@@ -614,12 +616,65 @@ int msc_grouped_gemm_nvfp4_swiglu_ragged(const void* a_q, const void* a_sf, cons
   p.out_q = static_cast<uint8_t*>(d_q);
   p.out_sf = static_cast<uint8_t*>(d_sf);
   p.out_gs = out_global_scale;
+  p.row_dest = nullptr;
+  for (auto& b : p.scatter_base) b = nullptr;
 #ifdef MSC_DEBUG
   p.trace = g_trace;
   p.debug_flags = g_debug_flags;
 #endif
   return launch_pair_gemm(KIND_NVFP4, a_q, w1_q, rows_total, k / 2, p, cfg ? cfg->stages : 0,
                           cfg ? cfg->max_ctas : 0, static_cast<cudaStream_t>(stream), false);
+}
+
+int msc_grouped_gemm_nvfp4_scatter_ragged(const void* a_q, const void* a_sf, const void* b_q,
+                                          const void* b_sf, const float* alpha,
+                                          const int32_t* group_offsets, const int32_t* group_rows,
+                                          const float* row_scale, const int32_t* row_dest,
+                                          void* const* dest_bases, int dest_count, int l,
+                                          int rows_total, int n, int k, const msc_gemm_cfg* cfg,
+                                          void* stream) {
+  using namespace msc;
+  if (!a_q || !a_sf || !b_q || !b_sf || !group_offsets || !group_rows || !row_dest || !dest_bases)
+    return fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (dest_count < 1 || dest_count > 16)
+    return fail(MSC_ERR_UNSUPPORTED, "dest_count=%d must be in [1, 16]", dest_count);
+  if (l <= 0 || rows_total <= 0 || n <= 0 || k <= 0) return fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (n % 256) return fail(MSC_ERR_BAD_ARG, "n=%d must be a multiple of 256", n);
+  if (k % 64) return fail(MSC_ERR_BAD_ARG, "k=%d must be a multiple of 64", k);
+  if (reinterpret_cast<uintptr_t>(a_sf) % 16 || reinterpret_cast<uintptr_t>(b_sf) % 16)
+    return fail(MSC_ERR_BAD_ARG, "scale pointers must be 16-byte aligned");
+  int* status = status_word();
+  if (!status) return fail(MSC_ERR_CUDA, "status word unavailable on this device");
+  GemmParams p;
+  p.sfa = static_cast<const uint8_t*>(a_sf);
+  p.sfb = static_cast<const uint8_t*>(b_sf);
+  p.alpha = alpha;
+  p.row_scale = row_scale;
+  p.group_rows = group_rows;
+  p.group_offsets = group_offsets;
+  p.out = nullptr;
+  p.status = status;
+  p.l = l;
+  p.m_stride = 0;
+  p.n = n;
+  p.k_stages = (k / 2 + 127) / 128;
+  p.sf_chunks = k / 64;
+  p.raster = 0;
+  p.out_q = nullptr;
+  p.out_sf = nullptr;
+  p.out_gs = nullptr;
+  p.row_dest = row_dest;
+  for (int i = 0; i < 16; ++i) {
+    p.scatter_base[i] = i < dest_count ? static_cast<uint8_t*>(dest_bases[i]) : nullptr;
+    if (i < dest_count && (!dest_bases[i] || reinterpret_cast<uintptr_t>(dest_bases[i]) % 16))
+      return fail(MSC_ERR_BAD_ARG, "destination %d must be a 16-byte aligned device pointer", i);
+  }
+#ifdef MSC_DEBUG
+  p.trace = g_trace;
+  p.debug_flags = g_debug_flags;
+#endif
+  return launch_pair_gemm(KIND_NVFP4, a_q, b_q, rows_total, k / 2, p, 4, cfg ? cfg->max_ctas : 0,
+                          static_cast<cudaStream_t>(stream), false);
 }
 
 int msc_grouped_gemm_mxfp8_ragged(const void* a_q, const void* a_sf, const void* b_q,

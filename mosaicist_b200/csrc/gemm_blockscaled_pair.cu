@@ -20,7 +20,7 @@
 
 namespace msc {
 
-template <int STAGES, bool SFW = false>
+template <int STAGES, bool SFW = false, bool SCATTER = false>
 struct PairSmem {
   static constexpr int kHeader = 1024;
   static constexpr int kA = 128 * 128;
@@ -37,21 +37,25 @@ struct PairSmem {
   static constexpr int kThreads = (kEpiWarps + 2 + kSfWarps) * 32;
   // two 4 KB store boxes per epilogue warp when the ring leaves room (up to 4 stages), so the
   // second 64-column half never waits for the first half's store to drain
-  static constexpr int kCPerWarp = (STAGES <= 4) ? 8192 : 4096;
+  // the row-scatter epilogue stages 32 linear rows of 256 B at a 272-byte pitch (conflict-free
+  // 16-byte stores: bank = 4 (row + chunk) mod 32)
+  static constexpr int kScatterPitch = 272;
+  static constexpr int kCPerWarp = SCATTER ? 32 * kScatterPitch : (STAGES <= 4) ? 8192 : 4096;
   static constexpr int kC = kEpiWarps * kCPerWarp;
   static constexpr int kTotal = kOffC + kC;
   static constexpr int kAlloc = kTotal + 1024;
   static_assert(kAlloc <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
-template <int KIND, int STAGES, bool SFW, bool SWIGLU>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<STAGES, SFW>::kThreads, 1)
+template <int KIND, int STAGES, bool SFW, bool SWIGLU, bool SCATTER>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<STAGES, SFW, SCATTER>::kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa,
                  const __grid_constant__ CUtensorMap tmap_sfb,
                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
-  using L = PairSmem<STAGES, SFW>;
+  using L = PairSmem<STAGES, SFW, SCATTER>;
+  static_assert(!(SWIGLU && SCATTER), "one epilogue at a time");
   constexpr int kTileN = 256;
   constexpr int kMmaWarp = L::kEpiWarps;
   constexpr int kProducerWarp = L::kEpiWarps + 1;
@@ -403,6 +407,35 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
 
       const int col0 = nt * kTileN + slab * 128;
+      if (SCATTER) {
+        // Every row goes to its own destination (another GPU's memory included): the lane
+        // stages its row's 128 bf16 columns linearly and sends them as one 256-byte bulk copy.
+        // A lane only ever touches its own staging row, so no warp-level ordering is needed.
+        const int dcode = valid ? __ldg(p.row_dest + out_row) : -1;
+        bulk_wait_group_read0();   // this lane's previous copy has left its staging row
+        const uint32_t rowaddr = box0 + lane * L::kScatterPitch;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float lo = __uint_as_float(v[c][q * 8 + 2 * e]) * scale;
+              const float hi = __uint_as_float(v[c][q * 8 + 2 * e + 1]) * scale;
+              __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
+              w[e] = *reinterpret_cast<uint32_t*>(&pr);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (c * 4 + q) * 16),
+                         "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+          }
+        }
+        fence_proxy_async_smem();
+        uint8_t* base = dcode >= 0 ? p.scatter_base[(dcode >> 26) & 15] : nullptr;
+        if (base) bulk_store_1d(base + ((size_t)(dcode & 0x03ffffff) * p.n + col0) * 2, rowaddr, 256);
+        bulk_commit_group();
+        continue;
+      }
       if (whole_warp) {
 #pragma unroll
         for (int sub = 0; sub < 2; ++sub) {
@@ -457,7 +490,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-    if (lane == 0) bulk_wait_group_read0();
+    if (SCATTER) {
+      bulk_wait_group0();        // the row copies are complete, not just read
+      __threadfence_system();    // they may have gone to other GPUs
+    } else if (lane == 0) {
+      bulk_wait_group_read0();
+    }
   }
 
   tc_fence_before_sync();
@@ -482,10 +520,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-template <int KIND, int STAGES, bool SFW, bool SWIGLU = false>
+template <int KIND, int STAGES, bool SFW, bool SWIGLU = false, bool SCATTER = false>
 static int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStream_t stream) {
-  using L = PairSmem<STAGES, SFW>;
-  auto kern = gemm_pair_kernel<KIND, STAGES, SFW, SWIGLU>;
+  using L = PairSmem<STAGES, SFW, SCATTER>;
+  auto kern = gemm_pair_kernel<KIND, STAGES, SFW, SWIGLU, SCATTER>;
   static bool configured[64] = {false};
   int dev = 0;
   MSC_CUDA_OK(cudaGetDevice(&dev));
@@ -508,6 +546,11 @@ static int launch_pair_v(const CUtensorMap* maps, const GemmParams& p, int grid,
     if (KIND != KIND_NVFP4 || STAGES != 5)
       return fail(MSC_ERR_UNSUPPORTED, "the fused SwiGLU epilogue is built for NVFP4 with 5 stages");
     return launch_pair<KIND_NVFP4, 5, false, true>(maps, p, grid, stream);
+  }
+  if (p.row_dest) {
+    if (KIND != KIND_NVFP4 || STAGES != 4)
+      return fail(MSC_ERR_UNSUPPORTED, "the row-scatter epilogue is built for NVFP4 with 4 stages");
+    return launch_pair<KIND_NVFP4, 4, false, false, true>(maps, p, grid, stream);
   }
   if (sf_by_warps) {
     if (STAGES != 4) return fail(MSC_ERR_UNSUPPORTED, "scale-writer warps are built for 4 stages");
@@ -535,6 +578,9 @@ int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_
   if (p.out_q) {
     maps[4] = maps[0];  // the fused epilogue stores with plain writes: no store map needed
     stages = 5;
+  } else if (p.row_dest) {
+    maps[4] = maps[0];  // rows leave as untiled bulk copies: no store map needed
+    stages = 4;
   } else {
     rc = make_tmap_bf16_2d(&maps[4], p.out, (uint64_t)rows_total, (uint64_t)p.n, 32);
     if (rc) return rc;

@@ -28,6 +28,10 @@ struct GemmParams {
   uint8_t* out_q;            // (rows_total, n/4) packed e2m1 of silu(gate) * up
   uint8_t* out_sf;           // its e4m3 scales, tiled (rows_total/128, n/128, 32, 16)
   const float* out_gs;       // [l] global scale of the activation
+  // row-scatter epilogue: row r goes to scatter_base[code >> 26] + (code & 0x3ffffff) * n bf16,
+  // code = row_dest[r]; negative codes are skipped
+  const int* row_dest;       // [rows_total] or null
+  uint8_t* scatter_base[16]; // unused entries are null: rows coded for them are skipped
 #ifdef MSC_DEBUG
   unsigned long long* trace;  // [cta][8 tiles][3 roles][2] clock64 stamps, then [cta][2] at the end
   int debug_flags;            // 1: skip global stores, 2: skip scale loads/copies, 4: skip MMAs

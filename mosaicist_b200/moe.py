@@ -131,6 +131,13 @@ class MegaMoE:
     def run_experts(self):
         """GEMM1 -> SiLU*up + quantise -> GEMM2 over the grouped rows in a_q / a_sf (layout in
         group_offsets / group_rows), result rows times row_weight into y."""
+        self.run_gemm1()
+        ops.ragged_grouped_gemm_nvfp4(self.d_q, self.d_sf, self.w2_q, self.w2_sf, self.group_offsets,
+                                      self.group_rows, self.alpha2, self.row_weight, self.config,
+                                      out=self.y)
+
+    def run_gemm1(self):
+        """a_q / a_sf -> d_q / d_sf: GEMM1 with SiLU(gate) * up and the NVFP4 requantisation."""
         if self.fuse_gemm1:
             ops.ragged_gemm1_swiglu_quantize(self.a_q, self.a_sf, self.w1_q, self.w1_sf,
                                              self.group_offsets, self.group_rows, self.alpha1,
@@ -140,6 +147,3 @@ class MegaMoE:
                                           self.group_rows, self.alpha1, None, self.config, out=self.gateup)
             ops.quantize_nvfp4_ragged(self.gateup, self.a2_gs, self.group_offsets, self.group_rows,
                                       silu=True, out=(self.d_q, self.d_sf))
-        ops.ragged_grouped_gemm_nvfp4(self.d_q, self.d_sf, self.w2_q, self.w2_sf, self.group_offsets,
-                                      self.group_rows, self.alpha2, self.row_weight, self.config,
-                                      out=self.y)

@@ -144,10 +144,16 @@ class _DeviceBytes:
                                          "version": 3, "strides": None}
 
 
-def exchange_layout(rows_cap: int, hidden: int):
-    """Byte offsets of (a_q, sf_rows, row_weight, y) inside one rank's exchange allocation, and
-    its total size.  Sections start on 1 KB boundaries (TMA maps need 16 bytes)."""
-    sizes = (rows_cap * (hidden // 2), rows_cap * (hidden // 16), rows_cap * 4, rows_cap * hidden * 2)
+EXCHANGE_BUFFERS = ("a_q", "sf_rows", "row_weight", "y", "row_dest", "recv_y")
+
+
+def exchange_layout(rows_cap: int, hidden: int, pairs_cap: int = 0):
+    """Byte offsets of the EXCHANGE_BUFFERS inside one rank's exchange allocation, and its total
+    size.  Sections start on 1 KB boundaries (TMA maps and bulk copies need 16 bytes).
+    pairs_cap = tokens * topk this rank may route: the rows of recv_y, where the other ranks'
+    second GEMM delivers this rank's results (0: no such buffer, the combine pulls from y)."""
+    sizes = (rows_cap * (hidden // 2), rows_cap * (hidden // 16), rows_cap * 4, rows_cap * hidden * 2,
+             rows_cap * 4, pairs_cap * hidden * 2)
     offs, at = [], 0
     for n in sizes:
         offs.append(at)
@@ -155,9 +161,9 @@ def exchange_layout(rows_cap: int, hidden: int):
     return offs, at
 
 
-def exchange_views(base: torch.Tensor, rows_cap: int, hidden: int) -> dict:
-    """The four buffers as tensors over a flat uint8 allocation laid out by exchange_layout."""
-    offs, total = exchange_layout(rows_cap, hidden)
+def exchange_views(base: torch.Tensor, rows_cap: int, hidden: int, pairs_cap: int = 0) -> dict:
+    """The buffers as tensors over a flat uint8 allocation laid out by exchange_layout."""
+    offs, total = exchange_layout(rows_cap, hidden, pairs_cap)
     if base.dtype != torch.uint8 or base.numel() < total:
         raise ValueError(f"need a uint8 allocation of at least {total} bytes")
 
@@ -169,17 +175,20 @@ def exchange_views(base: torch.Tensor, rows_cap: int, hidden: int) -> dict:
         "sf_rows": cut(1, rows_cap * (hidden // 16)).view(rows_cap, hidden // 16),
         "row_weight": cut(2, rows_cap * 4).view(torch.float32),
         "y": cut(3, rows_cap * hidden * 2).view(torch.bfloat16).view(rows_cap, hidden),
+        "row_dest": cut(4, rows_cap * 4).view(torch.int32),
+        "recv_y": cut(5, pairs_cap * hidden * 2).view(torch.bfloat16).view(pairs_cap, hidden),
     }
 
 
 class PeerBuffers:
     """One rank's exchange allocation, mapped into every rank of `group` on the same box.
 
-    `tensors` are this rank's a_q / sf_rows / row_weight / y (a_q, row_weight and y double as
-    the MegaMoE workspace; sf_rows receives scale bytes row-major),
+    `tensors` are this rank's EXCHANGE_BUFFERS (a_q, row_weight and y double as the MegaMoE
+    workspace; sf_rows receives scale bytes row-major; row_dest and recv_y serve the push
+    combine),
     `pointers[name][r]` is rank r's buffer as seen from this process."""
 
-    def __init__(self, rows_cap: int, hidden: int, group=None):
+    def __init__(self, rows_cap: int, hidden: int, pairs_cap: int = 0, group=None):
         import ctypes
 
         from . import _lib
@@ -187,7 +196,7 @@ class PeerBuffers:
         lib = _lib.load()
         self.group, self.rows_cap, self.hidden = group, rows_cap, hidden
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        offs, total = exchange_layout(rows_cap, hidden)
+        offs, total = exchange_layout(rows_cap, hidden, pairs_cap)
         ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
         _lib.check(lib.msc_peer_alloc(total, ctypes.byref(ptr), handle))
         self._own, self._opened = ptr.value, []
@@ -205,9 +214,9 @@ class PeerBuffers:
         dev = torch.device("cuda", torch.cuda.current_device())
         flat = torch.as_tensor(_DeviceBytes(self._own, total), device=dev)
         flat.zero_()
-        self.tensors = exchange_views(flat, rows_cap, hidden)
-        self.pointers = {name: [b + offs[i] for b in bases]
-                         for i, name in enumerate(("a_q", "sf_rows", "row_weight", "y"))}
+        self.tensors = exchange_views(flat, rows_cap, hidden, pairs_cap)
+        self.tensors["row_dest"].fill_(-1)
+        self.pointers = {name: [b + offs[i] for b in bases] for i, name in enumerate(EXCHANGE_BUFFERS)}
         dist.barrier(group=group)   # every rank has zeroed its buffers before anyone writes
 
     def close(self):
@@ -239,7 +248,12 @@ class PeerExpertParallelMoE:
     on one device (each phase for every rank before the next phase)."""
 
     def __init__(self, layer, pointers: dict, sf_rows, input_gs_all, experts_total: int, topk: int,
-                 max_tokens: int, rank: int, world: int, group=None):
+                 max_tokens: int, rank: int, world: int, group=None, row_dest=None, recv_y=None):
+        """With `row_dest` (rows_cap,) i32 and `recv_y` (>= max_tokens * topk, h) bf16 — this
+        rank's buffers of those names, whose addresses on every rank are in `pointers` — the
+        combine is pushed: the second GEMM scatters each result row into the home rank's recv_y
+        while it runs, and `combine` only sums k local rows per token.  Without them `combine`
+        pulls the rows from the owners' y after the GEMM."""
         import ctypes
 
         if experts_total % world:
@@ -257,6 +271,16 @@ class PeerExpertParallelMoE:
         self.sf_rows = sf_rows
         self._q, self._sf = arr(*pointers["a_q"]), arr(*pointers["sf_rows"])
         self._rw, self._y = arr(*pointers["row_weight"]), arr(*pointers["y"])
+        self.push = row_dest is not None
+        if self.push:
+            if recv_y is None or recv_y.shape[0] < max_tokens * topk or recv_y.shape[1] != layer.h:
+                raise ValueError("recv_y must hold max_tokens * topk rows of h bf16 values")
+            if row_dest.data_ptr() != pointers["row_dest"][rank] or recv_y.data_ptr() != pointers["recv_y"][rank]:
+                raise ValueError("row_dest / recv_y are not the buffers the other ranks were given")
+            self.row_dest, self.recv_y = row_dest, recv_y
+            self._rd, self._ry = arr(*pointers["row_dest"]), arr(*pointers["recv_y"])
+        else:
+            self._rd = None
         dev = layer.a_q.device
         i32 = dict(dtype=torch.int32, device=dev)
         T, K = max_tokens, topk
@@ -313,8 +337,8 @@ class PeerExpertParallelMoE:
         _lib.check(_lib.load().msc_ep_dispatch_quantize(
             tokens.data_ptr(), self.ids.data_ptr(), self.weights.data_ptr(), self.rank_in_group.data_ptr(),
             self.send_base.data_ptr(), self.input_gs_all.data_ptr(), T, self.layer.h, self.topk, self.E,
-            self.world, self._q, self._sf, self._rw, self.rows_cap, self.pair_row.data_ptr(),
-            self._stream()))
+            self.world, self._q, self._sf, self._rw, self._rd, self.rank, self.rows_cap,
+            self.pair_row.data_ptr(), self._stream()))
 
     def experts(self):
         """Tiles the received scale rows for the MMA, then the two grouped GEMMs."""
@@ -323,7 +347,15 @@ class PeerExpertParallelMoE:
         L = self.layer
         _lib.check(_lib.load().msc_sf_swizzle(self.sf_rows.data_ptr(), L.a_sf.data_ptr(), 1, self.rows_cap,
                                               L.h // 16, self._stream()))
-        L.run_experts()
+        if not self.push:
+            L.run_experts()
+            return
+        L.run_gemm1()
+        _lib.check(_lib.load().msc_grouped_gemm_nvfp4_scatter_ragged(
+            L.d_q.data_ptr(), L.d_sf.data_ptr(), L.w2_q.data_ptr(), L.w2_sf.data_ptr(), L.alpha2.data_ptr(),
+            L.group_offsets.data_ptr(), L.group_rows.data_ptr(), L.row_weight.data_ptr(),
+            self.row_dest.data_ptr(), self._ry, self.world, L.E, self.rows_cap, L.h, L.n,
+            L.config.c(), self._stream()))
 
     def combine(self, out=None):
         from . import _lib
@@ -331,6 +363,10 @@ class PeerExpertParallelMoE:
         T = self._T
         if out is None:
             out = torch.empty((T, self.layer.h), dtype=torch.bfloat16, device=self.ids.device)
+        if self.push:
+            _lib.check(_lib.load().msc_ep_sum_pairs(self.recv_y.data_ptr(), out.data_ptr(), T, self.layer.h,
+                                                    self.topk, self._stream()))
+            return out
         _lib.check(_lib.load().msc_ep_combine(self._y, self.ids.data_ptr(), self.pair_row.data_ptr(),
                                               out.data_ptr(), T, self.layer.h, self.topk, self.E,
                                               self.world, self.rows_cap, self._stream()))

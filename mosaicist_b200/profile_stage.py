@@ -52,7 +52,7 @@ def run_workload():
     from . import _lib, ops
     from .bench_moe import rand_weights
     from .moe import MegaMoE
-    from .parallel import PeerExpertParallelMoE, exchange_layout, exchange_views
+    from .parallel import EXCHANGE_BUFFERS, PeerExpertParallelMoE, exchange_layout, exchange_views
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -115,29 +115,38 @@ def run_workload():
     ops.quantize_nvfp4_ragged(layer.gateup, layer.a2_gs, layer.group_offsets, layer.group_rows, silu=True,
                               out=(layer.d_q, layer.d_sf))
 
-    # expert-parallel exchange kernels, two ranks' layers on this one device in lockstep
-    world, el = 2, E // 2
-    rows_cap = (T * k + 127 * el + 127) // 128 * 128
-    _, total = exchange_layout(rows_cap, hid)
-    spaces = [exchange_views(torch.zeros(total, dtype=torch.uint8, device=dev), rows_cap, hid) for _ in range(world)]
-    ptrs = {nm: [s[nm].data_ptr() for s in spaces] for nm in ("a_q", "sf_rows", "row_weight", "y")}
-    ranks = []
-    for r in range(world):
-        sl = slice(r * el, (r + 1) * el)
-        inner = MegaMoE(*[t[sl] for t in w], gs_in[sl], gs_a2[sl], topk=1, max_tokens=1, expert_first=r * el,
-                        rows_cap=rows_cap, workspace=spaces[r])
-        ranks.append(PeerExpertParallelMoE(inner, ptrs, spaces[r]["sf_rows"], gs_in, E, k, T // 2, r, world))
-    halves = [tokens[: T // 2].contiguous(), tokens[T // 2:].contiguous()]
-    for ep, lg in zip(ranks, [logits[: T // 2].contiguous(), logits[T // 2:].contiguous()]):
-        ep.count(lg)
-    counts_all = torch.stack([ep.counts for ep in ranks]).contiguous()
-    for ep, tk in zip(ranks, halves):
-        ep.place(counts_all)
-        ep.dispatch(tk)
-    for ep in ranks:
-        ep.experts()
-    for ep in ranks:
-        ep.combine()
+    # expert-parallel exchange kernels: two ranks' layers on this one device in lockstep, once
+    # with the combine pulled from the owners' results and once pushed by the GEMM2 epilogue
+    del layer
+    world, el, T2 = 2, E // 2, T // 2
+    rows_cap = (T2 * k + 127 * el + 127) // 128 * 128
+    for push in (False, True):
+        pairs_cap = T2 // 2 * k if push else 0
+        _, total = exchange_layout(rows_cap, hid, pairs_cap)
+        spaces = [exchange_views(torch.zeros(total, dtype=torch.uint8, device=dev), rows_cap, hid, pairs_cap)
+                  for _ in range(world)]
+        ptrs = {nm: [s[nm].data_ptr() for s in spaces] for nm in EXCHANGE_BUFFERS}
+        ranks = []
+        for r in range(world):
+            sl = slice(r * el, (r + 1) * el)
+            inner = MegaMoE(*[t[sl] for t in w], gs_in[sl], gs_a2[sl], topk=1, max_tokens=1, expert_first=r * el,
+                            rows_cap=rows_cap, workspace=spaces[r])
+            extra = dict(row_dest=spaces[r]["row_dest"], recv_y=spaces[r]["recv_y"]) if push else {}
+            ranks.append(PeerExpertParallelMoE(inner, ptrs, spaces[r]["sf_rows"], gs_in, E, k, T2 // 2, r, world,
+                                               **extra))
+        parts = [slice(0, T2 // 2), slice(T2 // 2, T2)]
+        for ep, sl in zip(ranks, parts):
+            ep.count(logits[sl].contiguous())
+        counts_all = torch.stack([ep.counts for ep in ranks]).contiguous()
+        for ep, sl in zip(ranks, parts):
+            ep.place(counts_all)
+            ep.dispatch(tokens[sl].contiguous())
+        for ep in ranks:
+            ep.experts()
+        for ep in ranks:
+            ep.combine()
+        torch.cuda.synchronize()
+        del ranks, spaces
     torch.cuda.synchronize()
     if _lib.status_word() != 0:
         raise RuntimeError("a kernel reported an error status")

@@ -67,7 +67,7 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def _peer_worker(rank, world, port, q):
+def _peer_worker(rank, world, port, q, push):
     """PeerExpertParallelMoE between real processes: buffers mapped through CUDA IPC, dispatch
     stores and combine loads crossing NVLink.  Checked bit for bit against the single-GPU layer
     run on this rank's tokens with all experts, and against the oracle within tolerance."""
@@ -101,12 +101,14 @@ def _peer_worker(rank, world, port, q):
                  w2_sf=T(O.e4m3_bytes(O.retile(w["w2_sf"]))), w2_gs=T(w["w2_gs"]), w2_alpha=T(w["w2_alpha"]))
         sl = slice(rank * E_loc, (rank + 1) * E_loc)
         rows_cap = (world * T_loc * k + 127 * E_loc + 127) // 128 * 128
-        bufs = PeerBuffers(rows_cap, h)
+        bufs = PeerBuffers(rows_cap, h, T_loc * k if push else 0)
+        extra = dict(row_dest=bufs.tensors["row_dest"], recv_y=bufs.tensors["recv_y"]) if push else {}
         local = MegaMoE(d["w1_q"][sl], d["w1_sf"][sl], d["w1_gs"][sl], d["w1_alpha"][sl], d["w2_q"][sl],
                         d["w2_sf"][sl], d["w2_gs"][sl], d["w2_alpha"][sl], T(input_gs[sl]), T(a2_gs[sl]),
                         topk=1, max_tokens=1, expert_first=rank * E_loc, rows_cap=rows_cap,
                         workspace=bufs.tensors)
-        ep = PeerExpertParallelMoE(local, bufs.pointers, bufs.tensors["sf_rows"], T(input_gs), E, k, T_loc, rank, world)
+        ep = PeerExpertParallelMoE(local, bufs.pointers, bufs.tensors["sf_rows"], T(input_gs), E, k, T_loc, rank,
+                                   world, **extra)
         tk = T(np.asarray(tokens, np.float32)).to(torch.bfloat16)
         for _ in range(3):
             got_t = ep.forward(tk, T(logits))
@@ -129,14 +131,15 @@ def _peer_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("push", [False, True], ids=["pull", "push"])
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_peer_memory_expert_parallel_two_gpus():
+def test_peer_memory_expert_parallel_two_gpus(push):
     import torch.multiprocessing as mp
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, q, push)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:

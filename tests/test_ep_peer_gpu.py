@@ -15,23 +15,26 @@ from tests.test_moe_gpu import T, _dev_weights, _weights
 pytestmark = pytest.mark.gpu
 
 
-def _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs):
+def _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs, push=False):
     from mosaicist_b200.moe import MegaMoE
-    from mosaicist_b200.parallel import PeerExpertParallelMoE, exchange_layout, exchange_views
+    from mosaicist_b200.parallel import EXCHANGE_BUFFERS, PeerExpertParallelMoE, exchange_layout, exchange_views
 
     el = E // world
     d = _dev_weights(w)
-    _, total = exchange_layout(rows_cap, h)
-    spaces = [exchange_views(torch.zeros(total, dtype=torch.uint8, device="cuda"), rows_cap, h)
+    pairs_cap = T_loc * k if push else 0
+    _, total = exchange_layout(rows_cap, h, pairs_cap)
+    spaces = [exchange_views(torch.zeros(total, dtype=torch.uint8, device="cuda"), rows_cap, h, pairs_cap)
               for _ in range(world)]
-    pointers = {name: [s[name].data_ptr() for s in spaces] for name in ("a_q", "sf_rows", "row_weight", "y")}
+    pointers = {name: [s[name].data_ptr() for s in spaces] for name in EXCHANGE_BUFFERS}
     ranks = []
     for r in range(world):
         sl = slice(r * el, (r + 1) * el)
         layer = MegaMoE(d["w1_q"][sl], d["w1_sf"][sl], d["w1_gs"][sl], d["w1_alpha"][sl], d["w2_q"][sl],
                         d["w2_sf"][sl], d["w2_gs"][sl], d["w2_alpha"][sl], T(input_gs[sl]), T(a2_gs[sl]),
                         topk=1, max_tokens=1, expert_first=r * el, rows_cap=rows_cap, workspace=spaces[r])
-        ranks.append(PeerExpertParallelMoE(layer, pointers, spaces[r]["sf_rows"], T(input_gs), E, k, T_loc, r, world))
+        extra = dict(row_dest=spaces[r]["row_dest"], recv_y=spaces[r]["recv_y"]) if push else {}
+        ranks.append(PeerExpertParallelMoE(layer, pointers, spaces[r]["sf_rows"], T(input_gs), E, k, T_loc, r,
+                                           world, **extra))
     return ranks
 
 
@@ -48,9 +51,10 @@ def _lockstep(ranks, tokens, logits):
     return [ep.combine() for ep in ranks], counts_all
 
 
+@pytest.mark.parametrize("push", [False, True], ids=["pull", "push"])
 @pytest.mark.parametrize("world,E,k,h,n,T_loc", [(2, 32, 2, 256, 128, 160), (4, 32, 4, 512, 256, 96),
                                                   (8, 64, 8, 256, 128, 40)])
-def test_emulated_ranks_equal_single_gpu_layer(world, E, k, h, n, T_loc):
+def test_emulated_ranks_equal_single_gpu_layer(world, E, k, h, n, T_loc, push):
     from mosaicist_b200 import _lib
     from mosaicist_b200.moe import MegaMoE
 
@@ -62,7 +66,7 @@ def test_emulated_ranks_equal_single_gpu_layer(world, E, k, h, n, T_loc):
     input_gs = np.where(np.arange(E) % 3 == 0, 2688.0 / 4.0, 2688.0 / 5.0).astype(np.float32)
     a2_gs = np.full(E, 2688.0 / 4.0, np.float32)
     rows_cap = (world * T_loc * k + 127 * (E // world) + 127) // 128 * 128
-    ranks = _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs)
+    ranks = _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs, push)
     tk = [T(np.asarray(t, np.float32)).to(torch.bfloat16) for t in tokens]
     lg = [T(l) for l in logits]
     for _ in range(2):                                     # buffers are reusable as they are
