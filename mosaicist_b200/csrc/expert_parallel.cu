@@ -19,6 +19,7 @@
 
 #include "../../include/mosaicist_sm100a.h"
 #include "host_common.h"
+#include "ptx.cuh"
 #include "quantize_common.cuh"
 
 namespace msc {
@@ -129,6 +130,84 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchParams
       *reinterpret_cast<uint32_t*>(p.sf[owner] + (size_t)dest * kblocks + kb) = word;
   }
   __threadfence_system();   // the stores went to other GPUs: order them before the kernel ends
+}
+
+// The same dispatch with the rows leaving as bulk copies: one block per token quantises the
+// row into shared memory (3.5 KB of values + 448 scale bytes at hidden 7168) and one thread
+// sends it to each of the token's experts as two untiled bulk copies, so NVLink sees a few
+// large writes per row instead of hundreds of 8-byte stores.  The row is re-quantised only when
+// an expert's global scale differs from the one in shared memory.  Needs hidden % 256 == 0
+// (the scale row must be a multiple of 16 bytes).
+__global__ void __launch_bounds__(256) ep_dispatch_bulk_kernel(const EpDispatchParams p) {
+  extern __shared__ __align__(16) uint8_t row_smem[];   // [hidden/2] values, [hidden/16] scales
+  __shared__ int s_owner[32], s_dest[32];
+  __shared__ float s_gs[32];
+  const int token = blockIdx.x;
+  const int kblocks = p.hidden >> 4;
+  uint8_t* s_q = row_smem;
+  uint8_t* s_sf = row_smem + (p.hidden >> 1);
+  if (threadIdx.x < 32) {
+    const int k = threadIdx.x;
+    int owner = -1, dest = 0;
+    float gs = 0.0f;
+    if (k < p.topk) {
+      const long long entry = (long long)token * p.topk + k;
+      const int e = __ldg(p.ids + entry);
+      if (e >= 0 && e < p.experts_total) {
+        dest = __ldg(p.send_base + e) + __ldg(p.rank_in_group + entry);
+        if (dest >= 0 && dest < p.rows_cap) {
+          owner = e / p.experts_local;
+          gs = __ldg(p.gs + e);
+          p.row_weight[owner][dest] = __ldg(p.weights + entry);
+          if (p.row_dest[owner]) p.row_dest[owner][dest] = (p.rank << 26) | (int)entry;
+          p.pair_row[entry] = dest;
+        } else {
+          atomicOr(p.status, kStatusEpOverflow);
+          p.pair_row[entry] = -1;
+        }
+      } else {
+        p.pair_row[entry] = -1;
+      }
+    }
+    s_owner[k] = owner;
+    s_dest[k] = dest;
+    s_gs[k] = gs;
+  }
+  __syncthreads();
+  float have_gs = -1.0f;
+  for (int k = 0; k < p.topk; ++k) {          // block-uniform control flow throughout
+    const int owner = s_owner[k];
+    if (owner < 0) continue;
+    const float gs = s_gs[k];
+    if (gs != have_gs) {
+      if (have_gs >= 0.0f) {                  // earlier copies still read the row: let them finish
+        if (threadIdx.x == 0) bulk_wait_group_read0();
+        __syncthreads();
+      }
+      for (int kb = threadIdx.x; kb < kblocks; kb += blockDim.x) {
+        float v[16];
+        load16_bf16(p.tokens + (size_t)token * p.hidden + kb * 16, v);
+        uint2 q8;
+        uint32_t sfb;
+        quantize_16(v, gs, q8, sfb);
+        *reinterpret_cast<uint2*>(s_q + kb * 8) = q8;
+        s_sf[kb] = (uint8_t)sfb;
+      }
+      fence_proxy_async_smem();
+      __syncthreads();
+      have_gs = gs;
+    }
+    if (threadIdx.x == 0) {
+      const int dest = s_dest[k];
+      bulk_store_1d(p.q[owner] + (size_t)dest * (p.hidden >> 1), smem_u32(s_q), (uint32_t)(p.hidden >> 1));
+      bulk_store_1d(p.sf[owner] + (size_t)dest * kblocks, smem_u32(s_sf), (uint32_t)kblocks);
+      bulk_commit_group();
+    }
+  }
+  // the block may retire once the copies have read the row; the writes themselves are complete
+  // when the grid is, which is what the next operation in the stream (the barrier) waits for
+  if (threadIdx.x == 0) bulk_wait_group_read0();
+  __threadfence_system();   // the scalar stores of the first warp went to other GPUs too
 }
 
 // ---- combine ---------------------------------------------------------------------------------
@@ -307,6 +386,12 @@ int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const 
   p.rank = rank;
   p.entries = tokens * topk; p.hidden = hidden; p.topk = topk;
   p.experts_total = experts_total; p.experts_local = experts_total / world; p.rows_cap = rows_cap;
+  if (hidden % 256 == 0 && topk <= 32 && hidden <= 65536) {
+    const int smem = hidden / 2 + hidden / 16;
+    msc::ep_dispatch_bulk_kernel<<<(unsigned)tokens, 256, smem, static_cast<cudaStream_t>(stream)>>>(p);
+    MSC_CUDA_OK(cudaGetLastError());
+    return MSC_OK;
+  }
   const long long units = (long long)tokens * (hidden / 16);
   const long long blocks = (units + 255) / 256;
   if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
