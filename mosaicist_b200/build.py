@@ -1,6 +1,10 @@
 """Builds libmosaicist_sm100a.so (and the PTX text beside it) in-tree with nvcc.
 
-    python -m mosaicist_b200.build [--force]
+    python -m mosaicist_b200.build [--force] [--debug]
+
+`--debug` also builds libmosaicist_sm100a_debug.so with -DMSC_DEBUG: the same kernels plus
+per-CTA clock stamps (clock64 and the global nanosecond timer) and pipeline-stage skip flags,
+used by `mosaicist_b200.clock_probe`; nothing else loads it.
 
 The library is compiled for sm_100a only.  nvcc cross-compiles without a GPU, so this
 runs on a CPU-only machine; the resulting .so is what the GPU machine loads.
@@ -18,6 +22,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "libmosaicist_sm100a.so"
 PTX = PKG / "libmosaicist_sm100a.ptx"
 PTXAS_LOG = PKG / "libmosaicist_sm100a.ptxas.log"
+DEBUG_LIB = PKG / "libmosaicist_sm100a_debug.so"
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo"]
@@ -61,6 +66,22 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     return LIB
 
 
+def build_debug(force: bool = False) -> pathlib.Path:
+    """The -DMSC_DEBUG build (clock stamps, skip flags); returns its path."""
+    deps = list(CSRC.glob("*")) + [PKG.parent / "include" / "mosaicist_sm100a.h"]
+    if not force and DEBUG_LIB.exists() and all(p.stat().st_mtime <= DEBUG_LIB.stat().st_mtime for p in deps):
+        return DEBUG_LIB
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cmd = [nvcc, *ARCH, *COMMON, "-DMSC_DEBUG", "-shared", "-Xcompiler", "-fPIC", "-cudart", "static",
+           "-o", str(DEBUG_LIB), *[str(s) for s in sources()], "-ldl"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stderr[-4000:])
+    return DEBUG_LIB
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose=True)
     print("built", path)
+    if "--debug" in sys.argv:
+        print("built", build_debug(force="--force" in sys.argv))
