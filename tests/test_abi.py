@@ -150,3 +150,38 @@ def test_profile_stage_summary_table():
     table = summarise("\n".join(rows)).splitlines()
     assert table[2].startswith("| gemm_pair_kernel<0, 5, 0, 0> | 2 | 20.0 | 6.00 | 1.50 | 375 | 55.0 | 35.0 | 153 | 16.0 |")
     assert table[3].startswith("| moe_plan_kernel | 1 | 5.0 | 1.00 | 0.00 | 200 |")
+
+
+def test_expert_parallel_entry_points_reject_bad_arguments(lib):
+    """Argument checks of the peer-memory exchange run before any CUDA call."""
+    from mosaicist_b200 import _lib
+
+    one = ctypes.c_void_p(256)
+    two = (ctypes.c_void_p * 2)(256, 256)
+    rc = lib.msc_ep_offsets(one, 3, 0, 32, 1024, one, one, one, one, None)
+    assert rc == _lib.ERR_BAD_ARG and b"do not split" in lib.msc_last_error()
+    rc = lib.msc_ep_offsets(one, 2, 2, 32, 1024, one, one, one, one, None)
+    assert rc == _lib.ERR_BAD_ARG and b"rank=2" in lib.msc_last_error()
+    rc = lib.msc_ep_offsets(one, 2, 0, 32, 1000, one, one, one, one, None)
+    assert rc == _lib.ERR_BAD_ARG and b"rows_cap" in lib.msc_last_error()
+    rc = lib.msc_ep_offsets(one, 17, 0, 34, 1024, one, one, one, one, None)
+    assert rc == _lib.ERR_UNSUPPORTED and b"world=17" in lib.msc_last_error()
+    rc = lib.msc_ep_dispatch_quantize(one, one, one, one, one, one, 8, 100, 2, 32, 2, two, two, two, None, 0,
+                                      1024, one, None)
+    assert rc == _lib.ERR_BAD_ARG and b"hidden=100" in lib.msc_last_error()
+    rc = lib.msc_ep_dispatch_quantize(one, one, one, one, one, one, 1 << 24, 256, 8, 32, 2, two, two, two, None,
+                                      0, 1024, one, None)
+    assert rc == _lib.ERR_UNSUPPORTED and b"26 bits" in lib.msc_last_error()
+    rc = lib.msc_ep_combine(None, one, one, one, 8, 256, 2, 32, 2, 1024, None)
+    assert rc == _lib.ERR_BAD_ARG and b"NULL" in lib.msc_last_error()
+    rc = lib.msc_ep_sum_pairs(one, one, 8, 100, 2, None)
+    assert rc == _lib.ERR_BAD_ARG and b"hidden=100" in lib.msc_last_error()
+    cfg = _lib.GemmCfg()
+    rc = lib.msc_grouped_gemm_nvfp4_scatter_ragged(one, one, one, one, None, one, one, None, one, two, 2, 4, 512,
+                                                   384, 256, cfg, None)
+    assert rc == _lib.ERR_BAD_ARG and b"n=384" in lib.msc_last_error()
+    rc = lib.msc_grouped_gemm_nvfp4_scatter_ragged(one, one, one, one, None, one, one, None, one, two, 17, 4, 512,
+                                                   256, 256, cfg, None)
+    assert rc == _lib.ERR_UNSUPPORTED and b"dest_count=17" in lib.msc_last_error()
+    rc = lib.msc_peer_alloc(0, ctypes.byref(ctypes.c_void_p()), ctypes.create_string_buffer(64))
+    assert rc == _lib.ERR_BAD_ARG
