@@ -180,6 +180,15 @@ int msc_int4_dequant_bf16(const void* q, const void* scales, void* out, int grou
 int msc_grouped_gemm_bf16_ragged(const void* a, const void* b, const float* alpha,
                                  const int32_t* group_offsets, const int32_t* group_rows, void* out,
                                  int l, int rows_total, int n, int k, int max_ctas, void* stream);
+/* The two calls above as one kernel (the reference's problem statement dequantises inside the
+ * GEMM, problems.py:84-87): b_q (l, n, k/2) packed int4 and scales (l, n, k/group_size) bf16 are
+ * read once; converter warps expand each 64-element K stage to bf16(q) * scale in shared memory
+ * for the tensor core.  Same bits as the two-call path.  n % 256 == 0, k % 64 == 0,
+ * group_size % 64 == 0 and dividing k (MSC_ERR_UNSUPPORTED otherwise). */
+int msc_grouped_gemm_bf16_int4_ragged(const void* a, const void* b_q, const void* scales,
+                                      const float* alpha, const int32_t* group_offsets,
+                                      const int32_t* group_rows, void* out, int l, int rows_total,
+                                      int n, int k, int group_size, int max_ctas, void* stream);
 
 /* ---- MoE routing and token movement ---------------------------------------------------
  * The reference's MoE takes per-expert padded batches and has no routing, permutation or

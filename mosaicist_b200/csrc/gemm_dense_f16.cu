@@ -32,19 +32,24 @@ struct DenseParams {
   int band;               // m-tiles per raster band
   int is_bf16;
   int* status;
+  const __nv_bfloat16* scales;   // int4 form: (groups, n, k / group_size)
+  int group_size;
   GemmParams g;           // grouped form: group_rows / group_offsets / alpha / out / l / n
 };
 
-template <int STAGES>
+template <int STAGES, bool INT4 = false>
 struct DenseSmem {
   static constexpr int kHeader = 1024;
   static constexpr int kA = 128 * 128;       // 128 rows x 64 K-elements
   static constexpr int kB = 2 * 64 * 128;    // two boxes of 64 K rows x 64 columns
+  static constexpr int kP = INT4 ? 128 * 32 : 0;   // packed int4: 128 weight rows x 64 K-elements
   static constexpr int kOffA = kHeader;
   static constexpr int kOffB = kOffA + STAGES * kA;
-  static constexpr int kOffC = kOffB + STAGES * kB;
+  static constexpr int kOffP = kOffB + STAGES * kB;
+  static constexpr int kOffC = kOffP + STAGES * kP;
   static constexpr int kEpiWarps = 8;
-  static constexpr int kThreads = (kEpiWarps + 2) * 32;
+  static constexpr int kConvWarps = INT4 ? 8 : 0;  // warps expanding int4 to bf16 in shared memory
+  static constexpr int kThreads = (kEpiWarps + 2 + kConvWarps) * 32;
   static constexpr int kCPerWarp = 4096;
   static constexpr int kTotal = kOffC + kEpiWarps * kCPerWarp;
   static constexpr int kAlloc = kTotal + 1024;
@@ -62,15 +67,19 @@ __device__ __forceinline__ void dense_tile(const DenseParams& p, int t, int& mt,
   mt = b * p.band + (u - nt * rows);
 }
 
-template <int STAGES, bool GROUPED>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DenseSmem<STAGES>::kThreads, 1)
+template <int STAGES, bool GROUPED, bool INT4 = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DenseSmem<STAGES, INT4>::kThreads, 1)
 gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                       const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_c, const DenseParams p) {
-  using L = DenseSmem<STAGES>;
+  using L = DenseSmem<STAGES, INT4>;
+  static_assert(!INT4 || GROUPED, "int4 weights come with the grouped form");
   constexpr int kMmaWarp = L::kEpiWarps;
   constexpr int kProducerWarp = L::kEpiWarps + 1;
-  constexpr uint32_t kStageBytes = L::kA + L::kB;  // per CTA
+  constexpr int kFirstConvWarp = L::kEpiWarps + 2;
+  // bytes TMA brings per CTA and stage onto the leader's full barrier: with int4 weights only A
+  // (the packed weights land on each CTA's own barrier and reach the MMA through the converters)
+  constexpr uint32_t kStageBytes = INT4 ? L::kA : L::kA + L::kB;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -80,6 +89,8 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t bar_empty = sbase + 8 * STAGES;
   const uint32_t bar_acc_full = sbase + 16 * STAGES;  // 2 x 8
   const uint32_t bar_acc_empty = bar_acc_full + 16;   // 2 x 8, leader's are used
+  const uint32_t bar_packed = bar_acc_empty + 16;     // STAGES x 8: this CTA's packed weights landed
+  const uint32_t bar_conv = bar_packed + 8 * STAGES;  // STAGES x 8 (leader's): bf16 weights written
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + 512);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(sgen + 516);
 
@@ -105,6 +116,12 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, 2 * L::kEpiWarps);
+    }
+    if (INT4) {
+      for (int s = 0; s < STAGES; ++s) {
+        mbar_init(bar_packed + 8 * s, 1);
+        mbar_init(bar_conv + 8 * s, 2 * L::kConvWarps);
+      }
     }
     *abort_flag = 0u;
     fence_barrier_init();
@@ -152,7 +169,11 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (elect_one()) {
           if (leader) mbar_arrive_expect_tx(full, 2 * kStageBytes);
           tma_load_2d_pair(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
-          if (GROUPED) {
+          if (INT4) {
+            const uint32_t packed = bar_packed + 8 * s;
+            mbar_arrive_expect_tx(packed, L::kP);
+            tma_load_2d(sbase + L::kOffP + s * L::kP, &tmap_b, packed, kb * 32, col0);
+          } else if (GROUPED) {
             tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, col0);
           } else {
             tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, col0, kb * 64);
@@ -189,6 +210,7 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t acc = tmem_base + buf * 256;
         for (int kb = 0; kb < p.k_stages; ++kb) {
           ok = warp_wait(bar_full + 8 * s, (bits >> s) & 1u, abort_flag, p.status, 3);
+          if (ok && INT4) ok = warp_wait(bar_conv + 8 * s, (bits >> s) & 1u, abort_flag, p.status, 5);
           if (!ok) break;
           bits ^= 1u << s;
           tc_fence_after_sync();
@@ -207,6 +229,71 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (ok && elect_one()) tc_commit_pair(bar_acc_full + 8 * buf, 3);
         __syncwarp();
+      }
+    }
+  } else if (INT4 && warp >= kFirstConvWarp) {
+    // ------------------------------ int4 -> bf16 converters (both CTAs) ---------
+    // Two threads share weight row r of this CTA's 128: per stage each reads 16 of the row's 32
+    // packed bytes (32 K-elements), forms bf16(q) * scale in bf16 (the reference's order,
+    // problems.py:75-81) and writes four of the eight 16-byte chunks of the row in the K-major,
+    // 128-byte-swizzled operand tile the MMA reads (chunk j of row r sits at chunk j ^ (r & 7)).
+    // An int4 value q becomes bf16 exactly: the nibble with its sign bit flipped is q + 8, OR-ed
+    // into the mantissa of 128.0 it reads 136 + q, and subtracting 136 is exact.  The nibbles
+    // of a word are expanded as (n0,n4) (n1,n5) (n2,n6) (n3,n7) - one mask per pair - and
+    // byte-permuted back into K order afterwards.
+    const int ct = (warp - kFirstConvWarp) * 32 + lane;
+    const int r = ct >> 1, half = ct & 1;
+    const int groups_k = p.k_stages * 64 / p.group_size;
+    const int stages_per_group = p.group_size >> 6;
+    uint32_t bits = 0, s = 0;
+    bool ok = true;
+    TileCursor cur;
+    cur.mshift = 8;
+    const __nv_bfloat162 k136 = __float2bfloat162_rn(136.0f);
+    for (int t = pair; ok; t += npairs) {
+      int mt, nt;
+      if (!cur.seek(p.g, ntiles_g, t, mt, nt)) break;
+      const __nv_bfloat16* srow =
+          p.scales + ((size_t)cur.g * p.g.n + nt * 256 + (int)rank * 128 + r) * groups_k;
+      __nv_bfloat16 sc = __ldg(srow);
+      for (int kb = 0; kb < p.k_stages; ++kb) {
+        const int kg = kb / stages_per_group;
+        // the next group's scale is requested before this stage's data is waited for
+        __nv_bfloat16 sc_next = sc;
+        if (kb + 1 < p.k_stages && (kb + 1) % stages_per_group == 0) sc_next = __ldg(srow + kg + 1);
+        ok = warp_wait(bar_packed + 8 * s, (bits >> s) & 1u, abort_flag, p.status, 6);
+        if (!ok) break;
+        bits ^= 1u << s;
+        const uint32_t src = sbase + L::kOffP + s * L::kP + r * 32 + half * 16;
+        const uint32_t dst = sbase + L::kOffB + s * L::kB + r * 128;
+        const __nv_bfloat162 sc2 = __halves2bfloat162(sc, sc);
+        uint32_t w[4];
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(src) : "memory");
+#pragma unroll
+        for (int jl = 0; jl < 4; ++jl) {
+          const uint32_t x = w[jl] ^ 0x88888888u;
+          uint32_t e[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t m = ((x >> (4 * i)) & 0x000F000Fu) | 0x43004300u;   // (n_i, n_{i+4})
+            __nv_bfloat162 v = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&m), k136);
+            v = __hmul2(v, sc2);
+            e[i] = *reinterpret_cast<uint32_t*>(&v);
+          }
+          const uint32_t o0 = __byte_perm(e[0], e[1], 0x5410);   // (n0, n1)
+          const uint32_t o1 = __byte_perm(e[2], e[3], 0x5410);   // (n2, n3)
+          const uint32_t o2 = __byte_perm(e[0], e[1], 0x7632);   // (n4, n5)
+          const uint32_t o3 = __byte_perm(e[2], e[3], 0x7632);   // (n6, n7)
+          const int j = half * 4 + jl;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                       ::"r"(dst + ((j ^ (r & 7)) << 4)), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
+        }
+        fence_proxy_async_smem();   // the tensor core reads these bytes through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster((bar_conv + 8 * s) & kLeaderMask);
+        sc = sc_next;
+        s = (s + 1 == STAGES) ? 0u : s + 1;
       }
     }
   } else {
@@ -235,27 +322,35 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      uint32_t v[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-        tmem_ld_32x32b_x32(tmem_base + lane_base + buf * 256 + slab * 128 + c * 32, v[c]);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster((bar_acc_empty + 8 * buf) & kLeaderMask);
-
       const int row_in = (2 * mt + (int)rank) * 128 + quad * 32;   // row inside the group / matrix
       const int row0 = (GROUPED ? cur.off : 0) + row_in;
       const int colb = (nt * 256 + slab * 128) * 2;   // byte column
-      float scale = 1.0f;
-      if (GROUPED) {
-        scale = p.g.alpha ? __ldg(p.g.alpha + cur.g) : 1.0f;
-        if (row_in + 32 > cur.rows) {
+      const float scale = (GROUPED && p.g.alpha) ? __ldg(p.g.alpha + cur.g) : 1.0f;
+      const bool ragged = GROUPED && row_in + 32 > cur.rows;
+      // The warp's 128 columns are drained in one pass, or in two 64-column passes where the
+      // converter warps leave fewer registers per thread; the accumulator is handed back after
+      // the last read either way (there are two accumulators, the next tile is not waiting).
+      constexpr int kPasses = INT4 ? 2 : 1;
+      constexpr int kCh = 4 / kPasses;          // 32-column chunks per pass
+      constexpr int kSubs = 2 / kPasses;        // 64-column store boxes per pass
+#pragma unroll
+      for (int pass = 0; pass < kPasses; ++pass) {
+        uint32_t v[kCh][32];
+#pragma unroll
+        for (int c = 0; c < kCh; ++c)
+          tmem_ld_32x32b_x32(tmem_base + lane_base + buf * 256 + slab * 128 + (pass * kCh + c) * 32, v[c]);
+        tmem_ld_wait();
+        if (pass == kPasses - 1) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster((bar_acc_empty + 8 * buf) & kLeaderMask);
+        }
+        if (ragged) {
           // ragged end of a group: plain stores of the valid rows only
           if (row_in + lane < cur.rows) {
-            __nv_bfloat16* dst = p.g.out + (size_t)(row0 + lane) * p.g.n + (colb >> 1);
+            __nv_bfloat16* dst = p.g.out + (size_t)(row0 + lane) * p.g.n + (colb >> 1) + pass * kCh * 32;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < kCh; ++c) {
               uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -272,40 +367,41 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           continue;
         }
-      }
 #pragma unroll
-      for (int sub = 0; sub < 2; ++sub) {
-        if (lane == 0) bulk_wait_group_read0();
-        __syncwarp();
+        for (int s2 = 0; s2 < kSubs; ++s2) {
+          const int sub = pass * kSubs + s2;
+          if (lane == 0) bulk_wait_group_read0();
+          __syncwarp();
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = sub * 2 + cc;
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = s2 * 2 + cc;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint32_t w[4];
+            for (int q = 0; q < 4; ++q) {
+              uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float lo = __uint_as_float(v[c][q * 8 + 2 * e]) * scale;
-              const float hi = __uint_as_float(v[c][q * 8 + 2 * e + 1]) * scale;
-              if (p.is_bf16) {
-                __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
-                w[e] = *reinterpret_cast<uint32_t*>(&pr);
-              } else {
-                __half2 pr = __floats2half2_rn(lo, hi);
-                w[e] = *reinterpret_cast<uint32_t*>(&pr);
+              for (int e = 0; e < 4; ++e) {
+                const float lo = __uint_as_float(v[c][q * 8 + 2 * e]) * scale;
+                const float hi = __uint_as_float(v[c][q * 8 + 2 * e + 1]) * scale;
+                if (p.is_bf16) {
+                  __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
+                  w[e] = *reinterpret_cast<uint32_t*>(&pr);
+                } else {
+                  __half2 pr = __floats2half2_rn(lo, hi);
+                  w[e] = *reinterpret_cast<uint32_t*>(&pr);
+                }
               }
+              const int j = cc * 4 + q;
+              const uint32_t addr = box + lane * 128 + ((j ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]),
+                           "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
             }
-            const int j = cc * 4 + q;
-            const uint32_t addr = box + lane * 128 + ((j ^ (lane & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]),
-                         "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
           }
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&tmap_c, box, colb + sub * 128, row0);
-          bulk_commit_group();
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_c, box, colb + sub * 128, row0);
+            bulk_commit_group();
+          }
         }
       }
     }
@@ -395,6 +491,8 @@ extern "C" int msc_grouped_gemm_bf16_ragged(const void* a, const void* b, const 
   p.band = 8;
   p.is_bf16 = 1;
   p.status = status;
+  p.scales = nullptr;
+  p.group_size = 0;
   p.g = GemmParams{};
   p.g.alpha = alpha;
   p.g.group_rows = group_rows;
@@ -411,6 +509,68 @@ extern "C" int msc_grouped_gemm_bf16_ragged(const void* a, const void* b, const 
   constexpr int kStages = 6;
   using L = DenseSmem<kStages>;
   auto kern = gemm_dense_f16_kernel<kStages, true>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  MSC_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+    configured[dev & 63] = true;
+  }
+  cudaLaunchAttribute attr[1];
+  cudaLaunchConfig_t lc =
+      pdl_launch_config(2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream), attr);
+  MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p));
+  return MSC_OK;
+}
+
+extern "C" int msc_grouped_gemm_bf16_int4_ragged(const void* a, const void* b_q, const void* scales,
+                                                 const float* alpha, const int32_t* group_offsets,
+                                                 const int32_t* group_rows, void* out, int l,
+                                                 int rows_total, int n, int k, int group_size,
+                                                 int max_ctas, void* stream) {
+  using namespace msc;
+  if (!a || !b_q || !scales || !out || !group_offsets || !group_rows)
+    return fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (l <= 0 || rows_total <= 0 || n <= 0 || k <= 0) return fail(MSC_ERR_BAD_ARG, "sizes must be positive");
+  if (n % 256) return fail(MSC_ERR_BAD_ARG, "n=%d must be a multiple of 256", n);
+  if (k % 64) return fail(MSC_ERR_BAD_ARG, "k=%d must be a multiple of 64", k);
+  if (group_size <= 0 || group_size % 64 || k % group_size)
+    return fail(MSC_ERR_UNSUPPORTED,
+                "group_size=%d must be a multiple of 64 that divides k (use msc_int4_dequant_bf16 + "
+                "msc_grouped_gemm_bf16_ragged otherwise)", group_size);
+  int* status = status_word();
+  if (!status) return fail(MSC_ERR_CUDA, "status word unavailable on this device");
+  CUtensorMap ta, tb, tc;
+  int rc = make_tmap_pitched_2d(&ta, a, (uint64_t)rows_total, (uint64_t)k * 2, (uint64_t)k * 2, 128);
+  if (rc) return rc;
+  rc = make_tmap_narrow_2d(&tb, b_q, (uint64_t)l * n, (uint64_t)k / 2, 128);
+  if (rc) return rc;
+  rc = make_tmap_pitched_2d(&tc, out, (uint64_t)rows_total, (uint64_t)n * 2, (uint64_t)n * 2, 32);
+  if (rc) return rc;
+  DenseParams p;
+  p.m_tiles = p.n_tiles = 0;
+  p.k_stages = k / 64;
+  p.band = 8;
+  p.is_bf16 = 1;
+  p.status = status;
+  p.scales = static_cast<const __nv_bfloat16*>(scales);
+  p.group_size = group_size;
+  p.g = GemmParams{};
+  p.g.alpha = alpha;
+  p.g.group_rows = group_rows;
+  p.g.group_offsets = group_offsets;
+  p.g.out = static_cast<__nv_bfloat16*>(out);
+  p.g.l = l;
+  p.g.m_stride = 0;
+  p.g.n = n;
+  p.g.raster = 0;
+  int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
+  if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
+  const long long tiles = ((long long)(rows_total + 255) / 256 + l) * (n / 256);
+  if (pairs > tiles) pairs = (int)tiles;
+  constexpr int kStages = 5;
+  using L = DenseSmem<kStages, true>;
+  auto kern = gemm_dense_f16_kernel<kStages, true, true>;
   static bool configured[64] = {false};
   int dev = 0;
   MSC_CUDA_OK(cudaGetDevice(&dev));
@@ -450,6 +610,8 @@ extern "C" int msc_gemm_f16(const void* a, const void* b, void* c, int m, int n,
   p.band = 8;
   p.is_bf16 = dtype;
   p.status = status;
+  p.scales = nullptr;
+  p.group_size = 0;
   p.g = GemmParams{};
   int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
   if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");

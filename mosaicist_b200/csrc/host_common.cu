@@ -57,7 +57,7 @@ namespace {
 struct TmapKey {
   const void* base;
   uint64_t rows, row_bytes;
-  uint32_t box_rows;  // bit 31: bf16 store map; bit 30: unswizzled scale map; else operand map
+  uint32_t box_rows;  // bits 31-30: 2 bf16 store map, 1 unswizzled scale map, 3 unswizzled 32-byte box, 0 operand map
   bool operator==(const TmapKey& o) const {
     return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows;
   }
@@ -113,20 +113,26 @@ int make_tmap_sf_2d(CUtensorMap* map, const void* base, uint64_t rows128, uint32
   return cached_tmap(map, base, rows128, 128, box_rows, 1);
 }
 
+int make_tmap_narrow_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                        uint32_t box_rows) {
+  return cached_tmap(map, base, rows, row_bytes, box_rows, 3);
+}
+
 namespace {
 int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                    uint32_t box_rows, int flavour) {
   const bool bf16 = flavour == 2;
-  const bool swizzled = flavour != 1;
+  const bool swizzled = flavour == 0 || flavour == 2;
+  const cuuint32_t box_bytes = flavour == 3 ? 32u : 128u;
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return MSC_ERR_CUDA;
   if (reinterpret_cast<uintptr_t>(base) % 16 || row_bytes % 16)
     return fail(MSC_ERR_BAD_ARG, "operand base and row pitch must be 16-byte aligned");
   if (box_rows == 0 || box_rows > 256) return fail(MSC_ERR_BAD_ARG, "box rows out of range");
-  // the box is always 128 bytes wide: 128 byte elements or 64 bf16 elements
+  // the box is 128 bytes wide (128 byte elements or 64 bf16 elements), 32 for the narrow flavour
   cuuint64_t dims[2] = {bf16 ? row_bytes / 2 : row_bytes, rows};
   cuuint64_t strides[1] = {row_bytes};
-  cuuint32_t box[2] = {bf16 ? 64u : 128u, box_rows};
+  cuuint32_t box[2] = {bf16 ? 64u : box_bytes, box_rows};
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                    const_cast<void*>(base), dims, strides,

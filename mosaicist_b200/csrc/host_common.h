@@ -39,6 +39,11 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
 // (each 512-byte chunk is four such rows).
 int make_tmap_sf_2d(CUtensorMap* map, const void* base, uint64_t rows128, uint32_t box_rows);
 
+// 2-D byte tensor [rows][row_bytes] with a [box_rows][32 B] box, no swizzle (packed int4
+// weights: 64 K-elements of box_rows rows).
+int make_tmap_narrow_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                        uint32_t box_rows);
+
 // 2-D byte tensor [rows][row_bytes] whose rows are `pitch_bytes` apart, with a
 // [box_rows][128 B] box and 128-byte swizzle (operands and outputs of the dense GEMM, where a
 // shard of a larger matrix keeps the parent's pitch).

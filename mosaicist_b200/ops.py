@@ -292,11 +292,39 @@ def ragged_grouped_gemm_bf16(a, b, group_offsets, group_rows, alpha=None, out=No
 
 
 def mixed_grouped_gemm_int4(a, b_q, scales, group_offsets, group_rows, alpha=None, group_size: int = 128,
-                            workspace=None, out=None):
-    """bf16 activations x int4 weights: expands the weights to bf16 (`workspace`, (l, n, k) bf16,
-    reusable while the weights do not change) and runs the grouped bf16 GEMM."""
-    b = dequant_int4(b_q, scales, group_size, out=workspace)
-    return ragged_grouped_gemm_bf16(a, b, group_offsets, group_rows, alpha, out=out)
+                            workspace=None, out=None, fused: bool | None = None, max_ctas: int = 0):
+    """bf16 activations x int4 weights (ports/hopper_mixed_dtype_grouped_gemm/problems.py:75-87).
+
+    fused (default whenever k and group_size are multiples of 64): one kernel, converter warps
+    expand each stage of packed weights to bf16 in shared memory on their way to the tensor
+    core; the weights cross HBM once, as int4.  Otherwise two launches: expand the weights to
+    bf16 (`workspace`, (l, n, k) bf16, reusable while the weights do not change) and run the
+    grouped bf16 GEMM.  Both produce the same bits."""
+    _need(b_q, "b_q", (torch.uint8, torch.int8))
+    l, n, kh = b_q.shape
+    k = kh * 2
+    can_fuse = k % 64 == 0 and group_size % 64 == 0 and k % group_size == 0
+    if fused is None:
+        fused = can_fuse and workspace is None
+    if not fused:
+        b = dequant_int4(b_q, scales, group_size, out=workspace)
+        return ragged_grouped_gemm_bf16(a, b, group_offsets, group_rows, alpha, out=out, max_ctas=max_ctas)
+    if not can_fuse:
+        raise ValueError("the fused kernel needs k and group_size to be multiples of 64")
+    _need(a, "a", (torch.bfloat16,))
+    rows_total = a.shape[0]
+    _need(a, "a", (torch.bfloat16,), (rows_total, k))
+    _need(scales, "scales", (torch.bfloat16,), (l, n, k // group_size))
+    _need(group_offsets, "group_offsets", (torch.int32,), (l,))
+    _need(group_rows, "group_rows", (torch.int32,), (l,))
+    if alpha is not None:
+        _need(alpha, "alpha", (torch.float32,), (l,))
+    if out is None:
+        out = torch.empty((rows_total, n), dtype=torch.bfloat16, device=a.device)
+    _lib.check(_lib.load().msc_grouped_gemm_bf16_int4_ragged(
+        _ptr(a), _ptr(b_q), _ptr(scales), _ptr(alpha), _ptr(group_offsets), _ptr(group_rows), _ptr(out), l,
+        rows_total, n, k, group_size, max_ctas, _stream()))
+    return out
 
 
 def ragged_gemm1_swiglu_quantize(a_q, a_sf, w1_q, w1_sf, group_offsets, group_rows, alpha, out_global_scale,

@@ -44,7 +44,8 @@ def test_int4_dequant_bit_exact():
 
 @pytest.mark.parametrize("rows_list,n,k", [([128], 256, 128), ([64, 512, 0, 300, 17], 256, 1024),
                                            ([250, 1000, 16], 512, 384)])      # check_matrix.py ragged M
-def test_mixed_int4_exact(rows_list, n, k):
+@pytest.mark.parametrize("fused", [True, False], ids=["fused", "two_launches"])
+def test_mixed_int4_exact(rows_list, n, k, fused):
     from mosaicist_b200 import _lib, ops
 
     gsz = 128
@@ -57,7 +58,7 @@ def test_mixed_int4_exact(rows_list, n, k):
     alpha = np.exp2(rng.integers(-1, 2, l)).astype(np.float32)
     out = torch.full((tot, n), float("nan"), dtype=torch.bfloat16, device="cuda")
     ops.mixed_grouped_gemm_int4(_bf16_t(a), T(X.pack_int4(q)), _bf16_t(sc), T(np.array(offs, np.int32)),
-                                T(np.array(rows_list, np.int32)), T(alpha), gsz, out=out)
+                                T(np.array(rows_list, np.int32)), T(alpha), gsz, out=out, fused=fused)
     assert _lib.status_word() == 0
     want = X.ragged_gemm_f64(a, X.dequant(q, sc, gsz), offs, rows_list, alpha)
     # every partial sum is a multiple of 1/8 below 2^20: exact in fp32, so the only rounding
@@ -96,3 +97,28 @@ def test_mixed_int4_random_within_tolerance():
         lib_out = torch.matmul(at[o:o + r], bd[g_].T).float().cpu().numpy()
         rep = gate.compare_outputs(lib_out, got[o:o + r], ref[o:o + r], "bf16")
         assert rep.passed, rep.failures
+
+
+@pytest.mark.parametrize("gsz,k", [(128, 1024), (64, 448), (256, 1536)])
+def test_fused_int4_kernel_equals_the_two_launch_path(gsz, k):
+    """Random activations, the full int4 range and arbitrary scales: the in-kernel expansion
+    (converter warps writing the swizzled bf16 tile) must give the bits of the separate
+    expansion kernel followed by the bf16 grouped GEMM."""
+    from mosaicist_b200 import _lib, ops
+
+    rows_list, n = [300, 0, 129, 512, 7], 512
+    l = len(rows_list)
+    offs, tot = _layout(rows_list)
+    g = torch.Generator(device="cuda").manual_seed(k)
+    a = torch.randn((tot, k), device="cuda", generator=g).bfloat16()
+    bq = torch.randint(0, 256, (l, n, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+    sc = (torch.randn((l, n, k // gsz), device="cuda", generator=g) * 0.05).bfloat16()
+    alpha = torch.rand((l,), device="cuda", generator=g) + 0.5
+    o_t, r_t = T(np.array(offs, np.int32)), T(np.array(rows_list, np.int32))
+    one = torch.full((tot, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    two = torch.full((tot, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.mixed_grouped_gemm_int4(a, bq, sc, o_t, r_t, alpha, gsz, out=one, fused=True)
+    ops.mixed_grouped_gemm_int4(a, bq, sc, o_t, r_t, alpha, gsz, out=two, fused=False)
+    assert _lib.status_word() == 0
+    assert torch.equal(one.view(torch.int16), two.view(torch.int16))       # NaN rows compare as bits
+    assert int(torch.isnan(one).sum()) == (tot - sum(rows_list)) * n
