@@ -285,10 +285,30 @@ int msc_peer_free(void* ptr);
 /* counts_all (world, experts_total) i32: pairs each rank routes to each expert.  Writes
  * send_base (experts_total): the first row of this rank's pairs of expert e in the owner's
  * buffers (owner's 128-aligned group offset + the pairs of lower ranks), and this rank's own
- * group table group_rows / group_offsets (experts_total / world), total_rows (1). */
+ * group table group_rows / group_offsets (experts_total / world), total_rows (1).  With
+ * wait_flags (or NULL) the kernel first waits for the peers' flags of wait_slot to reach
+ * wait_epoch (see msc_ep_wait): the counts were written by the peers' msc_ep_signal. */
 int msc_ep_offsets(const int32_t* counts_all, int world, int rank, int experts_total, int rows_cap,
                    int32_t* send_base, int32_t* group_rows, int32_t* group_offsets,
-                   int32_t* total_rows, void* stream);
+                   int32_t* total_rows, const int32_t* wait_flags, int wait_slot, int wait_epoch,
+                   void* stream);
+
+/* Signalling between ranks without a collective.  Every rank owns a flag table of 4 slots x 16
+ * ints (zero at start) in memory its peers have mapped.  msc_ep_signal raises this rank's flag
+ * of `slot` to `epoch` on every peer (peer_flags: host array of `world` table pointers) after a
+ * system-scope fence; launched after the kernels whose peer-memory writes it announces, it
+ * makes them visible to a peer that then sees the flag.  With `counts` (experts_total) i32 it
+ * first copies them into row `rank` of every peer's counts table (peer_counts_all: host array
+ * of pointers to (world, experts_total) i32) - the all-gather of the per-expert counts.
+ * msc_ep_wait (or msc_ep_offsets with wait_flags) waits until all `world` flags of `slot` in
+ * this rank's own table have reached `epoch`: a bounded spin on local memory (one second), after
+ * which bit 0x00D00000 is raised in the status word and the kernel returns.  Epochs must
+ * increase from call to call.  Never run a wait before the matching signals when several
+ * ranks share one GPU: launches of one device do not overlap reliably. */
+int msc_ep_signal(int32_t* const* peer_flags, int world, int rank, int slot, int epoch,
+                  const int32_t* counts, int32_t* const* peer_counts_all, int experts_total,
+                  void* stream);
+int msc_ep_wait(const int32_t* flags, int world, int slot, int epoch, void* stream);
 
 /* msc_moe_permute_quantize across ranks: pair (token, k) with global expert e is quantised with
  * input_gs[e] (experts_total) and stored at row send_base[e] + rank_in_group[pair] of rank

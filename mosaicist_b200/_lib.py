@@ -60,7 +60,9 @@ SIGNATURES = {
     "msc_peer_open": (_I, [_P, ctypes.POINTER(ctypes.c_void_p)]),
     "msc_peer_close": (_I, [_P]),
     "msc_peer_free": (_I, [_P]),
-    "msc_ep_offsets": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "msc_ep_offsets": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _P]),
+    "msc_ep_signal": (_I, [_P, _I, _I, _I, _I, _P, _P, _I, _P]),
+    "msc_ep_wait": (_I, [_P, _I, _I, _I, _P]),
     "msc_ep_dispatch_quantize": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P]),
     "msc_ep_sum_pairs": (_I, [_P, _P, _I, _I, _I, _P]),
     "msc_grouped_gemm_nvfp4_scatter_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _CFG, _P]),

@@ -47,6 +47,8 @@ def main():
     ap.add_argument("--cta-pair", type=int, default=0)
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer")
+    ap.add_argument("--sync", choices=["flags", "nccl"], default="flags",
+                    help="peer exchange: synchronise through flags in peer memory / NCCL collectives")
     ap.add_argument("--combine", choices=["push", "pull"], default="push",
                     help="peer exchange: GEMM2 scatters result rows to the home ranks / the home rank pulls them")
     args = ap.parse_args()
@@ -88,8 +90,10 @@ def main():
     else:
         rows_cap = (2 * T_loc * k + 127 * E_loc + 127) // 128 * 128
         push = args.combine == "push"
-        bufs = PeerBuffers(rows_cap, h, T_loc * k if push else 0)
+        bufs = PeerBuffers(rows_cap, h, T_loc * k if push else 0, E)
         extra = dict(row_dest=bufs.tensors["row_dest"], recv_y=bufs.tensors["recv_y"]) if push else {}
+        if args.sync == "flags":
+            extra.update(flags=bufs.tensors["flags"], counts_all=bufs.tensors["counts_all"])
         inner = MegaMoE(*w, gs_in, gs_a2, topk=1, max_tokens=1, expert_first=rank * E_loc, config=cfg,
                         rows_cap=rows_cap, workspace=bufs.tensors)
         gs_all = torch.full((E,), 2688.0 / 5.0, dtype=torch.float32, device=dev)
@@ -125,7 +129,7 @@ def main():
                       (f"ep{world}, all-to-all bf16 dispatch + combine" if args.exchange == "nccl" else
                        f"ep{world}, NVFP4 dispatch into peer memory, bf16 results " +
                        ("scattered to the home rank by the GEMM2 epilogue" if args.combine == "push" else
-                        "pulled from peer memory"))}}
+                        "pulled from peer memory") + f", sync by {args.sync}")}}
 
     if world == 1:
         # per-stage device times on one GPU
@@ -168,14 +172,29 @@ def main():
     if world > 1 and args.exchange == "peer":
         # device time of each phase on this rank (waiting for slower ranks shows up in the barriers)
         L = layer
-        phases = [("route_count", lambda: L.count(logits)),
-                  ("allgather_counts", lambda: dist.all_gather_into_tensor(L.counts_all, L.counts)),
-                  ("place", lambda: L.place(L.counts_all)),
-                  ("dispatch", lambda: L.dispatch(tokens)),
-                  ("barrier_rows_landed", lambda: dist.all_reduce(L._flag)),
-                  ("experts", L.experts),
-                  ("barrier_results_ready", lambda: dist.all_reduce(L._flag)),
-                  ("combine", L.combine)]
+        from .parallel import SLOT_COUNTS, SLOT_RESULTS_READY, SLOT_ROWS_LANDED
+
+        def bump():
+            L.epoch += 1
+
+        if args.sync == "flags":
+            phases = [("route_count", lambda: (bump(), L.count(logits))),
+                      ("publish_counts", lambda: L.signal(SLOT_COUNTS, with_counts=True)),
+                      ("place", lambda: L.place(wait=True)),
+                      ("dispatch", lambda: L.dispatch(tokens)),
+                      ("barrier_rows_landed", lambda: (L.signal(SLOT_ROWS_LANDED), L.wait(SLOT_ROWS_LANDED))),
+                      ("experts", L.experts),
+                      ("barrier_results_ready", lambda: (L.signal(SLOT_RESULTS_READY), L.wait(SLOT_RESULTS_READY))),
+                      ("combine", L.combine)]
+        else:
+            phases = [("route_count", lambda: L.count(logits)),
+                      ("allgather_counts", lambda: dist.all_gather_into_tensor(L.counts_all, L.counts)),
+                      ("place", lambda: L.place(L.counts_all)),
+                      ("dispatch", lambda: L.dispatch(tokens)),
+                      ("barrier_rows_landed", lambda: dist.all_reduce(L._flag)),
+                      ("experts", L.experts),
+                      ("barrier_results_ready", lambda: dist.all_reduce(L._flag)),
+                      ("combine", L.combine)]
         acc = {name: 0.0 for name, _ in phases}
         reps = 5
         for _ in range(reps):

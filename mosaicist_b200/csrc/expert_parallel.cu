@@ -27,19 +27,95 @@ namespace msc {
 constexpr int kMaxPeers = 16;
 constexpr uint32_t kStatusEpOverflow = 0x00E00000u;   // a destination row beyond rows_cap
 
+// ---- signalling between ranks ----------------------------------------------------------------
+// Each rank owns a small table of flags, 16 per slot, one per peer, that only the peers write
+// (monotonically increasing epochs) and only the owner reads.  A signal is a system-scope
+// release store into every peer's table after a system fence; it is launched after the kernels
+// whose peer-memory writes it announces, so those writes have completed.  A wait spins, with a
+// time limit, on the owner's own memory; nothing here blocks on another GPU's progress without
+// that limit, and a wait that gives up raises a status bit and returns.
+constexpr uint32_t kStatusEpWaitTimeout = 0x00D00000u;
+constexpr int kFlagSlots = 4;   // a flag table is kFlagSlots x kMaxPeers ints
+constexpr long long kEpWaitBudgetNs = 1000000000LL;   // one second
+
+__device__ __forceinline__ void flag_store_release_sys(int* addr, int value) {
+  asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(addr), "r"(value) : "memory");
+}
+__device__ __forceinline__ int flag_load_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Lanes below `world` each wait for one peer's flag of `slot` to reach `epoch`; true if all did.
+__device__ __forceinline__ bool wait_for_peers(const int* flags, int world, int slot, int epoch,
+                                               uint32_t* status) {
+  bool ok = true;
+  if ((int)threadIdx.x < world) {
+    const int* f = flags + slot * kMaxPeers + threadIdx.x;
+    const unsigned long long t0 = global_timer_ns();
+    while (flag_load_acquire_sys(f) < epoch) {
+      if ((long long)(global_timer_ns() - t0) > kEpWaitBudgetNs) {
+        atomicOr(status, kStatusEpWaitTimeout);
+        ok = false;
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  return ok;
+}
+
+struct EpSignalParams {
+  int* flags[kMaxPeers];        // every rank's flag table
+  int* counts_all[kMaxPeers];   // every rank's (world, experts_total) table, or null entries
+  const int* counts;            // this rank's (experts_total) counts, or null
+  int world, rank, slot, epoch, experts_total;
+};
+
+// Optionally copies this rank's per-expert counts into row `rank` of every peer's table, then
+// raises this rank's flag of `slot` on every peer.
+__global__ void __launch_bounds__(256) ep_signal_kernel(const EpSignalParams p) {
+  if (p.counts) {
+    for (int i = threadIdx.x; i < p.world * p.experts_total; i += blockDim.x) {
+      const int peer = i / p.experts_total, e = i - peer * p.experts_total;
+      p.counts_all[peer][(size_t)p.rank * p.experts_total + e] = __ldg(p.counts + e);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < p.world)
+    flag_store_release_sys(p.flags[threadIdx.x] + p.slot * kMaxPeers + p.rank, p.epoch);
+}
+
+__global__ void __launch_bounds__(32)
+ep_wait_kernel(const int* flags, int world, int slot, int epoch, uint32_t* status) {
+  wait_for_peers(flags, world, slot, epoch, status);
+}
+
 // ---- offsets ---------------------------------------------------------------------------------
 // counts_all[s][e]: pairs rank s routes to global expert e.  One block computes, for every
 // expert, the first row this rank's pairs take in the owner's buffers (the owner's 128-aligned
 // group offset plus the pairs of lower ranks), and this rank's own group table.
 __global__ void __launch_bounds__(256)
-ep_offsets_kernel(const int* __restrict__ counts_all, int world, int rank, int experts_total,
+ep_offsets_kernel(const int* counts_all, int world, int rank, int experts_total,
                   int experts_local, int rows_cap, int* __restrict__ send_base,
                   int* __restrict__ group_rows, int* __restrict__ group_offsets,
-                  int* __restrict__ total_rows, uint32_t* __restrict__ status) {
+                  int* __restrict__ total_rows, uint32_t* __restrict__ status,
+                  const int* wait_flags, int wait_slot, int wait_epoch) {
   extern __shared__ int aligned_total[];   // experts_total entries
+  if (wait_flags) {   // the counts arrive from the peers: wait for all of them to be published
+    wait_for_peers(wait_flags, world, wait_slot, wait_epoch, status);
+    __syncthreads();
+  }
   for (int e = threadIdx.x; e < experts_total; e += blockDim.x) {
     int total = 0;
-    for (int s = 0; s < world; ++s) total += __ldg(counts_all + (size_t)s * experts_total + e);
+    for (int s = 0; s < world; ++s) total += __ldcg(counts_all + (size_t)s * experts_total + e);
     aligned_total[e] = (total + 127) & ~127;
   }
   __syncthreads();
@@ -49,7 +125,7 @@ ep_offsets_kernel(const int* __restrict__ counts_all, int world, int rank, int e
     for (int j = owner * experts_local; j < e; ++j) off += aligned_total[j];
     int before = 0, total = 0;
     for (int s = 0; s < world; ++s) {
-      const int c = __ldg(counts_all + (size_t)s * experts_total + e);
+      const int c = __ldcg(counts_all + (size_t)s * experts_total + e);
       if (s < rank) before += c;
       total += c;
     }
@@ -332,7 +408,8 @@ int msc_peer_free(void* ptr) {
 
 int msc_ep_offsets(const int32_t* counts_all, int world, int rank, int experts_total, int rows_cap,
                    int32_t* send_base, int32_t* group_rows, int32_t* group_offsets,
-                   int32_t* total_rows, void* stream) {
+                   int32_t* total_rows, const int32_t* wait_flags, int wait_slot, int wait_epoch,
+                   void* stream) {
   if (!counts_all || !send_base || !group_rows || !group_offsets || !total_rows)
     return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
   int rc = msc::check_world(world, experts_total);
@@ -340,11 +417,13 @@ int msc_ep_offsets(const int32_t* counts_all, int world, int rank, int experts_t
   if (rank < 0 || rank >= world) return msc::fail(MSC_ERR_BAD_ARG, "rank=%d outside [0, %d)", rank, world);
   if (experts_total > 8192) return msc::fail(MSC_ERR_UNSUPPORTED, "experts_total=%d exceeds 8192", experts_total);
   if (rows_cap <= 0 || rows_cap % 128) return msc::fail(MSC_ERR_BAD_ARG, "rows_cap=%d must be a positive multiple of 128", rows_cap);
+  if (wait_flags && (wait_slot < 0 || wait_slot >= msc::kFlagSlots))
+    return msc::fail(MSC_ERR_BAD_ARG, "slot=%d outside [0, %d)", wait_slot, msc::kFlagSlots);
   uint32_t* status = reinterpret_cast<uint32_t*>(msc::status_word());
   if (!status) return MSC_ERR_CUDA;
   msc::ep_offsets_kernel<<<1, 256, experts_total * sizeof(int), static_cast<cudaStream_t>(stream)>>>(
       counts_all, world, rank, experts_total, experts_total / world, rows_cap, send_base, group_rows,
-      group_offsets, total_rows, status);
+      group_offsets, total_rows, status, wait_flags, wait_slot, wait_epoch);
   MSC_CUDA_OK(cudaGetLastError());
   return MSC_OK;
 }
@@ -420,6 +499,44 @@ int msc_ep_combine(const void* const* peer_y, const int32_t* ids, const int32_t*
   const long long blocks = (units + 255) / 256;
   if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
   msc::ep_combine_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+int msc_ep_signal(int32_t* const* peer_flags, int world, int rank, int slot, int epoch,
+                  const int32_t* counts, int32_t* const* peer_counts_all, int experts_total,
+                  void* stream) {
+  if (!peer_flags) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (world < 1 || world > msc::kMaxPeers)
+    return msc::fail(MSC_ERR_UNSUPPORTED, "world=%d must be in [1, %d]", world, msc::kMaxPeers);
+  if (rank < 0 || rank >= world) return msc::fail(MSC_ERR_BAD_ARG, "rank=%d outside [0, %d)", rank, world);
+  if (slot < 0 || slot >= msc::kFlagSlots)
+    return msc::fail(MSC_ERR_BAD_ARG, "slot=%d outside [0, %d)", slot, msc::kFlagSlots);
+  if (counts && (!peer_counts_all || experts_total <= 0))
+    return msc::fail(MSC_ERR_BAD_ARG, "counts need peer_counts_all and experts_total");
+  msc::EpSignalParams p;
+  for (int r = 0; r < msc::kMaxPeers; ++r) {
+    if (r < world && (!peer_flags[r] || (counts && !peer_counts_all[r])))
+      return msc::fail(MSC_ERR_BAD_ARG, "NULL buffer for rank %d", r);
+    p.flags[r] = r < world ? peer_flags[r] : nullptr;
+    p.counts_all[r] = (r < world && counts) ? peer_counts_all[r] : nullptr;
+  }
+  p.counts = counts;
+  p.world = world; p.rank = rank; p.slot = slot; p.epoch = epoch; p.experts_total = experts_total;
+  msc::ep_signal_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+int msc_ep_wait(const int32_t* flags, int world, int slot, int epoch, void* stream) {
+  if (!flags) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (world < 1 || world > msc::kMaxPeers)
+    return msc::fail(MSC_ERR_UNSUPPORTED, "world=%d must be in [1, %d]", world, msc::kMaxPeers);
+  if (slot < 0 || slot >= msc::kFlagSlots)
+    return msc::fail(MSC_ERR_BAD_ARG, "slot=%d outside [0, %d)", slot, msc::kFlagSlots);
+  uint32_t* status = reinterpret_cast<uint32_t*>(msc::status_word());
+  if (!status) return MSC_ERR_CUDA;
+  msc::ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, slot, epoch, status);
   MSC_CUDA_OK(cudaGetLastError());
   return MSC_OK;
 }

@@ -144,16 +144,19 @@ class _DeviceBytes:
                                          "version": 3, "strides": None}
 
 
-EXCHANGE_BUFFERS = ("a_q", "sf_rows", "row_weight", "y", "row_dest", "recv_y")
+EXCHANGE_BUFFERS = ("a_q", "sf_rows", "row_weight", "y", "row_dest", "recv_y", "flags", "counts_all")
+FLAG_SLOTS, FLAG_PEERS = 4, 16     # a flag table: slots x peers int32 (msc_ep_signal / msc_ep_wait)
+SLOT_COUNTS, SLOT_ROWS_LANDED, SLOT_RESULTS_READY = 0, 1, 2
 
 
-def exchange_layout(rows_cap: int, hidden: int, pairs_cap: int = 0):
+def exchange_layout(rows_cap: int, hidden: int, pairs_cap: int = 0, world: int = 0, experts_total: int = 0):
     """Byte offsets of the EXCHANGE_BUFFERS inside one rank's exchange allocation, and its total
     size.  Sections start on 1 KB boundaries (TMA maps and bulk copies need 16 bytes).
     pairs_cap = tokens * topk this rank may route: the rows of recv_y, where the other ranks'
-    second GEMM delivers this rank's results (0: no such buffer, the combine pulls from y)."""
+    second GEMM delivers this rank's results (0: no such buffer, the combine pulls from y).
+    world * experts_total sizes the table the peers write their per-expert counts into."""
     sizes = (rows_cap * (hidden // 2), rows_cap * (hidden // 16), rows_cap * 4, rows_cap * hidden * 2,
-             rows_cap * 4, pairs_cap * hidden * 2)
+             rows_cap * 4, pairs_cap * hidden * 2, FLAG_SLOTS * FLAG_PEERS * 4, world * experts_total * 4)
     offs, at = [], 0
     for n in sizes:
         offs.append(at)
@@ -161,9 +164,10 @@ def exchange_layout(rows_cap: int, hidden: int, pairs_cap: int = 0):
     return offs, at
 
 
-def exchange_views(base: torch.Tensor, rows_cap: int, hidden: int, pairs_cap: int = 0) -> dict:
+def exchange_views(base: torch.Tensor, rows_cap: int, hidden: int, pairs_cap: int = 0, world: int = 0,
+                   experts_total: int = 0) -> dict:
     """The buffers as tensors over a flat uint8 allocation laid out by exchange_layout."""
-    offs, total = exchange_layout(rows_cap, hidden, pairs_cap)
+    offs, total = exchange_layout(rows_cap, hidden, pairs_cap, world, experts_total)
     if base.dtype != torch.uint8 or base.numel() < total:
         raise ValueError(f"need a uint8 allocation of at least {total} bytes")
 
@@ -177,6 +181,8 @@ def exchange_views(base: torch.Tensor, rows_cap: int, hidden: int, pairs_cap: in
         "y": cut(3, rows_cap * hidden * 2).view(torch.bfloat16).view(rows_cap, hidden),
         "row_dest": cut(4, rows_cap * 4).view(torch.int32),
         "recv_y": cut(5, pairs_cap * hidden * 2).view(torch.bfloat16).view(pairs_cap, hidden),
+        "flags": cut(6, FLAG_SLOTS * FLAG_PEERS * 4).view(torch.int32),
+        "counts_all": cut(7, world * experts_total * 4).view(torch.int32).view(world, experts_total),
     }
 
 
@@ -188,7 +194,7 @@ class PeerBuffers:
     combine),
     `pointers[name][r]` is rank r's buffer as seen from this process."""
 
-    def __init__(self, rows_cap: int, hidden: int, pairs_cap: int = 0, group=None):
+    def __init__(self, rows_cap: int, hidden: int, pairs_cap: int = 0, experts_total: int = 0, group=None):
         import ctypes
 
         from . import _lib
@@ -196,7 +202,7 @@ class PeerBuffers:
         lib = _lib.load()
         self.group, self.rows_cap, self.hidden = group, rows_cap, hidden
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        offs, total = exchange_layout(rows_cap, hidden, pairs_cap)
+        offs, total = exchange_layout(rows_cap, hidden, pairs_cap, self.world, experts_total)
         ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
         _lib.check(lib.msc_peer_alloc(total, ctypes.byref(ptr), handle))
         self._own, self._opened = ptr.value, []
@@ -214,7 +220,7 @@ class PeerBuffers:
         dev = torch.device("cuda", torch.cuda.current_device())
         flat = torch.as_tensor(_DeviceBytes(self._own, total), device=dev)
         flat.zero_()
-        self.tensors = exchange_views(flat, rows_cap, hidden, pairs_cap)
+        self.tensors = exchange_views(flat, rows_cap, hidden, pairs_cap, self.world, experts_total)
         self.tensors["row_dest"].fill_(-1)
         self.pointers = {name: [b + offs[i] for b in bases] for i, name in enumerate(EXCHANGE_BUFFERS)}
         dist.barrier(group=group)   # every rank has zeroed its buffers before anyone writes
@@ -248,12 +254,16 @@ class PeerExpertParallelMoE:
     on one device (each phase for every rank before the next phase)."""
 
     def __init__(self, layer, pointers: dict, sf_rows, input_gs_all, experts_total: int, topk: int,
-                 max_tokens: int, rank: int, world: int, group=None, row_dest=None, recv_y=None):
+                 max_tokens: int, rank: int, world: int, group=None, row_dest=None, recv_y=None,
+                 flags=None, counts_all=None):
         """With `row_dest` (rows_cap,) i32 and `recv_y` (>= max_tokens * topk, h) bf16 — this
         rank's buffers of those names, whose addresses on every rank are in `pointers` — the
         combine is pushed: the second GEMM scatters each result row into the home rank's recv_y
         while it runs, and `combine` only sums k local rows per token.  Without them `combine`
-        pulls the rows from the owners' y after the GEMM."""
+        pulls the rows from the owners' y after the GEMM.
+        With `flags` and `counts_all` (this rank's buffers of those names) the ranks synchronise
+        through flags in each other's memory (msc_ep_signal / msc_ep_wait) and exchange the
+        counts the same way; without them `forward` uses an NCCL all-gather and two all-reduces."""
         import ctypes
 
         if experts_total % world:
@@ -289,7 +299,17 @@ class PeerExpertParallelMoE:
         self.rank_in_group = torch.zeros((T, K), **i32)
         self.pair_row = torch.full((T, K), -1, **i32)
         self.counts = torch.zeros((experts_total,), **i32)
-        self.counts_all = torch.zeros((world, experts_total), **i32)
+        self.flag_sync = flags is not None
+        if self.flag_sync:
+            if counts_all is None or tuple(counts_all.shape) != (world, experts_total):
+                raise ValueError("counts_all must be this rank's (world, experts_total) exchange table")
+            if flags.data_ptr() != pointers["flags"][rank] or counts_all.data_ptr() != pointers["counts_all"][rank]:
+                raise ValueError("flags / counts_all are not the buffers the other ranks were given")
+            self.flags, self.counts_all = flags, counts_all
+            self._fl, self._ca = arr(*pointers["flags"]), arr(*pointers["counts_all"])
+            self.epoch = 0
+        else:
+            self.counts_all = torch.zeros((world, experts_total), **i32)
         self.send_base = torch.zeros((experts_total,), **i32)
         self._tmp = torch.zeros((experts_total + 8,), **i32)
         self._scratch = torch.zeros((4,), **i32)
@@ -318,15 +338,34 @@ class PeerExpertParallelMoE:
                                     self._scratch.data_ptr(), st))
         return self.counts
 
-    def place(self, counts_all):
-        """From all ranks' counts: where this rank's pairs go, and this rank's group table."""
+    def signal(self, slot: int, with_counts: bool = False):
+        """Raises this rank's flag of `slot` on every rank (after publishing its counts)."""
+        from . import _lib
+
+        _lib.check(_lib.load().msc_ep_signal(self._fl, self.world, self.rank, slot, self.epoch,
+                                             self.counts.data_ptr() if with_counts else None,
+                                             self._ca if with_counts else None, self.E, self._stream()))
+
+    def wait(self, slot: int):
+        """Waits (bounded) until every rank has raised its flag of `slot` for this layer call."""
+        from . import _lib
+
+        _lib.check(_lib.load().msc_ep_wait(self.flags.data_ptr(), self.world, slot, self.epoch, self._stream()))
+
+    def place(self, counts_all=None, wait: bool = False):
+        """From all ranks' counts: where this rank's pairs go, and this rank's group table.
+        wait=True (flag synchronisation): the kernel first waits for every rank's counts."""
         from . import _lib
 
         L = self.layer
+        if counts_all is None:
+            counts_all = self.counts_all
         _lib.check(_lib.load().msc_ep_offsets(counts_all.data_ptr(), self.world, self.rank, self.E,
                                               self.rows_cap, self.send_base.data_ptr(),
                                               L.group_rows.data_ptr(), L.group_offsets.data_ptr(),
-                                              L.total_rows.data_ptr(), self._stream()))
+                                              L.total_rows.data_ptr(),
+                                              self.flags.data_ptr() if wait else None, SLOT_COUNTS,
+                                              self.epoch if wait else 0, self._stream()))
 
     def dispatch(self, tokens):
         from . import _lib
@@ -375,6 +414,17 @@ class PeerExpertParallelMoE:
     def forward(self, tokens, logits, out=None):
         """tokens (T_local, h) bf16, logits (T_local, experts_total) f32 -> (T_local, h) bf16."""
         self.count(logits)
+        if self.flag_sync:
+            self.epoch += 1
+            self.signal(SLOT_COUNTS, with_counts=True)
+            self.place(wait=True)
+            self.dispatch(tokens)
+            self.signal(SLOT_ROWS_LANDED)
+            self.wait(SLOT_ROWS_LANDED)         # every rank's rows have landed
+            self.experts()
+            self.signal(SLOT_RESULTS_READY)
+            self.wait(SLOT_RESULTS_READY)       # every rank's results are complete
+            return self.combine(out)
         dist.all_gather_into_tensor(self.counts_all, self.counts, group=self.group)
         self.place(self.counts_all)
         self.dispatch(tokens)

@@ -122,8 +122,8 @@ def run_workload():
     rows_cap = (T2 * k + 127 * el + 127) // 128 * 128
     for push in (False, True):
         pairs_cap = T2 // 2 * k if push else 0
-        _, total = exchange_layout(rows_cap, hid, pairs_cap)
-        spaces = [exchange_views(torch.zeros(total, dtype=torch.uint8, device=dev), rows_cap, hid, pairs_cap)
+        _, total = exchange_layout(rows_cap, hid, pairs_cap, world, E)
+        spaces = [exchange_views(torch.zeros(total, dtype=torch.uint8, device=dev), rows_cap, hid, pairs_cap, world, E)
                   for _ in range(world)]
         ptrs = {nm: [s[nm].data_ptr() for s in spaces] for nm in EXCHANGE_BUFFERS}
         ranks = []

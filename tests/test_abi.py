@@ -158,13 +158,13 @@ def test_expert_parallel_entry_points_reject_bad_arguments(lib):
 
     one = ctypes.c_void_p(256)
     two = (ctypes.c_void_p * 2)(256, 256)
-    rc = lib.msc_ep_offsets(one, 3, 0, 32, 1024, one, one, one, one, None)
+    rc = lib.msc_ep_offsets(one, 3, 0, 32, 1024, one, one, one, one, None, 0, 0, None)
     assert rc == _lib.ERR_BAD_ARG and b"do not split" in lib.msc_last_error()
-    rc = lib.msc_ep_offsets(one, 2, 2, 32, 1024, one, one, one, one, None)
+    rc = lib.msc_ep_offsets(one, 2, 2, 32, 1024, one, one, one, one, None, 0, 0, None)
     assert rc == _lib.ERR_BAD_ARG and b"rank=2" in lib.msc_last_error()
-    rc = lib.msc_ep_offsets(one, 2, 0, 32, 1000, one, one, one, one, None)
+    rc = lib.msc_ep_offsets(one, 2, 0, 32, 1000, one, one, one, one, None, 0, 0, None)
     assert rc == _lib.ERR_BAD_ARG and b"rows_cap" in lib.msc_last_error()
-    rc = lib.msc_ep_offsets(one, 17, 0, 34, 1024, one, one, one, one, None)
+    rc = lib.msc_ep_offsets(one, 17, 0, 34, 1024, one, one, one, one, None, 0, 0, None)
     assert rc == _lib.ERR_UNSUPPORTED and b"world=17" in lib.msc_last_error()
     rc = lib.msc_ep_dispatch_quantize(one, one, one, one, one, one, 8, 100, 2, 32, 2, two, two, two, None, 0,
                                       1024, one, None)
@@ -183,5 +183,13 @@ def test_expert_parallel_entry_points_reject_bad_arguments(lib):
     rc = lib.msc_grouped_gemm_nvfp4_scatter_ragged(one, one, one, one, None, one, one, None, one, two, 17, 4, 512,
                                                    256, 256, cfg, None)
     assert rc == _lib.ERR_UNSUPPORTED and b"dest_count=17" in lib.msc_last_error()
+    rc = lib.msc_ep_offsets(one, 2, 0, 32, 1024, one, one, one, one, one, 9, 1, None)
+    assert rc == _lib.ERR_BAD_ARG and b"slot=9" in lib.msc_last_error()
+    rc = lib.msc_ep_signal(two, 2, 0, 4, 1, None, None, 0, None)
+    assert rc == _lib.ERR_BAD_ARG and b"slot=4" in lib.msc_last_error()
+    rc = lib.msc_ep_signal(two, 2, 0, 1, 1, one, None, 32, None)
+    assert rc == _lib.ERR_BAD_ARG and b"counts need" in lib.msc_last_error()
+    rc = lib.msc_ep_wait(None, 2, 0, 1, None)
+    assert rc == _lib.ERR_BAD_ARG
     rc = lib.msc_peer_alloc(0, ctypes.byref(ctypes.c_void_p()), ctypes.create_string_buffer(64))
     assert rc == _lib.ERR_BAD_ARG

@@ -101,8 +101,10 @@ def _peer_worker(rank, world, port, q, push):
                  w2_sf=T(O.e4m3_bytes(O.retile(w["w2_sf"]))), w2_gs=T(w["w2_gs"]), w2_alpha=T(w["w2_alpha"]))
         sl = slice(rank * E_loc, (rank + 1) * E_loc)
         rows_cap = (world * T_loc * k + 127 * E_loc + 127) // 128 * 128
-        bufs = PeerBuffers(rows_cap, h, T_loc * k if push else 0)
+        bufs = PeerBuffers(rows_cap, h, T_loc * k if push else 0, E)
         extra = dict(row_dest=bufs.tensors["row_dest"], recv_y=bufs.tensors["recv_y"]) if push else {}
+        if push:     # the pushed combine also runs on flag synchronisation, the pulled one on NCCL
+            extra.update(flags=bufs.tensors["flags"], counts_all=bufs.tensors["counts_all"])
         local = MegaMoE(d["w1_q"][sl], d["w1_sf"][sl], d["w1_gs"][sl], d["w1_alpha"][sl], d["w2_q"][sl],
                         d["w2_sf"][sl], d["w2_gs"][sl], d["w2_alpha"][sl], T(input_gs[sl]), T(a2_gs[sl]),
                         topk=1, max_tokens=1, expert_first=rank * E_loc, rows_cap=rows_cap,

@@ -15,15 +15,15 @@ from tests.test_moe_gpu import T, _dev_weights, _weights
 pytestmark = pytest.mark.gpu
 
 
-def _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs, push=False):
+def _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs, push=False, flags=False):
     from mosaicist_b200.moe import MegaMoE
     from mosaicist_b200.parallel import EXCHANGE_BUFFERS, PeerExpertParallelMoE, exchange_layout, exchange_views
 
     el = E // world
     d = _dev_weights(w)
     pairs_cap = T_loc * k if push else 0
-    _, total = exchange_layout(rows_cap, h, pairs_cap)
-    spaces = [exchange_views(torch.zeros(total, dtype=torch.uint8, device="cuda"), rows_cap, h, pairs_cap)
+    _, total = exchange_layout(rows_cap, h, pairs_cap, world, E)
+    spaces = [exchange_views(torch.zeros(total, dtype=torch.uint8, device="cuda"), rows_cap, h, pairs_cap, world, E)
               for _ in range(world)]
     pointers = {name: [s[name].data_ptr() for s in spaces] for name in EXCHANGE_BUFFERS}
     ranks = []
@@ -33,29 +33,55 @@ def _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs, push=False):
                         d["w2_sf"][sl], d["w2_gs"][sl], d["w2_alpha"][sl], T(input_gs[sl]), T(a2_gs[sl]),
                         topk=1, max_tokens=1, expert_first=r * el, rows_cap=rows_cap, workspace=spaces[r])
         extra = dict(row_dest=spaces[r]["row_dest"], recv_y=spaces[r]["recv_y"]) if push else {}
+        if flags:
+            extra.update(flags=spaces[r]["flags"], counts_all=spaces[r]["counts_all"])
         ranks.append(PeerExpertParallelMoE(layer, pointers, spaces[r]["sf_rows"], T(input_gs), E, k, T_loc, r,
                                            world, **extra))
     return ranks
 
 
 def _lockstep(ranks, tokens, logits):
+    """One layer call of every rank, phase by phase.  With flag synchronisation every rank's
+    signal of a phase is launched before any rank's wait for it, so no wait ever spins."""
+    from mosaicist_b200.parallel import SLOT_COUNTS, SLOT_RESULTS_READY, SLOT_ROWS_LANDED
+
+    flags = ranks[0].flag_sync
     for ep, lg in zip(ranks, logits):
         ep.count(lg)
-    counts_all = torch.stack([ep.counts for ep in ranks]).contiguous()
-    for ep in ranks:
-        ep.place(counts_all)
+    if flags:
+        for ep in ranks:
+            ep.epoch += 1
+            ep.signal(SLOT_COUNTS, with_counts=True)
+        for ep in ranks:
+            ep.place(wait=True)
+        counts_all = ranks[0].counts_all.clone()
+    else:
+        counts_all = torch.stack([ep.counts for ep in ranks]).contiguous()
+        for ep in ranks:
+            ep.place(counts_all)
     for ep, tk in zip(ranks, tokens):
         ep.dispatch(tk)
+    if flags:
+        for ep in ranks:
+            ep.signal(SLOT_ROWS_LANDED)
+        for ep in ranks:
+            ep.wait(SLOT_ROWS_LANDED)
     for ep in ranks:
         ep.experts()
+    if flags:
+        for ep in ranks:
+            ep.signal(SLOT_RESULTS_READY)
+        for ep in ranks:
+            ep.wait(SLOT_RESULTS_READY)
     return [ep.combine() for ep in ranks], counts_all
 
 
+@pytest.mark.parametrize("flags", [False, True], ids=["collectives", "flags"])
 @pytest.mark.parametrize("push", [False, True], ids=["pull", "push"])
 @pytest.mark.parametrize("world,E,k,h,n,T_loc", [(2, 32, 2, 256, 128, 160), (4, 32, 4, 512, 256, 96),
                                                   (8, 64, 8, 256, 128, 40),
                                                   (2, 32, 3, 384, 128, 70)])   # h % 256 != 0: store dispatch
-def test_emulated_ranks_equal_single_gpu_layer(world, E, k, h, n, T_loc, push):
+def test_emulated_ranks_equal_single_gpu_layer(world, E, k, h, n, T_loc, push, flags):
     if push and h % 256:
         pytest.skip("the row-scatter GEMM needs n % 256 == 0")
     from mosaicist_b200 import _lib
@@ -69,7 +95,7 @@ def test_emulated_ranks_equal_single_gpu_layer(world, E, k, h, n, T_loc, push):
     input_gs = np.where(np.arange(E) % 3 == 0, 2688.0 / 4.0, 2688.0 / 5.0).astype(np.float32)
     a2_gs = np.full(E, 2688.0 / 4.0, np.float32)
     rows_cap = (world * T_loc * k + 127 * (E // world) + 127) // 128 * 128
-    ranks = _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs, push)
+    ranks = _layers(world, E, k, h, n, T_loc, rows_cap, w, input_gs, a2_gs, push, flags)
     tk = [T(np.asarray(t, np.float32)).to(torch.bfloat16) for t in tokens]
     lg = [T(l) for l in logits]
     for _ in range(2):                                     # buffers are reusable as they are
@@ -124,3 +150,23 @@ def test_overflowing_rank_drops_rows_and_raises_the_status_bit():
         dest = M.ep_placement(ca, r)[0][ids] + ep.rank_in_group[:T_loc].cpu().numpy()
         assert np.array_equal(rows, np.where(dest < 128, dest, -1))     # dropped pairs are marked
         assert (rows == -1).any()
+
+
+def test_wait_without_signal_times_out_and_reports():
+    """A flag nobody raises: the wait gives up after its limit, sets the status bit, and the
+    context stays usable (the next kernel runs)."""
+    import time
+
+    from mosaicist_b200 import _lib
+
+    lib = _lib.load()
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    t0 = time.perf_counter()
+    _lib.check(lib.msc_ep_wait(flags.data_ptr(), 2, 1, 1, st))
+    torch.cuda.synchronize()
+    took = time.perf_counter() - t0
+    assert 0.5 < took < 10.0
+    assert _lib.status_word() & 0x00D00000
+    assert int((flags + 1).sum()) == 64          # the device still answers
+    assert _lib.status_word() == 0
