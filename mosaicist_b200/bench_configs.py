@@ -82,6 +82,43 @@ def headline_vs_flashinfer(reps):
             "bitwise_equal_fraction": float((y == y_ref).float().mean())}
 
 
+def masked_moe_path(reps):
+    """The masked MoE path at the shape the reference times end to end (l=8 experts, m=512 rows,
+    k=2048 hidden, n=1024 intermediate: quantise, GEMM1 + SiLU*up + quantise, GEMM2), warm, as
+    the reference times it (sum of kernel times, L2 warm): here one CUDA graph of 20 layers."""
+    from . import ops
+    from .candidates import cand_cuda_moe as cand
+    from .moe import moe_masked
+
+    from .moe import fold_alphas
+
+    args = cand._inputs()
+    (hidden, w1_q, w1_sf, w1_gs, w1_alpha, w2_q, w2_sf, w2_gs, w2_alpha, masked_m, in_gs, a2_gs) = args
+    folded = fold_alphas(w1_gs, w1_alpha, w2_gs, w2_alpha, in_gs, a2_gs)
+    us_layer = _time_graph(lambda: moe_masked(*args, folded_alphas=folded), reps=reps)
+    us_fused = _time_graph(lambda: moe_masked(*args, folded_alphas=folded, fuse_gemm1=True), reps=reps)
+    # the four kernels one by one, for the sum the reference quotes
+    a_q, a_sf = ops.quantize_nvfp4(hidden, in_gs, masked_m)
+    gateup = ops.masked_grouped_gemm(a_q, a_sf, w1_q, w1_sf, folded[0], masked_m)
+    d_q, d_sf = ops.silu_mul_quantize_nvfp4(gateup, a2_gs, masked_m)
+    y = torch.empty_like(hidden)
+    parts = {
+        "quantize": _time_graph(lambda: ops.quantize_nvfp4(hidden, in_gs, masked_m), reps=reps),
+        "gemm1": _time_graph(lambda: ops.masked_grouped_gemm(a_q, a_sf, w1_q, w1_sf, folded[0], masked_m, out=gateup),
+                             reps=reps),
+        "silu_mul_quantize": _time_graph(lambda: ops.silu_mul_quantize_nvfp4(gateup, a2_gs, masked_m), reps=reps),
+        "gemm2": _time_graph(lambda: ops.masked_grouped_gemm(d_q, d_sf, w2_q, w2_sf, folded[1], masked_m, out=y),
+                             reps=reps),
+    }
+    fl = 2.0 * cand.L * cand.M * (cand.K * 2 * cand.N + cand.N * cand.K)
+    return {"config": "masked MoE path l=8 m=512 k=2048 n=1024 (quantise, GEMM1, SiLU*up+quantise, GEMM2), warm",
+            "us_layer_graph_of_20": us_layer, "tflops": fl / us_layer / 1e6, "us_sum_of_kernels": sum(parts.values()),
+            "us_per_kernel": parts, "us_layer_with_fused_gemm1": us_fused,
+            "reference_flashinfer_us_sum_of_kernels": 46.0,
+            "reference_per_kernel_us": {"quantize": 10.9, "gemm1": 13.4, "silu_mul_quantize": 8.7, "gemm2": 9.4},
+            "reference_pallas_port_us": 60.8}
+
+
 def _layout(rows):
     offs, tot = [], 0
     for r in rows:
@@ -116,6 +153,8 @@ def main():
     out = []
     if args.vs_flashinfer and rank == 0:
         out.append(headline_vs_flashinfer(args.reps))
+    if rank == 0:
+        out.append(masked_moe_path(args.reps))
 
     # C2: dense fp16, this rank's column shard
     n = 8192

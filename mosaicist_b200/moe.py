@@ -19,17 +19,51 @@ import torch
 from . import _lib, ops
 
 
+_OFFSETS = {}
+
+
+def _masked_offsets(l: int, m: int, device) -> torch.Tensor:
+    """Row offsets g * m of a padded (l, m, ...) batch seen as row-concatenated groups."""
+    key = (l, m, str(device))
+    if key not in _OFFSETS:
+        _OFFSETS[key] = (torch.arange(l, dtype=torch.int32, device=device) * m).contiguous()
+    return _OFFSETS[key]
+
+
+def fold_alphas(w1_gs, w1_alpha, w2_gs, w2_alpha, input_global_scale, a2_global_scale):
+    """alpha_eff = alpha / (gs_activation * gs_weight) for the two GEMMs (moe.py:14-16)."""
+    return ((w1_alpha / (input_global_scale * w1_gs)).contiguous(),
+            (w2_alpha / (a2_global_scale * w2_gs)).contiguous())
+
+
 def moe_masked(hidden, w1_q, w1_sf, w1_gs, w1_alpha, w2_q, w2_sf, w2_gs, w2_alpha, masked_m,
                input_global_scale, a2_global_scale, gemm1_config=ops.GemmConfig(),
-               gemm2_config=ops.GemmConfig()):
+               gemm2_config=ops.GemmConfig(), fuse_gemm1: bool | None = None, folded_alphas=None):
     """(l, m, k) bf16 in, (l, m, k) bf16 out; rows >= masked_m[l] are left untouched.
     Same arguments as the reference's moe_masked: w1_q (l, 2n, k/2), w1_sf / w2_sf in the MMA
-    tiling, w2_q (l, k, n/2), per-expert global scales and alphas (l,) f32."""
+    tiling, w2_q (l, k, n/2), per-expert global scales and alphas (l,) f32.
+    fuse_gemm1: GEMM1, SiLU(gate) * up and the requantisation run as one kernel, as the
+    reference's fused variant does (gemm1_silu_quantize.py:94); bit-identical to the three-kernel
+    form.  Default: when 2n % 256 == 0 and k >= 4096 — the activation and quantiser arithmetic
+    in the epilogue hides under a long main loop, at k = 2048 it costs what the separate kernel
+    costs.  folded_alphas = fold_alphas(...) skips the four small elementwise kernels that fold
+    the global scales into the GEMM alphas (they only depend on the weights and scales)."""
     a_q, a_sf = ops.quantize_nvfp4(hidden, input_global_scale, masked_m)
-    g1_alpha = (w1_alpha / (input_global_scale * w1_gs)).contiguous()
-    gateup = ops.masked_grouped_gemm(a_q, a_sf, w1_q, w1_sf, g1_alpha, masked_m, gemm1_config)
-    d_q, d_sf = ops.silu_mul_quantize_nvfp4(gateup, a2_global_scale, masked_m)
-    g2_alpha = (w2_alpha / (a2_global_scale * w2_gs)).contiguous()
+    g1_alpha, g2_alpha = folded_alphas if folded_alphas is not None else fold_alphas(
+        w1_gs, w1_alpha, w2_gs, w2_alpha, input_global_scale, a2_global_scale)
+    l, m_rows, kh = a_q.shape
+    n2 = w1_q.shape[1]
+    if fuse_gemm1 is None:
+        fuse_gemm1 = n2 % 256 == 0 and kh * 2 >= 4096
+    if fuse_gemm1:
+        d_q, d_sf = ops.ragged_gemm1_swiglu_quantize(
+            a_q.view(l * m_rows, kh), a_sf.view(l * (m_rows // 128), *a_sf.shape[2:]), w1_q, w1_sf,
+            _masked_offsets(l, m_rows, a_q.device), masked_m, g1_alpha, a2_global_scale, gemm1_config)
+        d_q = d_q.view(l, m_rows, n2 // 4)
+        d_sf = d_sf.view(l, m_rows // 128, *d_sf.shape[1:])
+    else:
+        gateup = ops.masked_grouped_gemm(a_q, a_sf, w1_q, w1_sf, g1_alpha, masked_m, gemm1_config)
+        d_q, d_sf = ops.silu_mul_quantize_nvfp4(gateup, a2_global_scale, masked_m)
     return ops.masked_grouped_gemm(d_q, d_sf, w2_q, w2_sf, g2_alpha, masked_m, gemm2_config)
 
 

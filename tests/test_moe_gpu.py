@@ -178,12 +178,20 @@ def test_moe_masked_matches_reference_layer(l, m, k, n):
                                       w["w2_q"], w["w2_sf"], w["w2_gs"], w["w2_alpha"], masked_m,
                                       in_gs, a2_gs), np.float32)
     d = _dev_weights(w)
-    got = moe_masked(T(np.asarray(hidden, np.float32)).to(torch.bfloat16), d["w1_q"], d["w1_sf"],
-                     d["w1_gs"], d["w1_alpha"], d["w2_q"], d["w2_sf"], d["w2_gs"], d["w2_alpha"],
-                     T(masked_m), T(in_gs), T(a2_gs))
+    args = (T(np.asarray(hidden, np.float32)).to(torch.bfloat16), d["w1_q"], d["w1_sf"],
+            d["w1_gs"], d["w1_alpha"], d["w2_q"], d["w2_sf"], d["w2_gs"], d["w2_alpha"],
+            T(masked_m), T(in_gs), T(a2_gs))
+    from mosaicist_b200.moe import fold_alphas
+
+    got = moe_masked(*args, fuse_gemm1=True)             # GEMM1 + SiLU*up + quantise in one kernel
+    folded = fold_alphas(d["w1_gs"], d["w1_alpha"], d["w2_gs"], d["w2_alpha"], T(in_gs), T(a2_gs))
+    three = moe_masked(*args, fuse_gemm1=False, folded_alphas=folded)     # the three-kernel form
     assert _lib.status_word() == 0
     rows = np.arange(m)[None, :, None] < masked_m[:, None, None]
     _close(np.where(rows, got.float().cpu().numpy(), 0), want)
+    rows_t = torch.from_numpy(np.broadcast_to(rows, (l, m, k)).copy()).cuda()
+    assert torch.equal(torch.where(rows_t, got, torch.zeros_like(got)),
+                       torch.where(rows_t, three, torch.zeros_like(three)))
 
 
 @pytest.mark.parametrize("T_,E,k,h,n,first,local", [(256, 32, 4, 256, 128, 0, 32),
