@@ -133,6 +133,68 @@ def cpu_baseline(host_ops, budget_s: float = 12.0, max_passes: int = 20):
                       f"(median {med * 1e3:.0f} ms per pass, BLAS threads = all cores)"}
 
 
+def cpu_baselines_other_configs():
+    """`--cpu-baseline-configs`: the CPU oracle (numpy float64, BLAS on all host cores) timed on a
+    stated sub-shape of the other benchmark configurations (dense fp16, MXFP8 grouped, bf16 x int4
+    grouped, MoE layer); throughput in TFLOP/s, so a full-size time follows by proportion.  One
+    JSON line per configuration, next to what `python -m mosaicist_b200.bench_configs` and
+    `bench_moe` measure on the GPU."""
+    import ml_dtypes
+    import numpy as np
+
+    from oracle import mixed_int4 as X4, moe as OM, mxfp8 as X8, nvfp4 as O4
+
+    cores = os.cpu_count()
+    rng = np.random.default_rng(11)
+    res = []
+
+    def timed(fn, reps=3):
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return sorted(ts)[len(ts) // 2]
+
+    # C2: 1/64 of the 8192^3 problem (m and n cut to 1024, full k), fp16 operands, float64 product
+    a = (rng.standard_normal((1024, 8192)) / 8192 ** 0.5).astype(np.float16)
+    bm = (rng.standard_normal((8192, 1024)) / 8192 ** 0.5).astype(np.float16)
+    t = timed(lambda: a.astype(np.float64) @ bm.astype(np.float64))
+    res.append({"config": "C2 dense fp16", "cpu_tflops": 2.0 * 1024 * 8192 * 1024 / t / 1e12, "cores": cores,
+                "kind": "port", "sample": f"1024 x 8192 x 1024 sub-shape (1/64 of the FLOPs), median of 3: {t:.3f} s"})
+    # C3: two groups of 256 rows at n = 1024, full k = 7168 (1/128 of the FLOPs)
+    rows, k, n = [256, 256], 7168, 1024
+    aq, asf = X8.quantize_mxfp8(rng.standard_normal((512, k)).astype(np.float32))
+    bq, bsf = X8.quantize_mxfp8(rng.standard_normal((2 * n, k)).astype(np.float32))
+    t = timed(lambda: X8.ragged_grouped_gemm_f64(aq, asf, bq.reshape(2, n, k), bsf.reshape(2, n, -1), [0, 256], rows))
+    res.append({"config": "C3 MXFP8 grouped", "cpu_tflops": 2.0 * 512 * n * k / t / 1e12, "cores": cores, "kind": "port",
+                "sample": f"2 groups x 256 rows, n=1024, k=7168 (1/128 of the FLOPs), median of 3: {t:.3f} s"})
+    # C4: two groups of 256 rows at n = 512, full k (dequantise + float64 product)
+    q = rng.integers(-8, 8, (2, 512, k)).astype(np.int8)
+    sc = np.abs(rng.standard_normal((2, 512, k // 128)) * 0.02).astype(np.float32).astype(ml_dtypes.bfloat16)
+    x = rng.standard_normal((512, k)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    t = timed(lambda: X4.ragged_gemm_f64(x, X4.dequant(q, sc, 128), [0, 256], rows))
+    res.append({"config": "C4 bf16 x int4 grouped", "cpu_tflops": 2.0 * 512 * 512 * k / t / 1e12, "cores": cores,
+                "kind": "port", "sample": f"2 groups x 256 rows, n=512, k=7168, median of 3: {t:.3f} s"})
+    # C5: the routed layer on 64 tokens, 8 experts, top-2, hidden 1024, intermediate 512
+    T_, E, kk, h, ni = 64, 8, 2, 1024, 512
+    w1 = (rng.standard_normal((E, 2 * ni, h)) * 0.05).astype(np.float32)
+    w2 = (rng.standard_normal((E, h, ni)) * 0.05).astype(np.float32)
+    w1_gs, w2_gs = O4.global_scale_for(w1), O4.global_scale_for(w2)
+    w1_q, w1_sf = O4.quantize_nvfp4(w1, w1_gs)
+    w2_q, w2_sf = O4.quantize_nvfp4(w2, w2_gs)
+    tok = rng.standard_normal((T_, h)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    ids, wts = OM.route_topk(rng.standard_normal((T_, E)).astype(np.float32), kk)
+    one = np.ones(E, np.float32)
+    gs_in, gs_a2 = np.full(E, 2688.0 / 5, np.float32), np.full(E, 2688.0 / 4, np.float32)
+    t = timed(lambda: OM.routed_moe(tok, ids, wts, w1_q, w1_sf, w1_gs, one, w2_q, w2_sf, w2_gs, one, gs_in, gs_a2, 0),
+              reps=1)
+    res.append({"config": "C5 MegaMoE layer", "cpu_tflops": 2.0 * T_ * kk * (h * 2 * ni + ni * h) / t / 1e12,
+                "cores": cores, "kind": "port",
+                "sample": f"64 tokens, 8 experts, top-2, hidden 1024, intermediate 512, one pass: {t:.3f} s"})
+    return res
+
+
 def host_operands_numpy(seed: int):
     """Operand set for the CPU arm, quantised by the oracle itself (no GPU involved)."""
     import numpy as np
@@ -186,7 +248,13 @@ def main():
     ap.add_argument("--cta-pair", type=int, default=0, help="0 auto, 1 CTA pairs, 2 single CTA")
     ap.add_argument("--e2e-steps", type=int, default=30)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-baseline-configs", action="store_true",
+                    help="only time the CPU oracle on sub-shapes of the other configurations and exit")
     args = ap.parse_args()
+    if args.cpu_baseline_configs:
+        for row in cpu_baselines_other_configs():
+            print(json.dumps(row), flush=True)
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

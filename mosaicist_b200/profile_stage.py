@@ -9,11 +9,13 @@ src/mosaicist/backends/cuda.py).  This stage fills that slot for the kernels of 
 
 1. runs the workload once without the profiler (`--run`, this same module) and stops unless it
    exits 0;
-2. runs it again under `ncu --clock-control none` with seven named metrics (duration, DRAM
-   bytes read / written, DRAM and tensor-pipe utilisation, registers, active warps), limited to
-   this library's kernels and `--launches` launches;
-3. folds the CSV into one table row per kernel: launches, average duration, DRAM GB/s
-   (bytes / duration), DRAM % of peak, tensor pipe % of peak, registers per thread.
+2. runs it again under `ncu --clock-control none` with named metrics (duration, DRAM bytes
+   read / written, L2 -> SM bytes, DRAM and tensor-pipe utilisation, registers, active warps,
+   ten warp-stall reasons), limited to this library's kernels and `--launches` launches;
+3. folds the CSV into one row per kernel: launches, average duration, DRAM GB/s (bytes /
+   duration), DRAM % of peak, tensor pipe % of peak, registers per thread, the three largest
+   stall reasons (warps stalled per issue-active cycle) - as a markdown table and, with
+   `--json`, as one JSON object per kernel (the "machine" rows a capture bundle can carry).
 
 The workload is sized for a capture that ends by itself within a couple of minutes: operand
 sets of 0.1 - 1.5 GB (larger than L2, so DRAM figures mean something), one to three launches per
@@ -40,7 +42,11 @@ METRICS = [
     "sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_elapsed",
     "launch__registers_per_thread",
     "sm__warps_active.avg.pct_of_peak_sustained_active",
+    "l1tex__m_xbar2l1tex_read_bytes.sum",
 ]
+STALLS = ["long_scoreboard", "barrier", "wait", "short_scoreboard", "math_pipe_throttle", "mio_throttle",
+          "lg_throttle", "sleeping", "membar", "branch_resolving"]
+STALL_METRICS = [f"smsp__average_warps_issue_stalled_{name}_per_issue_active.ratio" for name in STALLS]
 KERNEL_FILTER = "regex:gemm_|quantize|swizzle|moe_|ep_|route_|int4_"
 
 
@@ -152,8 +158,8 @@ def run_workload():
         raise RuntimeError("a kernel reported an error status")
 
 
-def summarise(csv_text: str) -> str:
-    """ncu's --csv log (one row per launch and metric) -> markdown table per kernel."""
+def kernel_rows(csv_text: str) -> list[dict]:
+    """ncu's --csv log (one row per launch and metric) -> one dict per kernel, slowest first."""
     lines = csv_text.splitlines()
     start = next(i for i, ln in enumerate(lines) if ln.startswith('"ID"'))
     per = {}   # kernel -> launch id -> metric -> value
@@ -163,18 +169,34 @@ def summarise(csv_text: str) -> str:
         unit = row["Metric Unit"]
         if row["Metric Name"] == "gpu__time_duration.sum":
             val *= {"ns": 1e-3, "us": 1.0, "ms": 1e3, "s": 1e6}.get(unit, 1.0)          # -> us
-        if row["Metric Name"].startswith("dram__bytes"):
+        if "bytes" in row["Metric Name"]:
             val *= {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}.get(unit, 1.0)  # -> bytes
         per.setdefault(name, {}).setdefault(row["ID"], {})[row["Metric Name"]] = val
-    out = ["| kernel | launches | avg us | DRAM read MB | DRAM write MB | DRAM GB/s | DRAM % peak | tensor pipe % | regs | warps active % |",
-           "|---|---|---|---|---|---|---|---|---|---|"]
+    rows = []
     for name, launches in sorted(per.items(), key=lambda kv: -sum(m.get(METRICS[0], 0) for m in kv[1].values())):
         n = len(launches)
         avg = lambda key: sum(m.get(key, 0.0) for m in launches.values()) / n
         us, rd, wr = avg(METRICS[0]), avg(METRICS[1]), avg(METRICS[2])
-        gbs = (rd + wr) / (us * 1e-6) / 1e9 if us > 0 else 0.0
-        out.append(f"| {name} | {n} | {us:.1f} | {rd / 1e6:.2f} | {wr / 1e6:.2f} | {gbs:.0f} | {avg(METRICS[3]):.1f} | "
-                   f"{avg(METRICS[4]):.1f} | {avg(METRICS[5]):.0f} | {avg(METRICS[6]):.1f} |")
+        stalls = sorted(((avg(m), nm) for m, nm in zip(STALL_METRICS, STALLS)), reverse=True)
+        rows.append({"kernel": name, "launches": n, "avg_us": us, "dram_read_bytes": rd, "dram_write_bytes": wr,
+                     "dram_gbs": (rd + wr) / (us * 1e-6) / 1e9 if us > 0 else 0.0,
+                     "dram_pct_of_peak": avg(METRICS[3]), "tensor_pipe_pct_of_peak": avg(METRICS[4]),
+                     "registers_per_thread": avg(METRICS[5]), "warps_active_pct": avg(METRICS[6]),
+                     "l2_to_sm_bytes": avg(METRICS[7]),
+                     "top_stalls": [{"reason": nm, "warps_per_issue_active": v} for v, nm in stalls[:3] if v > 0]})
+    return rows
+
+
+def summarise(csv_text: str) -> str:
+    """The per-kernel rows as a markdown table."""
+    out = ["| kernel | launches | avg us | DRAM read MB | DRAM write MB | DRAM GB/s | DRAM % peak | tensor pipe % | regs | warps active % | L2->SM MB | top stalls (warps per issue-active cycle) |",
+           "|---|---|---|---|---|---|---|---|---|---|---|---|"]
+    for r in kernel_rows(csv_text):
+        stalls = ", ".join(f"{t['reason']} {t['warps_per_issue_active']:.1f}" for t in r["top_stalls"])
+        out.append(f"| {r['kernel']} | {r['launches']} | {r['avg_us']:.1f} | {r['dram_read_bytes'] / 1e6:.2f} | "
+                   f"{r['dram_write_bytes'] / 1e6:.2f} | {r['dram_gbs']:.0f} | {r['dram_pct_of_peak']:.1f} | "
+                   f"{r['tensor_pipe_pct_of_peak']:.1f} | {r['registers_per_thread']:.0f} | {r['warps_active_pct']:.1f} | "
+                   f"{r['l2_to_sm_bytes'] / 1e6:.1f} | {stalls} |")
     return "\n".join(out)
 
 
@@ -183,6 +205,7 @@ def main():
     ap.add_argument("--run", action="store_true", help="only launch the workload (what gets profiled)")
     ap.add_argument("--out", default="profiles/kernels_small_cases.md")
     ap.add_argument("--launches", type=int, default=80)
+    ap.add_argument("--json", default=None, help="also write the per-kernel rows as JSON lines to this file")
     ap.add_argument("--csv", default=None, help="summarise an existing ncu CSV log instead of profiling")
     ap.add_argument("--raw", default=str(pathlib.Path(tempfile.gettempdir()) / "profile_stage.csv"),
                     help="where ncu's CSV log goes")
@@ -191,7 +214,7 @@ def main():
         run_workload()
         return
     cmd = [sys.executable, "-m", "mosaicist_b200.profile_stage", "--run"]
-    ncu_cmd = ["ncu", "--clock-control", "none", "--metrics", ",".join(METRICS), "-k", KERNEL_FILTER,
+    ncu_cmd = ["ncu", "--clock-control", "none", "--metrics", ",".join(METRICS + STALL_METRICS), "-k", KERNEL_FILTER,
                "-c", str(args.launches), "--print-units", "base", "--csv", "--log-file", args.raw, *cmd]
     if args.csv is None:
         if shutil.which("ncu") is None:
@@ -203,6 +226,10 @@ def main():
     else:
         text = pathlib.Path(args.csv).read_text()
     table = summarise(text)
+    if args.json:
+        import json
+
+        pathlib.Path(args.json).write_text("".join(json.dumps(r) + "\n" for r in kernel_rows(text)))
     body = ("# Every kernel of the library under Nsight Compute, small cases\n\n"
             "Made by `python -m mosaicist_b200.profile_stage` (plain run first, then\n`"
             + " ".join(ncu_cmd[:-len(cmd)]) + " <same command>`).\n"

@@ -139,17 +139,24 @@ def test_profile_stage_summary_table():
 
     head = '"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size","Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"'
     rows = ["==PROF== Connected to process 1", head]
-    vals = {0: [10000, 4_000_000, 1_000_000, 50.0, 30.0, 153, 15.0], 1: [30000, 8_000_000, 2_000_000, 60.0, 40.0, 153, 17.0],
-            2: [5000, 1_000_000, 0, 10.0, 0.0, 32, 80.0]}
+    vals = {0: [10000, 4_000_000, 1_000_000, 50.0, 30.0, 153, 15.0, 70_000_000],
+            1: [30000, 8_000_000, 2_000_000, 60.0, 40.0, 153, 17.0, 90_000_000],
+            2: [5000, 1_000_000, 0, 10.0, 0.0, 32, 80.0, 0]}
     names = {0: "gemm_pair_kernel<0, 5, 0, 0>(CUtensorMap)", 1: "gemm_pair_kernel<0, 5, 0, 0>(CUtensorMap)",
              2: "moe_plan_kernel(const int *)"}
-    units = ["ns", "byte", "byte", "%", "%", "register/thread", "%"]
+    units = ["ns", "byte", "byte", "%", "%", "register/thread", "%", "byte"]
     for i, v in vals.items():
         for m, u, x in zip(METRICS, units, v):
             rows.append(f'"{i}","1","python","host","{names[i]}","1","7","(320, 1, 1)","(148, 1, 1)","0","10.0","Command line profiler metrics","{m}","{u}","{x}"')
+    for i in (0, 1):
+        rows.append(f'"{i}","1","python","host","{names[i]}","1","7","(320, 1, 1)","(148, 1, 1)","0","10.0","Command line profiler metrics","smsp__average_warps_issue_stalled_barrier_per_issue_active.ratio","","2.5"')
     table = summarise("\n".join(rows)).splitlines()
-    assert table[2].startswith("| gemm_pair_kernel<0, 5, 0, 0> | 2 | 20.0 | 6.00 | 1.50 | 375 | 55.0 | 35.0 | 153 | 16.0 |")
+    assert table[2].startswith("| gemm_pair_kernel<0, 5, 0, 0> | 2 | 20.0 | 6.00 | 1.50 | 375 | 55.0 | 35.0 | 153 | 16.0 | 80.0 |")
     assert table[3].startswith("| moe_plan_kernel | 1 | 5.0 | 1.00 | 0.00 | 200 |")
+    from mosaicist_b200.profile_stage import kernel_rows
+
+    rows_ = kernel_rows("\n".join(rows))
+    assert rows_[0]["top_stalls"][0] == {"reason": "barrier", "warps_per_issue_active": 2.5}
 
 
 def test_expert_parallel_entry_points_reject_bad_arguments(lib):
