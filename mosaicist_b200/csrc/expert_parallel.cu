@@ -283,7 +283,9 @@ __global__ void __launch_bounds__(256) ep_dispatch_bulk_kernel(const EpDispatchP
   // the block may retire once the copies have read the row; the writes themselves are complete
   // when the grid is, which is what the next operation in the stream (the barrier) waits for
   if (threadIdx.x == 0) bulk_wait_group_read0();
-  __threadfence_system();   // the scalar stores of the first warp went to other GPUs too
+  // only the first warp stored to other GPUs with plain stores (a system fence in every thread
+  // was the kernel's largest stall under the profiler)
+  if (threadIdx.x < 32) __threadfence_system();
 }
 
 // ---- combine ---------------------------------------------------------------------------------
