@@ -205,7 +205,8 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchParams
     if (valid && (kb & 3) == 0)
       *reinterpret_cast<uint32_t*>(p.sf[owner] + (size_t)dest * kblocks + kb) = word;
   }
-  __threadfence_system();   // the stores went to other GPUs: order them before the kernel ends
+  // no fence here: the stores are complete when the grid is, and what announces them to the
+  // other ranks (a signal kernel or a collective) is launched after this grid in the stream
 }
 
 // The same dispatch with the rows leaving as bulk copies: one block per token quantises the
