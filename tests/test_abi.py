@@ -200,3 +200,19 @@ def test_expert_parallel_entry_points_reject_bad_arguments(lib):
     assert rc == _lib.ERR_BAD_ARG
     rc = lib.msc_peer_alloc(0, ctypes.byref(ctypes.c_void_p()), ctypes.create_string_buffer(64))
     assert rc == _lib.ERR_BAD_ARG
+
+
+def test_torch_custom_op_is_registered_and_shape_propagates():
+    """torch.ops.mosaicist_sm100a.grouped_gemm_nvfp4 exists after import and FakeTensor tracing
+    sees its output shape / dtype without a GPU."""
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    import mosaicist_b200.torch_ops  # noqa: F401
+
+    with FakeTensorMode():
+        u8 = dict(dtype=torch.uint8, device="cuda")
+        out = torch.ops.mosaicist_sm100a.grouped_gemm_nvfp4(
+            torch.empty((8, 512, 1024), **u8), torch.empty((8, 4, 32, 32, 16), **u8),
+            torch.empty((8, 2048, 1024), **u8), torch.empty((8, 16, 32, 32, 16), **u8), None, None)
+        assert tuple(out.shape) == (8, 512, 2048) and out.dtype == torch.bfloat16

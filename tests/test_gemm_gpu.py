@@ -240,3 +240,19 @@ def test_random_mxfp8_within_tolerance():
         ok, worst = O.tolerance_ok(got[o:o + r], ref[o:o + r])
         assert ok, worst
         assert gate.gate_bf16(got[o:o + r], ref[o:o + r]).passed
+
+
+def test_torch_custom_op_matches_direct_call():
+    import mosaicist_b200.torch_ops  # noqa: F401
+    from mosaicist_b200 import ops
+
+    l, m, n, k = 2, 256, 256, 512
+    g = torch.Generator(device="cuda").manual_seed(1)
+    u8 = lambda *s, lo=0, hi=256: torch.randint(lo, hi, s, dtype=torch.uint8, device="cuda", generator=g)
+    a_q, b_q = u8(l, m, k // 2), u8(l, n, k // 2)
+    a_sf, b_sf = u8(l, m // 128, k // 64, 32, 16, lo=0x30, hi=0x40), u8(l, n // 128, k // 64, 32, 16, lo=0x30, hi=0x40)
+    masked = torch.tensor([m, 77], dtype=torch.int32, device="cuda")
+    got = torch.ops.mosaicist_sm100a.grouped_gemm_nvfp4(a_q, a_sf, b_q, b_sf, None, masked)
+    want = ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, None, masked,
+                                   out=torch.zeros((l, m, n), dtype=torch.bfloat16, device="cuda"))
+    assert torch.equal(got, want) and int((got[1, 77:] != 0).sum()) == 0 and int((got[1, :77] != 0).sum()) > 0
