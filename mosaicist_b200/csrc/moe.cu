@@ -19,6 +19,8 @@ namespace msc {
 constexpr int kMaxExpertsPerLane = 32;  // experts <= 1024
 
 // ---- routing -----------------------------------------------------------------------------
+// PER: register slots per lane (experts / 32 rounded up to 8 or 32); unused slots hold -inf / -1.
+template <int PER>
 __global__ void __launch_bounds__(128)
 route_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights,
                   int tokens, int experts, int topk) {
@@ -27,10 +29,10 @@ route_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float
   if (warp >= tokens) return;
   const float* row = logits + (size_t)warp * experts;
   const int per = experts >> 5;
-  float v[kMaxExpertsPerLane];
+  float v[PER];
   float mx = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+  for (int i = 0; i < PER; ++i) {
     v[i] = (i < per) ? __ldg(row + lane + 32 * i) : -INFINITY;
     mx = fmaxf(mx, v[i]);
   }
@@ -38,7 +40,7 @@ route_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float
   for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   float sum = 0.0f;
 #pragma unroll
-  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+  for (int i = 0; i < PER; ++i) {
     v[i] = (i < per) ? expf(__fsub_rn(v[i], mx)) : -1.0f;   // -1 marks "not a candidate"
     if (i < per) sum = __fadd_rn(sum, v[i]);
   }
@@ -52,7 +54,7 @@ route_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float
     float best = -1.0f;
     int best_i = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    for (int i = 0; i < PER; ++i) {
       const int idx = lane + 32 * i;
       if (v[i] > best || (v[i] == best && v[i] >= 0.0f && idx < best_i)) {
         best = v[i];
@@ -71,7 +73,7 @@ route_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float
     // the owner of the winning entry retires it (ties go to the lower expert index)
     if ((best_i & 31) == lane) {
 #pragma unroll
-      for (int i = 0; i < kMaxExpertsPerLane; ++i)
+      for (int i = 0; i < PER; ++i)
         if (i == (best_i >> 5)) v[i] = -1.0f;
     }
     const float pk = __fdiv_rn(best, sum);
@@ -212,28 +214,45 @@ __global__ void __launch_bounds__(256) moe_permute_quantize_kernel(const Permute
   uint2 q8 = make_uint2(0u, 0u);
   uint32_t sfb = 0;
   float have_gs = -1.0f;   // global scales are positive: nothing is cached yet
-  for (int k = 0; k < p.topk; ++k) {   // trip count uniform over the warp: the shuffles converge
-    const long long entry = token * p.topk + k;
-    int e = -1;
-    if (live) e = __ldg(p.ids + entry) - p.expert_first;
-    const bool valid = e >= 0 && e < p.experts_local;   // uniform over the 4 lanes of a unit
-    int dest = 0;
-    if (valid) {
-      const float gs = __ldg(p.gs + e);
-      if (gs != have_gs) {
-        quantize_16(v, gs, q8, sfb);
-        have_gs = gs;
-      }
-      dest = __ldg(p.group_offsets + e) + __ldg(p.rank + entry);
-      *reinterpret_cast<uint2*>(p.q + (size_t)dest * (p.hidden >> 1) + kb * 8) = q8;
-      if (kb == 0) {
-        p.row_weight[dest] = __ldg(p.weights + entry);
-        p.row_token[dest] = (int)token;
+  // Experts are handled eight at a time: first every lookup of the batch (expert id, then its
+  // global scale, group offset and the pair's rank) is issued, so the dependent loads of the
+  // eight experts overlap instead of forming one chain per expert; then the rows are written.
+  constexpr int kBatch = 8;
+  for (int k0 = 0; k0 < p.topk; k0 += kBatch) {   // trip counts uniform over the warp
+    int dest[kBatch];
+    float gsv[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int k = k0 + j;
+      int e = -1;
+      if (live && k < p.topk) e = __ldg(p.ids + token * p.topk + k) - p.expert_first;
+      const bool valid = e >= 0 && e < p.experts_local;   // uniform over the 4 lanes of a unit
+      dest[j] = -1;
+      gsv[j] = 0.0f;
+      if (valid) {
+        gsv[j] = __ldg(p.gs + e);
+        dest[j] = __ldg(p.group_offsets + e) + __ldg(p.rank + token * p.topk + k);
       }
     }
-    const uint32_t word = gather_scale_word(sfb);
-    if (valid && (kb & 3) == 0)
-      *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word(dest, kb >> 2, kblocks >> 2)) = word;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (k0 + j >= p.topk) break;                        // uniform
+      const bool valid = dest[j] >= 0;
+      if (valid) {
+        if (gsv[j] != have_gs) {
+          quantize_16(v, gsv[j], q8, sfb);
+          have_gs = gsv[j];
+        }
+        *reinterpret_cast<uint2*>(p.q + (size_t)dest[j] * (p.hidden >> 1) + kb * 8) = q8;
+        if (kb == 0) {
+          p.row_weight[dest[j]] = __ldg(p.weights + token * p.topk + k0 + j);
+          p.row_token[dest[j]] = (int)token;
+        }
+      }
+      const uint32_t word = gather_scale_word(sfb);
+      if (valid && (kb & 3) == 0)
+        *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word(dest[j], kb >> 2, kblocks >> 2)) = word;
+    }
   }
 }
 
@@ -347,8 +366,12 @@ int msc_moe_route_topk(const float* logits, int32_t* ids, float* weights, int to
   if (topk < 1 || topk > 32 || topk > experts)
     return msc::fail(MSC_ERR_UNSUPPORTED, "topk=%d must be in [1, 32]", topk);
   const int blocks = (tokens + 3) / 4;
-  msc::route_topk_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      logits, ids, weights, tokens, experts, topk);
+  if (experts <= 256)
+    msc::route_topk_kernel<8><<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, ids, weights, tokens, experts, topk);
+  else
+    msc::route_topk_kernel<msc::kMaxExpertsPerLane><<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, ids, weights, tokens, experts, topk);
   MSC_CUDA_OK(cudaGetLastError());
   return MSC_OK;
 }

@@ -264,3 +264,39 @@ def test_fused_gemm1_swiglu_quantize_equals_two_kernel_path(rows_list, n, k):
     oq, osf = O.quantize_nvfp4(O.silu_mul(gu), a2_gs[g0:g0 + 1])
     sl = slice(offs[g0], offs[g0] + rows_list[g0])
     assert np.mean(gq[sl] == O.pack_e2m1(oq)[0]) > 0.99
+
+
+def test_megamoe_layer_replays_from_a_cuda_graph():
+    """The whole routed layer is stream-ordered launches without host synchronisation or
+    allocation (given `out`), so it captures into one CUDA graph; replays reproduce the eager
+    result for new inputs written into the captured buffers."""
+    from mosaicist_b200 import _lib
+    from mosaicist_b200.moe import MegaMoE
+
+    T_, E, k, h, n = 256, 32, 4, 512, 256
+    w = _weights(E, h, n, seed=77)
+    d = _dev_weights(w)
+    gs_in, gs_a2 = T(np.full(E, 2688.0 / 5.0, np.float32)), T(np.full(E, 2688.0 / 4.0, np.float32))
+    layer = MegaMoE(d["w1_q"], d["w1_sf"], d["w1_gs"], d["w1_alpha"], d["w2_q"], d["w2_sf"], d["w2_gs"],
+                    d["w2_alpha"], gs_in, gs_a2, topk=k, max_tokens=T_)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    tokens = torch.randn((T_, h), device="cuda", generator=g).bfloat16()
+    logits = torch.randn((T_, E), device="cuda", generator=g)
+    out = torch.empty((T_, h), dtype=torch.bfloat16, device="cuda")
+    layer.forward(tokens, logits, out=out)                     # warm-up: tensor maps, attributes
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            layer.forward(tokens, logits, out=out)
+    for seed in (6, 7):
+        g.manual_seed(seed)
+        tokens.copy_(torch.randn((T_, h), device="cuda", generator=g).bfloat16())
+        logits.copy_(torch.randn((T_, E), device="cuda", generator=g))
+        graph.replay()
+        torch.cuda.synchronize()
+        replayed = out.clone()
+        eager = layer.forward(tokens, logits)
+        assert torch.equal(replayed, eager) and int((eager != 0).sum()) > eager.numel() // 2
+    assert _lib.status_word() == 0
