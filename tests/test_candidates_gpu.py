@@ -56,3 +56,40 @@ def test_flashinfer_reference_kernel_on_identical_inputs():
     rep = gate.compare_outputs(theirs.float().cpu().numpy(), ours.float().cpu().numpy(), oracle, "bf16")
     assert rep.passed, rep.failures
     assert rep.bitwise_equal_fraction > 0.999
+
+
+@pytest.mark.parametrize("name,env,fmt", [("cand_cuda_dense", {"MOSAICIST_DENSE_DIM": "1024"}, "f16"),
+                                          ("cand_cuda_mxfp8", {"MOSAICIST_SHRINK": "8"}, "bf16"),
+                                          ("cand_cuda_int4", {"MOSAICIST_SHRINK": "8"}, "bf16")])
+def test_capture_modules_of_the_other_configurations(name, env, fmt, tmp_path, monkeypatch):
+    """Dense fp16, MXFP8 grouped and bf16 x int4 grouped as capture modules, at reduced size:
+    build() runs, a PTX lands in the dump directory, and the output is within the stated
+    tolerance of the module's float64 reference() and passes the numerics gate (reference arm:
+    the float64 opinion rounded to the output format)."""
+    import importlib
+
+    import torch
+
+    from mosaicist_b200 import _lib
+    from oracle import gate as G
+
+    monkeypatch.setenv("MOSAIC_GPU_DUMP_TO", str(tmp_path))
+    monkeypatch.delenv("MOSAICIST_KNOBS", raising=False)
+    for key, val in env.items():
+        monkeypatch.setenv(key, val)
+    m = importlib.reload(importlib.import_module(f"mosaicist_b200.candidates.{name}"))
+    fn, args = m.build()
+    got = fn(*args).float().cpu().numpy()
+    torch.cuda.synchronize()
+    assert _lib.status_word() == 0
+    assert list(tmp_path.rglob("*.ptx"))
+    ref = m.reference(*args)
+    assert got.shape == ref.shape and np.count_nonzero(ref) > ref.size // 4
+    ok, worst = O.tolerance_ok(got, ref)
+    assert ok, worst
+    arm = G.round_to_format(ref, fmt).astype(np.float32)
+    bad = np.abs(got.astype(np.float64) - ref) > np.abs(arm.astype(np.float64) - ref) * 4 + 1e-3 * np.sqrt(np.mean(ref ** 2))
+    assert bad.mean() < 1e-4      # almost everywhere within four roundings of the ideal arm
+    for key in env:
+        monkeypatch.delenv(key)
+    importlib.reload(m)            # leave the module at its full-size constants
