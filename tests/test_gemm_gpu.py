@@ -256,3 +256,48 @@ def test_torch_custom_op_matches_direct_call():
     want = ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, None, masked,
                                    out=torch.zeros((l, m, n), dtype=torch.bfloat16, device="cuda"))
     assert torch.equal(got, want) and int((got[1, 77:] != 0).sum()) == 0 and int((got[1, :77] != 0).sum()) > 0
+
+
+@pytest.mark.parametrize("rows_list,n,k", [([256], 256, 256), ([300, 0, 77, 512, 129], 512, 640)])
+def test_scatter_epilogue_equals_store_then_permute(rows_list, n, k):
+    """msc_grouped_gemm_nvfp4_scatter_ragged: every valid row lands, bit for bit, where its code
+    says - across two destination buffers, in a random order - rows coded negative are dropped,
+    and nothing else is written."""
+    import ctypes
+
+    from mosaicist_b200 import _lib, ops
+
+    rng = np.random.default_rng([9, n, k])
+    l = len(rows_list)
+    offs, tot = _ragged_layout(rows_list)
+    a_q, a_sf = O.exact_operands(rng, 1, tot, k)
+    b_q, b_sf = O.exact_operands(rng, l, n, k)
+    alpha = np.exp2(rng.integers(-1, 2, l)).astype(np.float32)
+    rs = np.exp2(rng.integers(-1, 2, tot)).astype(np.float32)
+    args = (T(O.pack_e2m1(a_q[0])), T(O.e4m3_bytes(O.to_mma_scale_layout(a_sf[0]))), T(O.pack_e2m1(b_q)),
+            T(O.e4m3_bytes(O.retile(b_sf))), T(np.array(offs, np.int32)), T(np.array(rows_list, np.int32)),
+            T(alpha), T(rs))
+    stored = torch.zeros((tot, n), dtype=torch.bfloat16, device="cuda")
+    ops.ragged_grouped_gemm_nvfp4(*args, ops.GemmConfig(cta_pair=1), out=stored)
+
+    valid = np.concatenate([np.arange(o, o + r) for o, r in zip(offs, rows_list)]).astype(np.int64)
+    slots = rng.permutation(len(valid))                      # destination slot of every valid row
+    which = rng.integers(0, 2, len(valid))                   # destination buffer of every valid row
+    dropped = rng.random(len(valid)) < 0.1
+    code = np.full(tot, -1, np.int32)
+    code[valid] = np.where(dropped, -1, (which << 26) | slots).astype(np.int32)
+    dest = [torch.full((len(valid), n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    bases = (ctypes.c_void_p * 2)(dest[0].data_ptr(), dest[1].data_ptr())
+    a_qt, a_sft, b_qt, b_sft, o_t, r_t, al_t, rs_t = args
+    _lib.check(_lib.load().msc_grouped_gemm_nvfp4_scatter_ragged(
+        a_qt.data_ptr(), a_sft.data_ptr(), b_qt.data_ptr(), b_sft.data_ptr(), al_t.data_ptr(), o_t.data_ptr(),
+        r_t.data_ptr(), rs_t.data_ptr(), T(code).data_ptr(), bases, 2, l, tot, n, k, ops.GemmConfig().c(),
+        torch.cuda.current_stream().cuda_stream))
+    assert _lib.status_word() == 0
+    want = [torch.full_like(d, float("nan")) for d in dest]
+    for row, slot, w, drop in zip(valid, slots, which, dropped):
+        if not drop:
+            want[w][slot] = stored[row]
+    for d, w in zip(dest, want):
+        assert torch.equal(d.view(torch.int16), w.view(torch.int16))
+    assert int((~torch.isnan(dest[0])).sum() + (~torch.isnan(dest[1])).sum()) == int((~dropped).sum()) * n
