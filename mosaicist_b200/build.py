@@ -21,6 +21,11 @@ PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libmosaicist_sm100a.so"
 PTX = PKG / "libmosaicist_sm100a.ptx"
+#: PTX text per GEMM translation unit; the first is the default kernel and sits where
+#: msc_ptx_path() points, the others beside it with a suffix
+PTX_UNITS = {"pair": ("gemm_blockscaled_pair.cu", PTX),
+             "single": ("gemm_blockscaled.cu", PKG / "libmosaicist_sm100a.single.ptx"),
+             "dense": ("gemm_dense_f16.cu", PKG / "libmosaicist_sm100a.dense.ptx")}
 PTXAS_LOG = PKG / "libmosaicist_sm100a.ptxas.log"
 DEBUG_LIB = PKG / "libmosaicist_sm100a_debug.so"
 
@@ -33,7 +38,7 @@ def sources() -> list[pathlib.Path]:
 
 
 def _stale() -> bool:
-    if not LIB.exists() or not PTX.exists():
+    if not LIB.exists() or not all(dst.exists() for _, dst in PTX_UNITS.values()):
         return True
     built = LIB.stat().st_mtime
     deps = list(CSRC.glob("*")) + [PKG.parent / "include" / "mosaicist_sm100a.h"]
@@ -59,10 +64,11 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     if verbose:
         print(res.stderr)
     # PTX text of the GEMM kernels: what a capture module hands to the PTX fingerprinter
-    cmd = [nvcc, *ARCH, *COMMON, "-ptx", "-o", str(PTX), str(CSRC / "gemm_blockscaled.cu")]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc -ptx failed:\n" + res.stderr[-4000:])
+    for src, dst in PTX_UNITS.values():
+        cmd = [nvcc, *ARCH, *COMMON, "-ptx", "-o", str(dst), str(CSRC / src)]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc -ptx failed:\n" + res.stderr[-4000:])
     return LIB
 
 

@@ -73,7 +73,14 @@ def build():
     alpha = torch.ones((L,), dtype=torch.float32, device=a_q.device)
     masked_m = torch.full((L,), M, dtype=torch.int32, device=a_q.device)
     out = torch.empty((L, M, N), dtype=torch.bfloat16, device=a_q.device)
-    drop_artifacts()
+    single = int(k["cta_pair"]) == 2 or int(k["tile_n"]) != 0
+    # mangled template arguments: <kind, stages, ...> of the pair kernel, <kind, tile_n, stages> of the other
+    pair_stages = min(max(int(k["stages"]) or 5, 2), 5)
+    tile = int(k["tile_n"]) or 128
+    single_stages = min(int(k["stages"]) or 9, 5 if tile == 128 else 3)
+    drop_artifacts("single" if single else "pair",
+                   f"gemm_blockscaled_kernelILi0ELi{tile}ELi{single_stages}E" if single
+                   else f"gemm_pair_kernelILi0ELi{pair_stages}ELb0ELb0ELb0E")
 
     def fn():
         return ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, alpha, masked_m, cfg, out=out)

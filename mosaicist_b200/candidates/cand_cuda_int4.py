@@ -65,7 +65,7 @@ def build():
     k = from_env(DEFAULTS)
     a, b_q, scales, offs, rows = _inputs()
     out = torch.zeros((a.shape[0], N), dtype=torch.bfloat16, device=a.device)
-    drop_artifacts()
+    drop_artifacts("dense", "gemm_dense_f16_kernelILi5ELb1ELb1E" if int(k["fused"]) else "gemm_dense_f16_kernelILi6ELb1ELb0E")
 
     def fn():
         return ops.mixed_grouped_gemm_int4(a, b_q, scales, offs, rows, None, GROUP_SIZE, out=out,

@@ -89,7 +89,14 @@ def build():
     args = _inputs()
     (_, _, _, w1_gs, w1_alpha, _, _, w2_gs, w2_alpha, _, in_gs, a2_gs) = args
     folded = fold_alphas(w1_gs, w1_alpha, w2_gs, w2_alpha, in_gs, a2_gs)   # constants of the weights
-    drop_artifacts()
+    single = int(k["cta_pair"]) == 2 or int(k["tile_n"]) != 0
+    # mangled template arguments: <kind, stages, ...> of the pair kernel, <kind, tile_n, stages> of the other
+    pair_stages = min(max(int(k["stages"]) or 5, 2), 5)
+    tile = int(k["tile_n"]) or 128
+    single_stages = min(int(k["stages"]) or 9, 5 if tile == 128 else 3)
+    drop_artifacts("single" if single else "pair",
+                   f"gemm_blockscaled_kernelILi0ELi{tile}ELi{single_stages}E" if single
+                   else f"gemm_pair_kernelILi0ELi{pair_stages}ELb0ELb0ELb0E")
 
     def fn():
         return moe_masked(*args, gemm1_config=cfg, gemm2_config=cfg, folded_alphas=folded)

@@ -97,7 +97,14 @@ def build():
     cfg = ops.GemmConfig(tile_n=int(k["tile_n"]), stages=int(k["stages"]), cta_pair=int(k["cta_pair"]))
     a_q, a_sf, b_q, b_sf, offs, rows, _, _ = _inputs()
     out = torch.zeros((a_q.shape[0], N), dtype=torch.bfloat16, device=a_q.device)
-    drop_artifacts()
+    single = int(k["cta_pair"]) == 2 or int(k["tile_n"]) != 0
+    # mangled template arguments: <kind, stages, ...> of the pair kernel, <kind, tile_n, stages> of the other
+    pair_stages = min(max(int(k["stages"]) or 5, 2), 5)
+    tile = int(k["tile_n"]) or 128
+    single_stages = min(int(k["stages"]) or 9, 5 if tile == 128 else 3)
+    drop_artifacts("single" if single else "pair",
+                   f"gemm_blockscaled_kernelILi1ELi{tile}ELi{single_stages}E" if single
+                   else f"gemm_pair_kernelILi1ELi{pair_stages}ELb0ELb0ELb0E")
 
     def fn():
         return ops.ragged_grouped_gemm_mxfp8(a_q, a_sf, b_q, b_sf, offs, rows, None, None, cfg, out=out)

@@ -216,3 +216,24 @@ def test_torch_custom_op_is_registered_and_shape_propagates():
             torch.empty((8, 512, 1024), **u8), torch.empty((8, 4, 32, 32, 16), **u8),
             torch.empty((8, 2048, 1024), **u8), torch.empty((8, 16, 32, 32, 16), **u8), None, None)
         assert tuple(out.shape) == (8, 512, 2048) and out.dtype == torch.bfloat16
+
+
+def test_dropped_ptx_is_reduced_to_the_running_instantiation(lib, tmp_path, monkeypatch):
+    """The capture module leaves a PTX holding only the kernel instantiation that runs (the
+    fingerprinter picks the entry with the most instructions)."""
+    import re
+
+    from mosaicist_b200.candidates import _common
+
+    toy = (".version 8.8\n.target sm_100a\n.extern .shared .b8 s[];\n"
+           ".visible .entry kA_ILi1E(\n .param .u64 p\n)\n{\n { nested } \n ret;\n}\n"
+           ".visible .entry kB_ILi2E(\n .param .u64 p\n)\n.maxntid 320\n{\n ret;\n}\n")
+    red = _common.only_entry(toy, "kB_ILi2E")
+    assert "kB_ILi2E" in red and "kA_ILi1E" not in red and red.startswith(".version 8.8") and ".maxntid 320" in red
+    assert _common.only_entry(toy, "missing") == toy
+    monkeypatch.setenv("MOSAIC_GPU_DUMP_TO", str(tmp_path))
+    _common.drop_artifacts("pair", "gemm_pair_kernelILi0ELi5ELb0ELb0ELb0E")
+    text = next(tmp_path.glob("*.ptx")).read_text()
+    entries = re.findall(r"^\.visible \.entry (\S+)\(", text, re.M)
+    assert len(entries) == 1 and "gemm_pair_kernelILi0ELi5ELb0ELb0ELb0E" in entries[0]
+    assert list(tmp_path.glob("ptxas*"))
