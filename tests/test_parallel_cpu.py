@@ -119,3 +119,28 @@ def _placement_worker(rank, world, port, experts):
 
 def test_peer_exchange_placement_world2():
     mp.spawn(_placement_worker, args=(2, _free_port(), 8), nprocs=2, join=True)
+
+
+def test_exchange_layout_sections_are_aligned_and_disjoint():
+    """The exchange allocation: every buffer starts on a 1 KB boundary (TMA maps and bulk copies
+    need 16 bytes), no two buffers overlap, and the views have the shapes the kernels expect."""
+    from mosaicist_b200.parallel import EXCHANGE_BUFFERS, exchange_layout, exchange_views
+
+    for rows_cap, hidden, pairs_cap, world, experts in [(128, 256, 0, 0, 0), (1280, 7168, 640, 8, 256),
+                                                        (384, 512, 96, 2, 32)]:
+        offs, total = exchange_layout(rows_cap, hidden, pairs_cap, world, experts)
+        assert len(offs) == len(EXCHANGE_BUFFERS) and all(o % 1024 == 0 for o in offs) and total % 1024 == 0
+        base = torch.zeros(total, dtype=torch.uint8)
+        views = exchange_views(base, rows_cap, hidden, pairs_cap, world, experts)
+        assert set(views) == set(EXCHANGE_BUFFERS)
+        assert tuple(views["a_q"].shape) == (rows_cap, hidden // 2)
+        assert tuple(views["sf_rows"].shape) == (rows_cap, hidden // 16)
+        assert tuple(views["y"].shape) == (rows_cap, hidden) and views["y"].dtype == torch.bfloat16
+        assert tuple(views["recv_y"].shape) == (pairs_cap, hidden)
+        assert tuple(views["counts_all"].shape) == (world, experts) and views["flags"].numel() == 64
+        spans = sorted((v.data_ptr() - base.data_ptr(), v.numel() * v.element_size()) for v in views.values())
+        for (a0, an), (b0, _) in zip(spans, spans[1:]):
+            assert a0 + an <= b0
+        assert spans[-1][0] + spans[-1][1] <= total
+    with pytest.raises(ValueError):
+        exchange_views(torch.zeros(10, dtype=torch.uint8), 128, 256)
