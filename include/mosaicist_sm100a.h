@@ -56,6 +56,12 @@ typedef struct msc_gemm_cfg {
 int msc_version(void);
 const char* msc_last_error(void);
 
+/* Releases what the library caches on the host: the encoded tensor maps, keyed by (address,
+ * shape, box).  The library owns no device memory besides two small static arrays (the status
+ * word and the planning scratch of msc_moe_plan_noalloc); every buffer belongs to the caller.
+ * Call it when no launch is being issued; later calls encode their maps again. */
+int msc_shutdown(void);
+
 /* Path of the PTX text of this library's kernels (written next to the .so at build time),
  * so a capture module can drop it where the reference's collect_artifacts looks
  * (src/mosaicist/capture.py:81-116).  Host string, owned by the library. */

@@ -37,6 +37,7 @@ _CFG = ctypes.POINTER(GemmCfg)
 SIGNATURES = {
     "msc_version": (_I, []),
     "msc_last_error": (ctypes.c_char_p, []),
+    "msc_shutdown": (_I, []),
     "msc_ptx_path": (ctypes.c_char_p, []),
     "msc_status_word_read": (_I, [ctypes.POINTER(ctypes.c_int)]),
     "msc_grouped_gemm_nvfp4": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _CFG, _P]),

@@ -77,10 +77,18 @@ int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t r
 // A tensor map only encodes address, shape and box, so one encoded for a buffer stays valid
 // for any later buffer at the same address with the same shape: cache them, the driver call
 // costs microseconds and the GEMM itself runs for about ten.
+static std::mutex g_tmap_mu;
+static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
+
+void clear_tmap_cache() {
+  std::lock_guard<std::mutex> lock(g_tmap_mu);
+  g_tmap_cache.clear();
+}
+
 static int cached_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                        uint32_t box_rows, int flavour) {
-  static std::mutex mu;
-  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  std::mutex& mu = g_tmap_mu;
+  auto& cache = g_tmap_cache;
   const TmapKey key{base, rows, row_bytes, box_rows | ((uint32_t)flavour << 30)};
   {
     std::lock_guard<std::mutex> lock(mu);
@@ -177,6 +185,11 @@ int num_sms() {
 extern "C" {
 
 int msc_version(void) { return 1; }
+
+int msc_shutdown(void) {
+  msc::clear_tmap_cache();
+  return MSC_OK;
+}
 
 const char* msc_last_error(void) { return msc::g_err; }
 

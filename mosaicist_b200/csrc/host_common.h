@@ -50,6 +50,9 @@ int make_tmap_narrow_2d(CUtensorMap* map, const void* base, uint64_t rows, uint6
 int make_tmap_pitched_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                          uint64_t pitch_bytes, uint32_t box_rows);
 
+// Forgets every cached tensor map (msc_shutdown).
+void clear_tmap_cache();
+
 int num_sms();
 
 // Launch configuration with programmatic stream serialization: the kernel's set-up may overlap

@@ -301,3 +301,17 @@ def test_scatter_epilogue_equals_store_then_permute(rows_list, n, k):
     for d, w in zip(dest, want):
         assert torch.equal(d.view(torch.int16), w.view(torch.int16))
     assert int((~torch.isnan(dest[0])).sum() + (~torch.isnan(dest[1])).sum()) == int((~dropped).sum()) * n
+
+
+def test_shutdown_drops_cached_tensor_maps_and_the_next_call_rebuilds_them():
+    from mosaicist_b200 import _lib, ops
+
+    l, m, n, k = 1, 256, 256, 256
+    rng = np.random.default_rng(12)
+    a_q, a_sf = O.exact_operands(rng, l, m, k)
+    b_q, b_sf = O.exact_operands(rng, l, n, k)
+    args = (T(O.pack_e2m1(a_q)), T(O.e4m3_bytes(O.retile(a_sf))), T(O.pack_e2m1(b_q)), T(O.e4m3_bytes(O.retile(b_sf))))
+    first = ops.masked_grouped_gemm(*args).clone()
+    assert _lib.load().msc_shutdown() == 0
+    again = ops.masked_grouped_gemm(*args)
+    assert torch.equal(first, again) and _lib.status_word() == 0
