@@ -237,3 +237,20 @@ def test_dropped_ptx_is_reduced_to_the_running_instantiation(lib, tmp_path, monk
     entries = re.findall(r"^\.visible \.entry (\S+)\(", text, re.M)
     assert len(entries) == 1 and "gemm_pair_kernelILi0ELi5ELb0ELb0ELb0E" in entries[0]
     assert list(tmp_path.glob("ptxas*"))
+
+
+def test_bench_reference_arm_runs_on_the_cpu_and_prints_the_contract_line():
+    """`bench.py --impl reference` needs no GPU: one JSON line with the same metric, unit and
+    workload as the GPU arm, the CPU baseline describing itself, and zero copied bytes."""
+    import subprocess
+    import sys
+
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0"], capture_output=True, text=True, check=True, cwd=ROOT).stdout
+    line = json.loads(out.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "nvfp4_grouped_gemm_tflops" and line["unit"] == "TFLOP/s"
+    assert line["n_gpus"] == 1 and line["steps"] == 1 and line["higher_is_better"] is True
+    assert "l=8 m=512 n=2048 k=2048" in line["config"]["workload"]
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["cpu_baseline"]["value"] == line["value"] > 0
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
