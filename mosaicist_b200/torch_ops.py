@@ -1,9 +1,17 @@
-"""The masked grouped GEMM as a torch custom operator, `torch.ops.mosaicist_sm100a.grouped_gemm_nvfp4`,
-for callers that build graphs of torch operators (tracing, FakeTensor shape propagation) instead of
-calling `ops.masked_grouped_gemm` directly.  Same operands as the reference's masked_grouped_gemm
-(masked_gemm.py:104-123) and FlashInfer's grouped_gemm_nt_masked call site
-(experiments/loop/ref_flashinfer_gemm.py:25-31); the CUDA implementation is the C-ABI entry point
-msc_grouped_gemm_nvfp4.  Importing this module registers the operator; it needs no GPU.
+"""The hot-path operators as torch custom operators (`torch.ops.mosaicist_sm100a.*`), for callers
+that build graphs of torch operators (tracing, FakeTensor shape propagation) instead of calling
+`mosaicist_b200.ops` directly:
+
+    grouped_gemm_nvfp4         masked grouped GEMM, the operands of the reference's
+                               masked_grouped_gemm (masked_gemm.py:104-123) and of FlashInfer's
+                               grouped_gemm_nt_masked call site (ref_flashinfer_gemm.py:25-31)
+    grouped_gemm_nvfp4_ragged  the same arithmetic over row-concatenated groups
+    quantize_nvfp4             quantize_nvfp4 (nvfp4.py:39-57) with scales in the MMA tiling
+    silu_mul_quantize_nvfp4    silu_mul (nvfp4.py:81-88) + quantize_nvfp4
+
+Each is the corresponding C-ABI entry point.  Operators return fresh tensors, so rows a masked
+call leaves untouched come back as zeros.  Importing this module registers the operators; it
+needs no GPU.
 """
 
 from __future__ import annotations
@@ -29,3 +37,57 @@ def grouped_gemm_nvfp4(a_q: torch.Tensor, a_sf: torch.Tensor, b_q: torch.Tensor,
 @grouped_gemm_nvfp4.register_fake
 def _(a_q, a_sf, b_q, b_sf, alpha, masked_m):
     return a_q.new_empty((a_q.shape[0], a_q.shape[1], b_q.shape[1]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("mosaicist_sm100a::grouped_gemm_nvfp4_ragged", mutates_args=(), device_types="cuda")
+def grouped_gemm_nvfp4_ragged(a_q: torch.Tensor, a_sf: torch.Tensor, b_q: torch.Tensor, b_sf: torch.Tensor,
+                              group_offsets: torch.Tensor, group_rows: torch.Tensor,
+                              alpha: Optional[torch.Tensor], row_scale: Optional[torch.Tensor]) -> torch.Tensor:
+    """(rows_total, k/2) x (l, n, k/2) -> (rows_total, n) bf16, group g owning rows
+    [group_offsets[g], + group_rows[g]); rows outside every group come back as zeros."""
+    out = torch.zeros((a_q.shape[0], b_q.shape[1]), dtype=torch.bfloat16, device=a_q.device)
+    return ops.ragged_grouped_gemm_nvfp4(a_q, a_sf, b_q, b_sf, group_offsets, group_rows, alpha, row_scale, out=out)
+
+
+@grouped_gemm_nvfp4_ragged.register_fake
+def _(a_q, a_sf, b_q, b_sf, group_offsets, group_rows, alpha, row_scale):
+    return a_q.new_empty((a_q.shape[0], b_q.shape[1]), dtype=torch.bfloat16)
+
+
+def _quantized_shapes(l, m, k):
+    return (l, m, k // 2), (l, m // 128, k // 64, 32, 16)
+
+
+@torch.library.custom_op("mosaicist_sm100a::quantize_nvfp4", mutates_args=(), device_types="cuda")
+def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor,
+                   masked_m: Optional[torch.Tensor]) -> tuple[torch.Tensor, torch.Tensor]:
+    """(l, m, k) bf16 / f32 -> packed e2m1 (l, m, k/2) and tiled e4m3 scales (l, m/128, k/64, 32, 16)."""
+    q, sf = ops.quantize_nvfp4(x, global_scale, masked_m)
+    if masked_m is not None:          # rows the kernel left untouched are uninitialised in q
+        rows = torch.arange(x.shape[1], device=x.device)[None, :, None] < masked_m[:, None, None]
+        q = torch.where(rows, q, torch.zeros_like(q))
+    return q, sf
+
+
+@quantize_nvfp4.register_fake
+def _(x, global_scale, masked_m):
+    qs, ss = _quantized_shapes(*x.shape)
+    return x.new_empty(qs, dtype=torch.uint8), x.new_empty(ss, dtype=torch.uint8)
+
+
+@torch.library.custom_op("mosaicist_sm100a::silu_mul_quantize_nvfp4", mutates_args=(), device_types="cuda")
+def silu_mul_quantize_nvfp4(gateup: torch.Tensor, global_scale: torch.Tensor,
+                            masked_m: Optional[torch.Tensor]) -> tuple[torch.Tensor, torch.Tensor]:
+    """(l, m, 2n) bf16 -> NVFP4 of silu(gate) * up: (l, m, n/2) and (l, m/128, n/64, 32, 16)."""
+    q, sf = ops.silu_mul_quantize_nvfp4(gateup, global_scale, masked_m)
+    if masked_m is not None:
+        rows = torch.arange(gateup.shape[1], device=gateup.device)[None, :, None] < masked_m[:, None, None]
+        q = torch.where(rows, q, torch.zeros_like(q))
+    return q, sf
+
+
+@silu_mul_quantize_nvfp4.register_fake
+def _(gateup, global_scale, masked_m):
+    l, m, n2 = gateup.shape
+    qs, ss = _quantized_shapes(l, m, n2 // 2)
+    return gateup.new_empty(qs, dtype=torch.uint8), gateup.new_empty(ss, dtype=torch.uint8)

@@ -216,6 +216,17 @@ def test_torch_custom_op_is_registered_and_shape_propagates():
             torch.empty((8, 512, 1024), **u8), torch.empty((8, 4, 32, 32, 16), **u8),
             torch.empty((8, 2048, 1024), **u8), torch.empty((8, 16, 32, 32, 16), **u8), None, None)
         assert tuple(out.shape) == (8, 512, 2048) and out.dtype == torch.bfloat16
+        x = torch.empty((8, 512, 2048), dtype=torch.bfloat16, device="cuda")
+        gs = torch.empty((8,), dtype=torch.float32, device="cuda")
+        q, sf = torch.ops.mosaicist_sm100a.quantize_nvfp4(x, gs, None)
+        assert tuple(q.shape) == (8, 512, 1024) and tuple(sf.shape) == (8, 4, 32, 32, 16)
+        q, sf = torch.ops.mosaicist_sm100a.silu_mul_quantize_nvfp4(x, gs, None)
+        assert tuple(q.shape) == (8, 512, 512) and tuple(sf.shape) == (8, 4, 16, 32, 16)
+        i32 = dict(dtype=torch.int32, device="cuda")
+        y = torch.ops.mosaicist_sm100a.grouped_gemm_nvfp4_ragged(
+            torch.empty((1024, 1024), **u8), torch.empty((8, 32, 32, 16), **u8), torch.empty((4, 512, 1024), **u8),
+            torch.empty((4, 4, 32, 32, 16), **u8), torch.empty((4,), **i32), torch.empty((4,), **i32), None, None)
+        assert tuple(y.shape) == (1024, 512) and y.dtype == torch.bfloat16
 
 
 def test_dropped_ptx_is_reduced_to_the_running_instantiation(lib, tmp_path, monkeypatch):

@@ -256,6 +256,22 @@ def test_torch_custom_op_matches_direct_call():
     want = ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, None, masked,
                                    out=torch.zeros((l, m, n), dtype=torch.bfloat16, device="cuda"))
     assert torch.equal(got, want) and int((got[1, 77:] != 0).sum()) == 0 and int((got[1, :77] != 0).sum()) > 0
+    # the quantisers and the ragged GEMM as operators
+    x = torch.randn((l, m, k), device="cuda", generator=g).bfloat16()
+    gs = torch.full((l,), 448.0, device="cuda")
+    q_op, sf_op = torch.ops.mosaicist_sm100a.quantize_nvfp4(x, gs, None)
+    q_d, sf_d = ops.quantize_nvfp4(x, gs)
+    assert torch.equal(q_op, q_d) and torch.equal(sf_op, sf_d)
+    q_op, sf_op = torch.ops.mosaicist_sm100a.silu_mul_quantize_nvfp4(x, gs, None)
+    q_d, sf_d = ops.silu_mul_quantize_nvfp4(x, gs)
+    assert torch.equal(q_op, q_d) and torch.equal(sf_op, sf_d)
+    offs = torch.tensor([0, 256], dtype=torch.int32, device="cuda")
+    rows = torch.tensor([200, 256], dtype=torch.int32, device="cuda")
+    y_op = torch.ops.mosaicist_sm100a.grouped_gemm_nvfp4_ragged(a_q.view(l * m, -1), a_sf.view(l * m // 128, k // 64, 32, 16),
+                                                                 b_q, b_sf, offs, rows, None, None)
+    y_d = ops.ragged_grouped_gemm_nvfp4(a_q.view(l * m, -1), a_sf.view(l * m // 128, k // 64, 32, 16), b_q, b_sf, offs,
+                                        rows, out=torch.zeros((l * m, n), dtype=torch.bfloat16, device="cuda"))
+    assert torch.equal(y_op, y_d) and int((y_op[200:256] != 0).sum()) == 0
 
 
 @pytest.mark.parametrize("rows_list,n,k", [([256], 256, 256), ([300, 0, 77, 512, 129], 512, 640)])
