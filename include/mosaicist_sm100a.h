@@ -11,8 +11,8 @@
  *     exits; msc_last_error() gives a thread-local one-line message for the last failure;
  *   - the caller owns every buffer; all pointers are DEVICE pointers unless a comment
  *     says "host"; the library allocates nothing on the device unless a comment says so;
- *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous and there is
- *     no hidden synchronisation;
+ *   - `stream` is a cudaStream_t passed as void*; every call that takes one only enqueues
+ *     work and never synchronises (msc_status_word_read, which takes none, does);
  *   - device-side waits are bounded: a kernel that gives up records a code in the
  *     library's status word (msc_status_word_read) and leaves the context usable.
  */
@@ -50,7 +50,10 @@ typedef struct msc_gemm_cfg {
                     ignores tile_n); 2: one CTA per tile; 0: the library chooses (pairs when
                     tile_n is 0, n % 256 == 0 and groups have >= 256 rows).  The counterpart
                     of the reference's `collective` knob (cand_pallas_gemm.py:31)          */
-  int reserved[2];
+  int sf_warps;  /* CTA-pair kernel only. 1: four extra warps write the scale factors into tensor
+                    memory (tcgen05.st) instead of the MMA warp copying them (tcgen05.cp);
+                    0: the default, copies                                              */
+  int reserved;
 } msc_gemm_cfg;
 
 int msc_version(void);
@@ -90,7 +93,8 @@ int msc_grouped_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, c
  * [group_offsets[g], group_offsets[g] + group_rows[g]) of a_q / out; offsets must be
  * multiples of 128 (the scale tiling is per 128 rows).  row_scale (rows_total) fp32 is read
  * when cfg->epilogue == MSC_EPI_ROW_SCALE.  The reference has no ragged form; this is the
- * layout BASELINE config 3 and the MoE layer use, with per-group semantics as above.
+ * layout the skewed-group MXFP8 benchmark (32 groups, Zipf row counts) and the MoE layer
+ * use, with per-group semantics as above.
  *   a_q (rows_total, k/2), a_sf (ceil(rows_total/128), k/64, 32, 16), out (rows_total, n) */
 int msc_grouped_gemm_nvfp4_ragged(const void* a_q, const void* a_sf, const void* b_q,
                                   const void* b_sf, const float* alpha,
@@ -116,7 +120,7 @@ int msc_grouped_gemm_nvfp4_swiglu_ragged(const void* a_q, const void* a_sf, cons
 /* MXFP8 grouped GEMM (e4m3 values, one ue8m0 scale per 32 K-elements), ragged rows as
  * above.  The nearest reference arithmetic is the Hopper analog's block-scaled FP8 GEMM
  * (experiments/flashinfer-megamoe-sm90a/quant.py:47-75) with the scale format and block
- * size BASELINE config 3 prescribes.
+ * size of the MX formats (OCP Microscaling: one power-of-two scale per 32 elements).
  *   a_q (rows_total, k) e4m3, a_sf (ceil(rows_total/128), k/128, 32, 16) ue8m0 (same
  *   128-row tiling, 4 scale columns per chunk), b_q (l, n, k), b_sf (l, n/128, k/128, 32, 16)
  * Requires k % 128 == 0. */
@@ -254,7 +258,10 @@ int msc_moe_unpermute(const void* y, const int32_t* ids, const int32_t* rank,
  * row r (times alpha and, if given, row_scale[r]) goes to
  * dest_bases[code >> 26] + (code & 0x3ffffff) * n bf16 with code = row_dest[r] (rows_total) i32;
  * rows with a negative code are skipped.  dest_bases is a host array of dest_count (<= 16)
- * device pointers, which may be other GPUs' mapped memory: each row leaves as untiled 256-byte
+ * device pointers to dest_rows rows of n bf16 each; a code that names a destination >= dest_count
+ * or a row >= dest_rows is not stored and raises bit 0x00C00000 in the status word (the codes
+ * are written by other ranks: reset row_dest to -1 between steps so a row nobody wrote in this
+ * step is skipped).  The destinations may be other GPUs' mapped memory: each row leaves as untiled 256-byte
  * bulk copies (cp.async.bulk shared -> global), never as a tiled or multicast operation.  The
  * MoE's second GEMM uses it to deliver every result row to the token's home rank while the
  * GEMM is still running.  No counterpart in the reference.  n % 256 == 0, k % 64 == 0. */
@@ -262,9 +269,9 @@ int msc_grouped_gemm_nvfp4_scatter_ragged(const void* a_q, const void* a_sf, con
                                           const void* b_sf, const float* alpha,
                                           const int32_t* group_offsets, const int32_t* group_rows,
                                           const float* row_scale, const int32_t* row_dest,
-                                          void* const* dest_bases, int dest_count, int l,
-                                          int rows_total, int n, int k, const msc_gemm_cfg* cfg,
-                                          void* stream);
+                                          void* const* dest_bases, int dest_count, int dest_rows,
+                                          int l, int rows_total, int n, int k,
+                                          const msc_gemm_cfg* cfg, void* stream);
 
 /* ---- expert-parallel exchange over peer memory --------------------------------------------
  * No counterpart in the reference, which runs on one GPU; the partitioning is the one its
@@ -275,8 +282,9 @@ int msc_grouped_gemm_nvfp4_scatter_ragged(const void* a_q, const void* a_sf, con
  * (rows_cap, hidden/16).  Every rank maps every other rank's buffers (msc_peer_*).  Per layer:
  * msc_moe_plan over all E experts (counts + position of each pair), an all-gather of the
  * counts, msc_ep_offsets, msc_ep_dispatch_quantize, a barrier, msc_sf_swizzle of the received
- * scale rows into the MMA tiling, the local GEMMs, a barrier, msc_ep_combine.  The barriers and the all-gather are the caller's (NCCL, stream-ordered);
- * no kernel of this library waits on another GPU.  A destination row at or beyond rows_cap is
+ * scale rows into the MMA tiling, the local GEMMs, a barrier, msc_ep_combine.  The barriers and
+ * the all-gather are either the caller's collectives (NCCL, stream-ordered) or this library's
+ * flags (msc_ep_signal / msc_ep_wait below).  A destination row at or beyond rows_cap is
  * never stored: the pair is dropped, its pair_row set to -1 and bit 0x00E00000 raised in the
  * status word (msc_status_word_read). */
 
@@ -339,8 +347,11 @@ int msc_ep_combine(const void* const* peer_y, const int32_t* ids, const int32_t*
 
 /* out[token] = bf16( sum over k (ascending, fp32) of y_pairs[token * topk + k] ): the last step
  * when the second GEMM scattered every pair's result row to the token's home rank.
- * y_pairs (tokens * topk, hidden) bf16, out (tokens, hidden) bf16. */
-int msc_ep_sum_pairs(const void* y_pairs, void* out, int tokens, int hidden, int topk, void* stream);
+ * y_pairs (tokens * topk, hidden) bf16, out (tokens, hidden) bf16.  pair_row (tokens, topk) i32
+ * or NULL: pairs marked negative by msc_ep_dispatch_quantize (dropped because the owner's
+ * buffers were full) are left out of the sum; their row of y_pairs holds stale data. */
+int msc_ep_sum_pairs(const void* y_pairs, const int32_t* pair_row, void* out, int tokens, int hidden,
+                     int topk, void* stream);
 
 #ifdef __cplusplus
 }

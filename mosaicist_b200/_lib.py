@@ -27,7 +27,7 @@ class MscError(RuntimeError):
 class GemmCfg(ctypes.Structure):
     _fields_ = [("tile_n", ctypes.c_int), ("stages", ctypes.c_int), ("raster", ctypes.c_int),
                 ("max_ctas", ctypes.c_int), ("epilogue", ctypes.c_int),
-                ("cta_pair", ctypes.c_int), ("reserved", ctypes.c_int * 2)]
+                ("cta_pair", ctypes.c_int), ("sf_warps", ctypes.c_int), ("reserved", ctypes.c_int)]
 
 
 _P, _I = ctypes.c_void_p, ctypes.c_int
@@ -65,8 +65,8 @@ SIGNATURES = {
     "msc_ep_signal": (_I, [_P, _I, _I, _I, _I, _P, _P, _I, _P]),
     "msc_ep_wait": (_I, [_P, _I, _I, _I, _P]),
     "msc_ep_dispatch_quantize": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P]),
-    "msc_ep_sum_pairs": (_I, [_P, _P, _I, _I, _I, _P]),
-    "msc_grouped_gemm_nvfp4_scatter_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _CFG, _P]),
+    "msc_ep_sum_pairs": (_I, [_P, _P, _P, _I, _I, _I, _P]),
+    "msc_grouped_gemm_nvfp4_scatter_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _CFG, _P]),
     "msc_ep_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
 }
 

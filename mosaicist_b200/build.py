@@ -4,7 +4,7 @@
 
 `--debug` also builds libmosaicist_sm100a_debug.so with -DMSC_DEBUG: the same kernels plus
 per-CTA clock stamps (clock64 and the global nanosecond timer) and pipeline-stage skip flags,
-used by `mosaicist_b200.clock_probe`; nothing else loads it.
+used by `python -m mosaicist_b200.profile_stage --in-kernel-clock`; nothing else loads it.
 
 The library is compiled for sm_100a only.  nvcc cross-compiles without a GPU, so this
 runs on a CPU-only machine; the resulting .so is what the GPU machine loads.

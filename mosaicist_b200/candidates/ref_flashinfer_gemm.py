@@ -16,7 +16,6 @@ packages that must be importable where this runs; nothing else in the repository
 from __future__ import annotations
 
 from . import cand_cuda_gemm as cand
-from ._common import drop_artifacts  # noqa: F401  (kept for symmetry; CuTeDSL dumps its own PTX)
 
 L, M, K, N = cand.L, cand.M, cand.K, cand.N
 GEMM_KW = dict(ab_dtype="float4_e2m1fn", sf_dtype="float8_e4m3fn", c_dtype="bfloat16", sf_vec_size=16)

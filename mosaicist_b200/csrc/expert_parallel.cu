@@ -131,10 +131,13 @@ ep_offsets_kernel(const int* counts_all, int world, int rank, int experts_total,
     }
     send_base[e] = off + before;
     if (owner == rank) {
+      // the table this rank's GEMMs walk never reaches beyond its buffers: a group that starts
+      // at or after rows_cap gets no rows, one that straddles it is cut (its senders drop the
+      // pairs that do not fit and the overflow bit below says so)
       const int el = e - owner * experts_local;
-      group_rows[el] = total;
-      group_offsets[el] = off;
-      if (el == experts_local - 1) *total_rows = off + aligned_total[e];
+      group_rows[el] = off >= rows_cap ? 0 : min(total, rows_cap - off);
+      group_offsets[el] = min(off, rows_cap);
+      if (el == experts_local - 1) *total_rows = min(off + aligned_total[e], rows_cap);
     }
     if (e == (owner + 1) * experts_local - 1 && off + aligned_total[e] > rows_cap)
       atomicOr(status, kStatusEpOverflow);
@@ -331,9 +334,11 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p
 
 // out[token] = bf16(sum over k, ascending, fp32) of y_pairs[token * topk + k]: the last step when
 // the second GEMM has already delivered every pair's result row to the token's home rank.
+// With pair_row, pairs marked negative (dropped on overflow, never delivered) are left out: their
+// row of y_pairs still holds an earlier step's data.
 __global__ void __launch_bounds__(256)
-ep_sum_pairs_kernel(const __nv_bfloat16* __restrict__ y_pairs, __nv_bfloat16* __restrict__ out,
-                    int tokens, int hidden, int topk) {
+ep_sum_pairs_kernel(const __nv_bfloat16* __restrict__ y_pairs, const int* __restrict__ pair_row,
+                    __nv_bfloat16* __restrict__ out, int tokens, int hidden, int topk) {
   const int vecs = hidden >> 3;
   const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long token = unit / vecs;
@@ -341,6 +346,7 @@ ep_sum_pairs_kernel(const __nv_bfloat16* __restrict__ y_pairs, __nv_bfloat16* __
   if (token >= tokens) return;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   for (int k = 0; k < topk; ++k) {
+    if (pair_row && __ldg(pair_row + token * topk + k) < 0) continue;
     const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(y_pairs + ((size_t)token * topk + k) * hidden) + vc);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
@@ -544,7 +550,8 @@ int msc_ep_wait(const int32_t* flags, int world, int slot, int epoch, void* stre
   return MSC_OK;
 }
 
-int msc_ep_sum_pairs(const void* y_pairs, void* out, int tokens, int hidden, int topk, void* stream) {
+int msc_ep_sum_pairs(const void* y_pairs, const int32_t* pair_row, void* out, int tokens, int hidden,
+                     int topk, void* stream) {
   if (!y_pairs || !out) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
   if (tokens <= 0 || topk <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
   if (hidden <= 0 || hidden % 8) return msc::fail(MSC_ERR_BAD_ARG, "hidden=%d must be a multiple of 8", hidden);
@@ -552,7 +559,8 @@ int msc_ep_sum_pairs(const void* y_pairs, void* out, int tokens, int hidden, int
   const long long blocks = (units + 255) / 256;
   if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
   msc::ep_sum_pairs_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(y_pairs), static_cast<__nv_bfloat16*>(out), tokens, hidden, topk);
+      static_cast<const __nv_bfloat16*>(y_pairs), pair_row, static_cast<__nv_bfloat16*>(out), tokens, hidden,
+      topk);
   MSC_CUDA_OK(cudaGetLastError());
   return MSC_OK;
 }

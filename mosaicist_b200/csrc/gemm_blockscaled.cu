@@ -428,13 +428,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
                   const GemmParams& p, int grid, cudaStream_t stream) {
   using L = Smem<TILE_N, STAGES>;
   auto kern = gemm_blockscaled_kernel<KIND, TILE_N, STAGES>;
-  static bool configured[64] = {false};
-  int dev = 0;
-  MSC_CUDA_OK(cudaGetDevice(&dev));
-  if (!configured[dev & 63]) {
-    MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
-    configured[dev & 63] = true;
-  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kAlloc)) return rc;
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t lc = pdl_launch_config(grid, L::kThreads, L::kAlloc, stream, attr);
   MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p));
@@ -512,6 +506,7 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   p.status = status;
   p.l = l;
   p.m_stride = m_stride;
+  p.rows_total = (int)rows_total;
   p.n = n;
   p.k_stages = (int)((k_bytes + 127) / 128);
   p.sf_chunks = k / chunk_elems;
@@ -520,6 +515,7 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   p.out_sf = nullptr;
   p.out_gs = nullptr;
   p.row_dest = nullptr;
+  p.scatter_count = p.scatter_rows = 0;
   for (auto& b : p.scatter_base) b = nullptr;
 #ifdef MSC_DEBUG
   p.trace = g_trace;
@@ -532,7 +528,7 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
     pair = (n % 256 == 0) && ((m_stride > 0 ? m_stride : rows_total / l) >= 256);
   if (pair)
     return launch_pair_gemm(kind, a_q, b_q, rows_total, k_bytes, p, cfg.stages, cfg.max_ctas,
-                            static_cast<cudaStream_t>(stream_v), cfg.reserved[0] == 1);
+                            static_cast<cudaStream_t>(stream_v), cfg.sf_warps == 1);
 
   const long long max_tiles = ((rows_total + 127) / 128 + l) * (long long)(n / tile_n);
   int grid = cfg.max_ctas > 0 ? cfg.max_ctas : num_sms();
@@ -609,6 +605,7 @@ int msc_grouped_gemm_nvfp4_swiglu_ragged(const void* a_q, const void* a_sf, cons
   p.status = status;
   p.l = l;
   p.m_stride = 0;
+  p.rows_total = rows_total;
   p.n = n2;
   p.k_stages = (k / 2 + 127) / 128;
   p.sf_chunks = k / 64;
@@ -617,6 +614,7 @@ int msc_grouped_gemm_nvfp4_swiglu_ragged(const void* a_q, const void* a_sf, cons
   p.out_sf = static_cast<uint8_t*>(d_sf);
   p.out_gs = out_global_scale;
   p.row_dest = nullptr;
+  p.scatter_count = p.scatter_rows = 0;
   for (auto& b : p.scatter_base) b = nullptr;
 #ifdef MSC_DEBUG
   p.trace = g_trace;
@@ -630,14 +628,16 @@ int msc_grouped_gemm_nvfp4_scatter_ragged(const void* a_q, const void* a_sf, con
                                           const void* b_sf, const float* alpha,
                                           const int32_t* group_offsets, const int32_t* group_rows,
                                           const float* row_scale, const int32_t* row_dest,
-                                          void* const* dest_bases, int dest_count, int l,
-                                          int rows_total, int n, int k, const msc_gemm_cfg* cfg,
-                                          void* stream) {
+                                          void* const* dest_bases, int dest_count, int dest_rows,
+                                          int l, int rows_total, int n, int k,
+                                          const msc_gemm_cfg* cfg, void* stream) {
   using namespace msc;
   if (!a_q || !a_sf || !b_q || !b_sf || !group_offsets || !group_rows || !row_dest || !dest_bases)
     return fail(MSC_ERR_BAD_ARG, "NULL pointer");
   if (dest_count < 1 || dest_count > 16)
     return fail(MSC_ERR_UNSUPPORTED, "dest_count=%d must be in [1, 16]", dest_count);
+  if (dest_rows < 1 || dest_rows > 0x04000000)
+    return fail(MSC_ERR_BAD_ARG, "dest_rows=%d must be in [1, 2^26]", dest_rows);
   if (l <= 0 || rows_total <= 0 || n <= 0 || k <= 0) return fail(MSC_ERR_BAD_ARG, "sizes must be positive");
   if (n % 256) return fail(MSC_ERR_BAD_ARG, "n=%d must be a multiple of 256", n);
   if (k % 64) return fail(MSC_ERR_BAD_ARG, "k=%d must be a multiple of 64", k);
@@ -656,6 +656,7 @@ int msc_grouped_gemm_nvfp4_scatter_ragged(const void* a_q, const void* a_sf, con
   p.status = status;
   p.l = l;
   p.m_stride = 0;
+  p.rows_total = rows_total;
   p.n = n;
   p.k_stages = (k / 2 + 127) / 128;
   p.sf_chunks = k / 64;
@@ -664,6 +665,8 @@ int msc_grouped_gemm_nvfp4_scatter_ragged(const void* a_q, const void* a_sf, con
   p.out_sf = nullptr;
   p.out_gs = nullptr;
   p.row_dest = row_dest;
+  p.scatter_count = dest_count;
+  p.scatter_rows = dest_rows;
   for (int i = 0; i < 16; ++i) {
     p.scatter_base[i] = i < dest_count ? static_cast<uint8_t*>(dest_bases[i]) : nullptr;
     if (i < dest_count && (!dest_bases[i] || reinterpret_cast<uintptr_t>(dest_bases[i]) % 16))

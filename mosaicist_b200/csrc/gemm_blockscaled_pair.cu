@@ -431,7 +431,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         fence_proxy_async_smem();
-        uint8_t* base = dcode >= 0 ? p.scatter_base[(dcode >> 26) & 15] : nullptr;
+        // the codes were written by other ranks: one that names a destination or a row this
+        // launch was not given is refused and reported, never turned into an address
+        uint8_t* base = nullptr;
+        if (dcode >= 0) {
+          const int drank = dcode >> 26, drow = dcode & 0x03ffffff;
+          if (drank < p.scatter_count && drow < p.scatter_rows) base = p.scatter_base[drank];
+          else atomicOr(reinterpret_cast<unsigned int*>(p.status), 0x00C00000u);
+        }
         if (base) bulk_store_1d(base + ((size_t)(dcode & 0x03ffffff) * p.n + col0) * 2, rowaddr, 256);
         bulk_commit_group();
         continue;
@@ -524,13 +531,7 @@ template <int KIND, int STAGES, bool SFW, bool SWIGLU = false, bool SCATTER = fa
 static int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = PairSmem<STAGES, SFW, SCATTER>;
   auto kern = gemm_pair_kernel<KIND, STAGES, SFW, SWIGLU, SCATTER>;
-  static bool configured[64] = {false};
-  int dev = 0;
-  MSC_CUDA_OK(cudaGetDevice(&dev));
-  if (!configured[dev & 63]) {
-    MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
-    configured[dev & 63] = true;
-  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kAlloc)) return rc;
   // programmatic stream serialization: this kernel's set-up may overlap the tail of the kernel
   // before it in the stream (it waits for that kernel before touching global memory)
   cudaLaunchAttribute attr[1];

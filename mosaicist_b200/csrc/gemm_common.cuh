@@ -21,6 +21,7 @@ struct GemmParams {
   __nv_bfloat16* out;        // [rows_total][n]
   int* status;
   int l, m_stride, n;
+  int rows_total;            // rows of a_q / out: no group may reach beyond them
   int k_stages;              // ceil(k_bytes / 128)
   int sf_chunks;             // scale chunks along K per 128-row tile
   int raster;
@@ -32,6 +33,8 @@ struct GemmParams {
   // code = row_dest[r]; negative codes are skipped
   const int* row_dest;       // [rows_total] or null
   uint8_t* scatter_base[16]; // unused entries are null: rows coded for them are skipped
+  int scatter_count;         // destinations in use; codes naming another one are refused
+  int scatter_rows;          // rows every destination holds; codes beyond them are refused
 #ifdef MSC_DEBUG
   unsigned long long* trace;  // [cta][8 tiles][3 roles][2] clock64 stamps, then [cta][2] at the end
   int debug_flags;            // 1: skip global stores, 2: skip scale loads/copies, 4: skip MMAs
@@ -74,6 +77,10 @@ struct TileCursor {
         if (p.m_stride > 0 && rows > p.m_stride) rows = p.m_stride;
         off = p.group_offsets ? __shfl_sync(0xffffffffu, __ldg(p.group_offsets + g), 0)
                               : g * p.m_stride;
+        // a group table that reaches beyond the buffers (an overflowing expert-parallel step,
+        // a stale table after a timed-out wait) is cut to what the buffers hold
+        if (off < 0 || off >= p.rows_total) rows = 0;
+        else if (rows > p.rows_total - off) rows = p.rows_total - off;
         mtiles = (rows + (1 << mshift) - 1) >> mshift;
         primed = true;
       }

@@ -500,6 +500,7 @@ extern "C" int msc_grouped_gemm_bf16_ragged(const void* a, const void* b, const 
   p.g.out = static_cast<__nv_bfloat16*>(out);
   p.g.l = l;
   p.g.m_stride = 0;
+  p.g.rows_total = rows_total;
   p.g.n = n;
   p.g.raster = 0;
   int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
@@ -509,13 +510,7 @@ extern "C" int msc_grouped_gemm_bf16_ragged(const void* a, const void* b, const 
   constexpr int kStages = 6;
   using L = DenseSmem<kStages>;
   auto kern = gemm_dense_f16_kernel<kStages, true>;
-  static bool configured[64] = {false};
-  int dev = 0;
-  MSC_CUDA_OK(cudaGetDevice(&dev));
-  if (!configured[dev & 63]) {
-    MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
-    configured[dev & 63] = true;
-  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kAlloc)) return rc;
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t lc =
       pdl_launch_config(2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream), attr);
@@ -562,6 +557,7 @@ extern "C" int msc_grouped_gemm_bf16_int4_ragged(const void* a, const void* b_q,
   p.g.out = static_cast<__nv_bfloat16*>(out);
   p.g.l = l;
   p.g.m_stride = 0;
+  p.g.rows_total = rows_total;
   p.g.n = n;
   p.g.raster = 0;
   int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
@@ -571,13 +567,7 @@ extern "C" int msc_grouped_gemm_bf16_int4_ragged(const void* a, const void* b_q,
   constexpr int kStages = 5;
   using L = DenseSmem<kStages, true>;
   auto kern = gemm_dense_f16_kernel<kStages, true, true>;
-  static bool configured[64] = {false};
-  int dev = 0;
-  MSC_CUDA_OK(cudaGetDevice(&dev));
-  if (!configured[dev & 63]) {
-    MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
-    configured[dev & 63] = true;
-  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kAlloc)) return rc;
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t lc =
       pdl_launch_config(2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream), attr);
@@ -620,13 +610,7 @@ extern "C" int msc_gemm_f16(const void* a, const void* b, void* c, int m, int n,
   constexpr int kStages = 6;
   using L = DenseSmem<kStages>;
   auto kern = gemm_dense_f16_kernel<kStages, false>;
-  static bool configured[64] = {false};
-  int dev = 0;
-  MSC_CUDA_OK(cudaGetDevice(&dev));
-  if (!configured[dev & 63]) {
-    MSC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
-    configured[dev & 63] = true;
-  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kAlloc)) return rc;
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t lc =
       pdl_launch_config(2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream), attr);

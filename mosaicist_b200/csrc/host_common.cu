@@ -6,7 +6,9 @@
 
 #include <mutex>
 #include <string>
+#include <set>
 #include <unordered_map>
+#include <utility>
 
 namespace msc {
 
@@ -36,6 +38,18 @@ int* status_word() {
     cached[dev] = static_cast<int*>(p);
   }
   return cached[dev];
+}
+
+int allow_dynamic_smem(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int dev = 0;
+  MSC_CUDA_OK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({kernel, dev})) return MSC_OK;
+  MSC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  done.insert({kernel, dev});
+  return MSC_OK;
 }
 
 EncodeTiledFn encode_tiled_fn() {

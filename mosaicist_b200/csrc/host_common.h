@@ -55,6 +55,10 @@ void clear_tmap_cache();
 
 int num_sms();
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device); safe to call from
+// several host threads.
+int allow_dynamic_smem(const void* kernel, int bytes);
+
 // Launch configuration with programmatic stream serialization: the kernel's set-up may overlap
 // the tail of its predecessor in the stream; the kernel calls grid_dependency_wait() before it
 // touches global memory.  `attr` must outlive the launch call.

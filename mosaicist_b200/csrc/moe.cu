@@ -347,6 +347,9 @@ int msc_moe_plan_noalloc(const int32_t* ids, int entries, int expert_first, int 
                      "experts_local=%d exceeds the %d experts the built-in scratch area holds; "
                      "use msc_moe_plan with caller-provided scratch",
                      experts_local, msc::kPlanStaticMaxExperts);
+  // refuse bad arguments before anything is enqueued on the stream
+  if (!ids || !rank || !group_offsets) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (entries <= 0 || experts_local <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
   int* scratch = nullptr;
   const int rc = msc::plan_scratch_address(&scratch);
   if (rc) return rc;

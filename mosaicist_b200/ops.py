@@ -26,10 +26,8 @@ class GemmConfig:
     sf_warps: int = 0
 
     def c(self, epilogue: int = _lib.EPI_PLAIN) -> _lib.GemmCfg:
-        cfg = _lib.GemmCfg(self.tile_n, self.stages, self.raster, self.max_ctas, epilogue,
-                           self.cta_pair)
-        cfg.reserved[0] = self.sf_warps
-        return cfg
+        return _lib.GemmCfg(self.tile_n, self.stages, self.raster, self.max_ctas, epilogue,
+                            self.cta_pair, self.sf_warps)
 
 
 def _ptr(t):

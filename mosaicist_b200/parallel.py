@@ -106,7 +106,10 @@ class ExpertParallelMoE:
         self._zero = torch.zeros((1,), dtype=torch.int32, device=layer.ids.device)
 
     def forward(self, tokens, logits):
-        """tokens (T_local, h) bf16, logits (T_local, experts_total) f32 -> (T_local, h) bf16."""
+        """tokens (T_local, h) bf16, logits (T_local, experts_total) f32 -> (T_local, h) bf16.
+        The result is defined only while the library's status word stays 0 (`_lib.status_word()`):
+        a step that overflowed a rank's rows_cap (bit 0x00E00000) drops the pairs that did not fit
+        from the sum, one whose wait for a peer ran out (0x00D00000) computed on incomplete data."""
         from . import _lib
 
         lib = _lib.load()
@@ -393,8 +396,10 @@ class PeerExpertParallelMoE:
         _lib.check(_lib.load().msc_grouped_gemm_nvfp4_scatter_ragged(
             L.d_q.data_ptr(), L.d_sf.data_ptr(), L.w2_q.data_ptr(), L.w2_sf.data_ptr(), L.alpha2.data_ptr(),
             L.group_offsets.data_ptr(), L.group_rows.data_ptr(), L.row_weight.data_ptr(),
-            self.row_dest.data_ptr(), self._ry, self.world, L.E, self.rows_cap, L.h, L.n,
-            L.config.c(), self._stream()))
+            self.row_dest.data_ptr(), self._ry, self.world, self.max_tokens * self.topk, L.E, self.rows_cap,
+            L.h, L.n, L.config.c(), self._stream()))
+        # rows nobody writes in the next step must not keep this step's destination
+        self.row_dest.fill_(-1)
 
     def combine(self, out=None):
         from . import _lib
@@ -403,8 +408,8 @@ class PeerExpertParallelMoE:
         if out is None:
             out = torch.empty((T, self.layer.h), dtype=torch.bfloat16, device=self.ids.device)
         if self.push:
-            _lib.check(_lib.load().msc_ep_sum_pairs(self.recv_y.data_ptr(), out.data_ptr(), T, self.layer.h,
-                                                    self.topk, self._stream()))
+            _lib.check(_lib.load().msc_ep_sum_pairs(self.recv_y.data_ptr(), self.pair_row.data_ptr(),
+                                                    out.data_ptr(), T, self.layer.h, self.topk, self._stream()))
             return out
         _lib.check(_lib.load().msc_ep_combine(self._y, self.ids.data_ptr(), self.pair_row.data_ptr(),
                                               out.data_ptr(), T, self.layer.h, self.topk, self.E,
@@ -412,7 +417,10 @@ class PeerExpertParallelMoE:
         return out
 
     def forward(self, tokens, logits, out=None):
-        """tokens (T_local, h) bf16, logits (T_local, experts_total) f32 -> (T_local, h) bf16."""
+        """tokens (T_local, h) bf16, logits (T_local, experts_total) f32 -> (T_local, h) bf16.
+        The result is defined only while the library's status word stays 0 (`_lib.status_word()`):
+        a step that overflowed a rank's rows_cap (bit 0x00E00000) drops the pairs that did not fit
+        from the sum, one whose wait for a peer ran out (0x00D00000) computed on incomplete data."""
         self.count(logits)
         if self.flag_sync:
             self.epoch += 1

@@ -1,26 +1,40 @@
-"""The profiling stage: every kernel of the library once under Nsight Compute, summarised as
+"""The profiling stage: the kernels of the library under Nsight Compute, summarised as
 tensor-pipe utilisation and DRAM GB/s per kernel.
 
 The reference pipeline has capture / time / converge stages and no profiling stage
 (src/mosaicist/cli.py; its timing comes from CUPTI activity records,
-src/mosaicist/backends/cuda.py).  This stage fills that slot for the kernels of this library:
+src/mosaicist/bench/cupti_trace.py).  This stage fills that slot for the kernels of this library:
 
-    python -m mosaicist_b200.profile_stage --out profiles/kernels_small_cases.md
+    python -m mosaicist_b200.profile_stage                       # launch list: every kernel's time
+    python -m mosaicist_b200.profile_stage --kernel gemm_pair_kernel --json profiles/rows.jsonl
+    python -m mosaicist_b200.profile_stage --in-kernel-clock     # SM clock inside the GEMM
 
-1. runs the workload once without the profiler (`--run`, this same module) and stops unless it
-   exits 0;
-2. runs it again under `ncu --clock-control none` with named metrics (duration, DRAM bytes
-   read / written, L2 -> SM bytes, DRAM and tensor-pipe utilisation, registers, active warps,
-   ten warp-stall reasons), limited to this library's kernels and `--launches` launches;
-3. folds the CSV into one row per kernel: launches, average duration, DRAM GB/s (bytes /
-   duration), DRAM % of peak, tensor pipe % of peak, registers per thread, the three largest
-   stall reasons (warps stalled per issue-active cycle) - as a markdown table and, with
-   `--json`, as one JSON object per kernel (the "machine" rows a capture bundle can carry).
+Every mode first runs the workload once without the profiler (`--run`, this same module) and
+stops unless it exits 0.  Then
 
-The workload is sized for a capture that ends by itself within a couple of minutes: operand
-sets of 0.1 - 1.5 GB (larger than L2, so DRAM figures mean something), one to three launches per
-kernel.  Durations under the profiler are serialised and cold-cache; they rank kernels and
-feed the GB/s column, they are not benchmark numbers.
+* without `--kernel`: one `ncu --clock-control none --metrics gpu__time_duration.sum` pass over
+  the library's kernels (a single-pass metric: nothing is replayed) -> launches, total and
+  average time per kernel;
+* with `--kernel NAME`: the named metrics (duration, DRAM bytes read / written, L2 -> SM bytes,
+  DRAM and tensor-pipe utilisation, registers, active warps, ten warp-stall reasons) for that
+  ONE kernel and at most `--launches` (default 3, never more than 5) launches of it, over the
+  part of the workload that launches it (`--section`, chosen from the name when omitted).  The
+  row is folded into `--json` (JSON lines keyed by kernel, the "machine" rows a capture
+  bundle can carry) and the markdown table `--out` is rebuilt from all rows collected so far.
+
+Each profiler run has a time limit (`--timeout`, default 600 s).  The workload is sized for
+captures that end by themselves: operand sets of 0.1 - 1.5 GB (larger than L2, so DRAM figures
+mean something).  Durations under the profiler are serialised and cold-cache; they rank
+kernels and feed the GB/s column, they are not benchmark numbers.
+
+`--in-kernel-clock` needs no profiler.  NVML's sampled SM clock stays at the maximum while a
+power-capped GPU lowers the clock inside a heavy kernel, so "fraction of the nominal peak"
+mixes kernel quality with power management.  The -DMSC_DEBUG build of the library
+(`python -m mosaicist_b200.build --debug`) stamps every CTA with clock64 (SM cycles) and the
+global nanosecond timer at the start and the end of its work; cycles / nanoseconds is the clock
+the kernel saw, and SMs x 16384 MAC/clk x 2 x clock the FP4 tensor peak at that clock (nominal:
+9 PFLOP/s dense, i.e. 1.86 GHz on 148 SMs).  The timed figure comes from the regular library
+(CUDA events, 30 launches); only the clock comes from the debug build, which is never timed.
 """
 
 from __future__ import annotations
@@ -28,6 +42,8 @@ from __future__ import annotations
 import argparse
 import csv
 import io
+import json
+import os
 import pathlib
 import shutil
 import subprocess
@@ -47,11 +63,23 @@ METRICS = [
 STALLS = ["long_scoreboard", "barrier", "wait", "short_scoreboard", "math_pipe_throttle", "mio_throttle",
           "lg_throttle", "sleeping", "membar", "branch_resolving"]
 STALL_METRICS = [f"smsp__average_warps_issue_stalled_{name}_per_issue_active.ratio" for name in STALLS]
-KERNEL_FILTER = "regex:gemm_|quantize|swizzle|moe_|ep_|route_|int4_"
+KERNEL_FILTER = "regex:gemm_|quantize|swizzle|moe_|ep_|route_|int4_|amax"
+SECTIONS = ("gemm", "mxfp8", "dense", "int4", "quantize", "moe", "ep")
+MAX_LAUNCHES = 5
 
 
-def run_workload():
-    """Launches every kernel of the library on a small representative case."""
+def section_of(kernel: str) -> str:
+    """The part of the workload that launches `kernel`."""
+    for key, sec in (("dense_f16", "dense"), ("int4", "int4"), ("ep_", "ep"), ("moe_", "moe"), ("route_", "moe"),
+                     ("quantize", "quantize"), ("swizzle", "quantize"), ("amax", "quantize"), ("gemm_", "gemm")):
+        if key in kernel:
+            return sec
+    return "all"
+
+
+def run_workload(section: str = "all"):
+    """Launches the library's kernels on small representative cases; `section` limits the run
+    to one family (SECTIONS)."""
     import numpy as np
     import torch
 
@@ -67,11 +95,15 @@ def run_workload():
     def u8(*shape, lo=0, hi=256):
         return torch.randint(lo, hi, shape, dtype=torch.uint8, device=dev, generator=g)
 
+    want = lambda name: section in ("all", name)
+
     # NVFP4 grouped GEMM: the headline shape (pair, single-CTA 128- and 256-column tiles) and a
     # compute-bound shape
     for (l, m, n, k), cfgs in [((8, 512, 2048, 2048), [ops.GemmConfig(), ops.GemmConfig(tile_n=128),
                                                         ops.GemmConfig(tile_n=256)]),
                                ((1, 4096, 4096, 8192), [ops.GemmConfig()])]:
+        if not want("gemm"):
+            break
         a_q, b_q = u8(l, m, k // 2), u8(l, n, k // 2)
         a_sf = u8(l, m // 128, k // 64, 32, 16, lo=0x30, hi=0x40)
         b_sf = u8(l, n // 128, k // 64, 32, 16, lo=0x30, hi=0x40)
@@ -82,34 +114,48 @@ def run_workload():
     rows = [1024, 512, 256, 128, 640, 384, 896, 256]
     offs = np.concatenate([[0], np.cumsum(rows)[:-1]]).astype(np.int32)
     tot, nn, kk = int(sum(rows)), 4096, 7168
-    ops.ragged_grouped_gemm_mxfp8(u8(tot, kk) & 0x77, u8(tot // 128, kk // 128, 32, 16, lo=120, hi=130),
-                                  u8(len(rows), nn, kk) & 0x77,
-                                  u8(len(rows), nn // 128, kk // 128, 32, 16, lo=120, hi=130),
-                                  torch.from_numpy(offs).to(dev), torch.tensor(rows, dtype=torch.int32, device=dev))
+    if want("mxfp8"):
+        ops.ragged_grouped_gemm_mxfp8(u8(tot, kk) & 0x77, u8(tot // 128, kk // 128, 32, 16, lo=120, hi=130),
+                                      u8(len(rows), nn, kk) & 0x77,
+                                      u8(len(rows), nn // 128, kk // 128, 32, 16, lo=120, hi=130),
+                                      torch.from_numpy(offs).to(dev),
+                                      torch.tensor(rows, dtype=torch.int32, device=dev))
 
     # dense fp16 GEMM
-    a = torch.randn((4096, 4096), device=dev, generator=g).half()
-    b = torch.randn((4096, 4096), device=dev, generator=g).half()
-    ops.gemm_f16(a, b)
+    if want("dense"):
+        a = torch.randn((4096, 4096), device=dev, generator=g).half()
+        b = torch.randn((4096, 4096), device=dev, generator=g).half()
+        ops.gemm_f16(a, b)
 
     # bf16 x int4 grouped GEMM (dequantise + bf16 grouped GEMM)
     rows = [256, 128, 384, 512, 128, 256, 256, 128]
     offs = np.concatenate([[0], np.cumsum(rows)[:-1]]).astype(np.int32)
     tot, nn, kk = int(sum(rows)), 2048, 7168
-    x = torch.randn((tot, kk), device=dev, generator=g).bfloat16()
-    sc = (torch.randn((len(rows), nn, kk // 128), device=dev, generator=g) * 0.02).abs().bfloat16()
-    ops.mixed_grouped_gemm_int4(x, u8(len(rows), nn, kk // 2), sc, torch.from_numpy(offs).to(dev),
-                                torch.tensor(rows, dtype=torch.int32, device=dev))
+    if want("int4"):
+        x = torch.randn((tot, kk), device=dev, generator=g).bfloat16()
+        sc = (torch.randn((len(rows), nn, kk // 128), device=dev, generator=g) * 0.02).abs().bfloat16()
+        ops.mixed_grouped_gemm_int4(x, u8(len(rows), nn, kk // 2), sc, torch.from_numpy(offs).to(dev),
+                                    torch.tensor(rows, dtype=torch.int32, device=dev))
 
     # quantiser, SiLU*up quantiser, scale swizzle
-    h = torch.randn((8, 2048, 7168), device=dev, generator=g).bfloat16()
-    gs = torch.full((8,), 448.0, dtype=torch.float32, device=dev)
-    ops.quantize_nvfp4(h, gs)
-    ops.silu_mul_quantize_nvfp4(h[:, :, :4096].contiguous(), gs)
-    ops.to_mma_scale_layout(u8(8, 2048, 448))
+    if want("quantize"):
+        h = torch.randn((8, 2048, 7168), device=dev, generator=g).bfloat16()
+        gs = torch.full((8,), 448.0, dtype=torch.float32, device=dev)
+        ops.quantize_nvfp4(h, gs)
+        ops.silu_mul_quantize_nvfp4(h[:, :, :4096].contiguous(), gs)
+        ops.to_mma_scale_layout(u8(8, 2048, 448))
+        if hasattr(ops, "global_scale_for"):
+            ops.global_scale_for(h)
+        if hasattr(ops, "quantize_mxfp8"):
+            ops.quantize_mxfp8(h.view(-1, 7168))
 
     # routed MoE layer: route, plan, gather + quantise, fused GEMM1, GEMM2, combine; then the
     # unfused GEMM1 pair
+    if not (want("moe") or want("ep")):
+        torch.cuda.synchronize()
+        if _lib.status_word() != 0:
+            raise RuntimeError("a kernel reported an error status")
+        return
     E, k, hid, inter, T = 64, 8, 7168, 2048, 4096
     w = rand_weights(E, inter, hid, dev, 3)
     gs_in = torch.full((E,), 2688.0 / 5.0, dtype=torch.float32, device=dev)
@@ -117,16 +163,17 @@ def run_workload():
     tokens = torch.randn((T, hid), device=dev, generator=g).bfloat16()
     logits = torch.randn((T, E), device=dev, generator=g)
     layer = MegaMoE(*w, gs_in, gs_a2, topk=k, max_tokens=T)
-    layer.forward(tokens, logits)
-    ops.quantize_nvfp4_ragged(layer.gateup, layer.a2_gs, layer.group_offsets, layer.group_rows, silu=True,
-                              out=(layer.d_q, layer.d_sf))
+    if want("moe"):
+        layer.forward(tokens, logits)
+        ops.quantize_nvfp4_ragged(layer.gateup, layer.a2_gs, layer.group_offsets, layer.group_rows, silu=True,
+                                  out=(layer.d_q, layer.d_sf))
 
     # expert-parallel exchange kernels: two ranks' layers on this one device in lockstep, once
     # with the combine pulled from the owners' results and once pushed by the GEMM2 epilogue
     del layer
     world, el, T2 = 2, E // 2, T // 2
     rows_cap = (T2 * k + 127 * el + 127) // 128 * 128
-    for push in (False, True):
+    for push in ((False, True) if want("ep") else ()):
         pairs_cap = T2 // 2 * k if push else 0
         _, total = exchange_layout(rows_cap, hid, pairs_cap, world, E)
         spaces = [exchange_views(torch.zeros(total, dtype=torch.uint8, device=dev), rows_cap, hid, pairs_cap, world, E)
@@ -200,43 +247,187 @@ def summarise(csv_text: str) -> str:
     return "\n".join(out)
 
 
+def launch_list(csv_text: str) -> str:
+    """The single-metric pass as a markdown table: launches, total and average time, share."""
+    rows = kernel_rows(csv_text)
+    total = sum(r["avg_us"] * r["launches"] for r in rows) or 1.0
+    out = ["| kernel | launches | total us | share | avg us |", "|---|---|---|---|---|"]
+    for r in rows:
+        t = r["avg_us"] * r["launches"]
+        out.append(f"| {r['kernel']} | {r['launches']} | {t:.1f} | {100 * t / total:.1f} % | {r['avg_us']:.2f} |")
+    return "\n".join(out)
+
+
+def table_from_rows(rows: list[dict]) -> str:
+    out = ["| kernel | launches | avg us | DRAM read MB | DRAM write MB | DRAM GB/s | DRAM % peak | tensor pipe % | regs | warps active % | L2->SM MB | top stalls (warps per issue-active cycle) |",
+           "|---|---|---|---|---|---|---|---|---|---|---|---|"]
+    for r in sorted(rows, key=lambda r: -r["avg_us"]):
+        stalls = ", ".join(f"{t['reason']} {t['warps_per_issue_active']:.1f}" for t in r["top_stalls"])
+        out.append(f"| {r['kernel']} | {r['launches']} | {r['avg_us']:.1f} | {r['dram_read_bytes'] / 1e6:.2f} | "
+                   f"{r['dram_write_bytes'] / 1e6:.2f} | {r['dram_gbs']:.0f} | {r['dram_pct_of_peak']:.1f} | "
+                   f"{r['tensor_pipe_pct_of_peak']:.1f} | {r['registers_per_thread']:.0f} | {r['warps_active_pct']:.1f} | "
+                   f"{r['l2_to_sm_bytes'] / 1e6:.1f} | {stalls} |")
+    return "\n".join(out)
+
+
+# ---- the SM clock inside the GEMM (--in-kernel-clock) ------------------------------------------
+CLOCK_SHAPES = [(1, 8192, 8192, 8192), (8, 2048, 4096, 7168), (8, 512, 2048, 2048)]
+MAC_PER_CLK_PER_SM_FP4 = 16384
+
+
+def _clock_operands(l, m, n, k, dev):
+    import torch
+
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def u8(*shape, lo=0, hi=256):
+        return torch.randint(lo, hi, shape, dtype=torch.uint8, device=dev, generator=g)
+
+    return (u8(l, m, k // 2), u8(l, m // 128, k // 64, 32, 16, lo=0x30, hi=0x40), u8(l, n, k // 2),
+            u8(l, n // 128, k // 64, 32, 16, lo=0x30, hi=0x40),
+            torch.empty((l, m, n), dtype=torch.bfloat16, device=dev))
+
+
+def _clock_child():
+    """Runs under the debug library (MSC_LIB_PATH): prints {shape: median SM MHz inside the kernel}."""
+    import ctypes
+
+    import numpy as np
+    import torch
+
+    from . import _lib, ops
+
+    lib = _lib.load()
+    lib.msc_debug_config.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    dev = torch.device("cuda", 0)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    res = {}
+    for shape in CLOCK_SHAPES:
+        a_q, a_sf, b_q, b_sf, out = _clock_operands(*shape, dev)
+        cfg = ops.GemmConfig(cta_pair=1)
+        trace = torch.zeros(sms * 50 + sms * 32, dtype=torch.int64, device=dev)
+        for _ in range(20):                               # reach the steady power state
+            ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, None, None, cfg, out=out)
+        lib.msc_debug_config(trace.data_ptr(), 0)
+        for _ in range(5):                                # the last launch's stamps remain
+            ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, None, None, cfg, out=out)
+        torch.cuda.synchronize()
+        lib.msc_debug_config(None, 0)
+        t = trace.cpu().numpy()
+        cyc = t[sms * 48: sms * 50].reshape(sms, 2)
+        ns = t[sms * 50:].reshape(sms, 32)[:, 30:32]
+        dc, dt = (cyc[:, 1] - cyc[:, 0]).astype(float), (ns[:, 1] - ns[:, 0]).astype(float)
+        ok = (dt > 0) & (dc > 0)
+        res["x".join(map(str, shape))] = float(np.median(dc[ok] / dt[ok] * 1e3))
+    print("CLOCKS " + json.dumps(res), flush=True)
+
+
+def in_kernel_clock():
+    import torch
+
+    from . import _lib, build, ops
+
+    debug_lib = build.build_debug()
+    env = dict(os.environ, MSC_LIB_PATH=str(debug_lib))
+    out = subprocess.run([sys.executable, "-m", "mosaicist_b200.profile_stage", "--clock-child"], env=env,
+                         capture_output=True, text=True, check=True, timeout=600).stdout
+    clocks = json.loads(next(ln for ln in out.splitlines() if ln.startswith("CLOCKS "))[7:])
+    dev = torch.device("cuda", 0)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for shape in CLOCK_SHAPES:
+        l, m, n, k = shape
+        a_q, a_sf, b_q, b_sf, o = _clock_operands(*shape, dev)
+        plan = ops.masked_grouped_gemm_plan(a_q, a_sf, b_q, b_sf, None, None, ops.GemmConfig(cta_pair=1), out=o)
+        for _ in range(10):
+            plan()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(30):
+            plan()
+        e.record()
+        torch.cuda.synchronize()
+        us = s.elapsed_time(e) * 1e3 / 30
+        tflops = 2.0 * l * m * n * k / us / 1e6
+        mhz = clocks["x".join(map(str, shape))]
+        peak = sms * MAC_PER_CLK_PER_SM_FP4 * 2 * mhz * 1e6 / 1e12
+        print(json.dumps({"shape_l_m_n_k": shape, "us": us, "tflops": tflops, "sm_mhz_in_kernel": mhz,
+                          "fp4_peak_at_that_clock_tflops": peak, "frac_of_peak_at_clock": tflops / peak,
+                          "frac_of_nominal_9000": tflops / 9000.0}), flush=True)
+    assert _lib.status_word() == 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--run", action="store_true", help="only launch the workload (what gets profiled)")
-    ap.add_argument("--out", default="profiles/kernels_small_cases.md")
-    ap.add_argument("--launches", type=int, default=80)
-    ap.add_argument("--json", default=None, help="also write the per-kernel rows as JSON lines to this file")
+    ap.add_argument("--section", default=None, choices=SECTIONS + ("all",),
+                    help="part of the workload to run (default: all, or the one --kernel belongs to)")
+    ap.add_argument("--kernel", default=None,
+                    help="capture the named metrics for this one kernel (substring of its name)")
+    ap.add_argument("--launches", type=int, default=3, help=f"launches of --kernel to capture (at most {MAX_LAUNCHES})")
+    ap.add_argument("--out", default=None, help="markdown file to write (default: print only)")
+    ap.add_argument("--json", default=None,
+                    help="JSON-lines file of per-kernel rows: this call's row replaces the one of the same kernel")
     ap.add_argument("--csv", default=None, help="summarise an existing ncu CSV log instead of profiling")
     ap.add_argument("--raw", default=str(pathlib.Path(tempfile.gettempdir()) / "profile_stage.csv"),
                     help="where ncu's CSV log goes")
+    ap.add_argument("--timeout", type=int, default=600, help="seconds each run may take")
+    ap.add_argument("--in-kernel-clock", action="store_true", help="SM clock inside the GEMM (debug build, no profiler)")
+    ap.add_argument("--clock-child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
-    if args.run:
-        run_workload()
+    if args.clock_child:
+        _clock_child()
         return
-    cmd = [sys.executable, "-m", "mosaicist_b200.profile_stage", "--run"]
-    ncu_cmd = ["ncu", "--clock-control", "none", "--metrics", ",".join(METRICS + STALL_METRICS), "-k", KERNEL_FILTER,
-               "-c", str(args.launches), "--print-units", "base", "--csv", "--log-file", args.raw, *cmd]
+    if args.in_kernel_clock:
+        in_kernel_clock()
+        return
+    section = args.section or (section_of(args.kernel) if args.kernel else "all")
+    if args.run:
+        run_workload(section)
+        return
+    cmd = [sys.executable, "-m", "mosaicist_b200.profile_stage", "--run", "--section", section]
+    if args.kernel:
+        launches = max(1, min(args.launches, MAX_LAUNCHES))
+        ncu_cmd = ["ncu", "--clock-control", "none", "--metrics", ",".join(METRICS + STALL_METRICS),
+                   "-k", f"regex:{args.kernel}", "-c", str(launches)]
+    else:
+        ncu_cmd = ["ncu", "--clock-control", "none", "--metrics", METRICS[0], "-k", KERNEL_FILTER, "-c", "400"]
+    ncu_cmd += ["--print-units", "base", "--csv", "--log-file", args.raw, *cmd]
     if args.csv is None:
         if shutil.which("ncu") is None:
             raise SystemExit("ncu is not on PATH")
-        subprocess.run(cmd, check=True)                  # must exit 0 before anything is profiled
+        subprocess.run(cmd, check=True, timeout=args.timeout)   # must exit 0 before anything is profiled
         pathlib.Path(args.raw).parent.mkdir(parents=True, exist_ok=True)
-        subprocess.run(ncu_cmd, check=True)
+        subprocess.run(ncu_cmd, check=True, timeout=args.timeout)
         text = pathlib.Path(args.raw).read_text()
     else:
         text = pathlib.Path(args.csv).read_text()
-    table = summarise(text)
-    if args.json:
-        import json
-
-        pathlib.Path(args.json).write_text("".join(json.dumps(r) + "\n" for r in kernel_rows(text)))
-    body = ("# Every kernel of the library under Nsight Compute, small cases\n\n"
-            "Made by `python -m mosaicist_b200.profile_stage` (plain run first, then\n`"
-            + " ".join(ncu_cmd[:-len(cmd)]) + " <same command>`).\n"
-            "Durations are under the profiler (serialised, cold caches): use them to rank kernels and for\n"
-            "the GB/s column, not as benchmark numbers.  DRAM GB/s = (read + write bytes) / duration.\n\n"
-            + table + "\n")
-    pathlib.Path(args.out).write_text(body)
+    shown = " ".join(ncu_cmd[:-len(cmd)]).replace(args.raw, "<log>") + " " + " ".join(["python", *cmd[1:]])
+    if not args.kernel:
+        body = ("# Launch list of the library's kernels, small cases\n\n"
+                "Made by `python -m mosaicist_b200.profile_stage` (plain run first, then\n`" + shown + "`).\n"
+                "Times are under the profiler (serialised, cold caches): compare shares, not absolutes.\n\n"
+                + launch_list(text) + "\n")
+    else:
+        rows = kernel_rows(text)
+        merged = {}
+        if args.json and pathlib.Path(args.json).exists():
+            for ln in pathlib.Path(args.json).read_text().splitlines():
+                if ln.strip():
+                    r = json.loads(ln)
+                    merged[r["kernel"]] = r
+        for r in rows:
+            merged[r["kernel"]] = r
+        if args.json:
+            pathlib.Path(args.json).write_text("".join(json.dumps(r) + "\n" for r in merged.values()))
+        body = ("# Kernels of the library under Nsight Compute, small cases\n\n"
+                "Made by `python -m mosaicist_b200.profile_stage --kernel <name>`, one kernel per call (plain run\n"
+                "first, then e.g. `" + shown + "`).\n"
+                "Durations are under the profiler (serialised, cold caches): use them to rank kernels and for\n"
+                "the GB/s column, not as benchmark numbers.  DRAM GB/s = (read + write bytes) / duration.\n\n"
+                + table_from_rows(list(merged.values())) + "\n")
+    if args.out:
+        pathlib.Path(args.out).write_text(body)
     print(body)
 
 

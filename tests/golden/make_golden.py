@@ -11,8 +11,10 @@ Two sources are executed, neither is copied:
 * `experiments/flashinfer-megamoe-sm100a/nvfp4.py` is "plain JAX" and JAX cannot be
   installed here, so the module is executed on top of a stand-in `jax` whose
   `jax.numpy` is numpy plus the ml_dtypes narrow floats (the same casts JAX uses) ->
-  nvfp4_golden.npz.  The stand-in only forwards names; all arithmetic statements that
-  run are the reference's.
+  nvfp4_golden.npz.  The stand-in only forwards names, with one exception: `jax.nn.sigmoid`
+  is written out here as 1 / (1 + exp(-x)) in float32, so the silu_mul vectors rest on this
+  file's statement of the sigmoid, not on JAX's; every other arithmetic statement that runs
+  is the reference's.
 
 The fixtures are small (a few KB) and are what tests/test_oracle_golden.py pins the
 oracle against.
@@ -150,7 +152,12 @@ def gate_golden(ref_root: pathlib.Path) -> dict:
 
 
 def main():
-    ref_root = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MOSAICIST_REFERENCE")
+    if not where:
+        raise SystemExit("usage: make_golden.py /path/to/reference  (or set MOSAICIST_REFERENCE)")
+    ref_root = pathlib.Path(where)
     np.savez_compressed(HERE / "nvfp4_golden.npz", **nvfp4_golden(ref_root))
     (HERE / "gate_golden.json").write_text(json.dumps(gate_golden(ref_root), indent=1))
     print("wrote", HERE / "nvfp4_golden.npz", HERE / "gate_golden.json")

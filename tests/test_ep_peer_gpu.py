@@ -152,6 +152,39 @@ def test_overflowing_rank_drops_rows_and_raises_the_status_bit():
         assert (rows == -1).any()
 
 
+def test_overflowing_push_layer_stays_inside_its_buffers_and_skips_dropped_pairs():
+    """The whole pushed layer with rows_cap far too small: the group tables are cut to rows_cap,
+    the GEMMs and the scatter stay inside the buffers, pairs that did not fit are left out of the
+    sum (their recv_y rows are pre-filled with NaN here, standing in for an earlier step's
+    data), and the status word says what happened."""
+    from mosaicist_b200 import _lib
+
+    world, E, k, h, n, T_loc = 2, 32, 2, 256, 128, 160
+    w = _weights(E, h, n, seed=2)
+    rng = np.random.default_rng(5)
+    tokens = [T(rng.standard_normal((T_loc, h)).astype(np.float32)).to(torch.bfloat16) for _ in range(world)]
+    logits = [T(rng.standard_normal((T_loc, E)).astype(np.float32)) for _ in range(world)]
+    gs = np.full(E, 2688.0 / 5.0, np.float32)
+    rows_cap = 256
+    ranks = _layers(world, E, k, h, n, T_loc, rows_cap, w, gs, gs, push=True)
+    for ep in ranks:
+        ep.recv_y.fill_(float("nan"))
+    outs, counts_all = _lockstep(ranks, tokens, logits)
+    torch.cuda.synchronize()
+    assert _lib.status_word() & 0x00E00000
+    for r, ep in enumerate(ranks):
+        assert int(ep.layer.total_rows[0]) <= rows_cap
+        table_end = (ep.layer.group_offsets + ep.layer.group_rows).max()
+        assert int(table_end) <= rows_cap
+        rows = ep.pair_row[:T_loc]
+        assert bool((rows < 0).any()) and bool((rows >= 0).any())
+        assert not bool(torch.isnan(outs[r]).any()), "a dropped pair's stale row entered the sum"
+        kept = (rows >= 0).any(dim=1)
+        assert bool((outs[r][kept].float().abs().sum(dim=1) > 0).all())
+        assert bool((outs[r][~kept] == 0).all())
+        assert bool((ep.row_dest == -1).all())     # reset for the next step
+
+
 def test_wait_without_signal_times_out_and_reports():
     """A flag nobody raises: the wait gives up after its limit, sets the status bit, and the
     context stays usable (the next kernel runs)."""

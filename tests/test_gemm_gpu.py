@@ -307,8 +307,8 @@ def test_scatter_epilogue_equals_store_then_permute(rows_list, n, k):
     a_qt, a_sft, b_qt, b_sft, o_t, r_t, al_t, rs_t = args
     _lib.check(_lib.load().msc_grouped_gemm_nvfp4_scatter_ragged(
         a_qt.data_ptr(), a_sft.data_ptr(), b_qt.data_ptr(), b_sft.data_ptr(), al_t.data_ptr(), o_t.data_ptr(),
-        r_t.data_ptr(), rs_t.data_ptr(), T(code).data_ptr(), bases, 2, l, tot, n, k, ops.GemmConfig().c(),
-        torch.cuda.current_stream().cuda_stream))
+        r_t.data_ptr(), rs_t.data_ptr(), T(code).data_ptr(), bases, 2, len(valid), l, tot, n, k,
+        ops.GemmConfig().c(), torch.cuda.current_stream().cuda_stream))
     assert _lib.status_word() == 0
     want = [torch.full_like(d, float("nan")) for d in dest]
     for row, slot, w, drop in zip(valid, slots, which, dropped):
@@ -317,6 +317,71 @@ def test_scatter_epilogue_equals_store_then_permute(rows_list, n, k):
     for d, w in zip(dest, want):
         assert torch.equal(d.view(torch.int16), w.view(torch.int16))
     assert int((~torch.isnan(dest[0])).sum() + (~torch.isnan(dest[1])).sum()) == int((~dropped).sum()) * n
+
+    # codes that name a destination or a row the call was not given are refused and reported:
+    # only one destination and half of its rows are declared, everything else must stay NaN
+    for d in dest:
+        d.fill_(float("nan"))
+    half = len(valid) // 2
+    _lib.check(_lib.load().msc_grouped_gemm_nvfp4_scatter_ragged(
+        a_qt.data_ptr(), a_sft.data_ptr(), b_qt.data_ptr(), b_sft.data_ptr(), al_t.data_ptr(), o_t.data_ptr(),
+        r_t.data_ptr(), rs_t.data_ptr(), T(code).data_ptr(), bases, 1, max(half, 1), l, tot, n, k,
+        ops.GemmConfig().c(), torch.cuda.current_stream().cuda_stream))
+    refused = (~dropped) & ((which != 0) | (slots >= max(half, 1)))
+    assert (_lib.status_word() == 0x00C00000) == bool(refused.any())
+    assert bool(torch.isnan(dest[1]).all())
+    want0 = torch.full_like(dest[0], float("nan"))
+    for row, slot, w, drop in zip(valid, slots, which, dropped):
+        if not drop and w == 0 and slot < max(half, 1):
+            want0[slot] = stored[row]
+    assert torch.equal(dest[0].view(torch.int16), want0.view(torch.int16))
+
+
+@pytest.mark.parametrize("cta_pair", [1, 2])
+def test_group_table_beyond_the_buffers_is_cut_not_followed(cta_pair):
+    """A group table that reaches past rows_total (what an overflowing expert-parallel step or a
+    stale table hands the GEMM): the kernels are told rows_total = 384 while every buffer really
+    holds 1024 rows, so the rows past 384 are a guard band inside the allocation.  The band must
+    stay untouched, rows below 384 must equal the honest call, for the plain store and the fused
+    SwiGLU epilogue alike."""
+    from mosaicist_b200 import _lib, ops
+
+    n, k, told, real = 256, 256, 384, 1024
+    rng = np.random.default_rng([21, cta_pair])
+    a_q, a_sf = O.exact_operands(rng, 1, real, k)
+    b_q, b_sf = O.exact_operands(rng, 3, n, k)
+    a_qt, a_sft = T(O.pack_e2m1(a_q[0])), T(O.e4m3_bytes(O.to_mma_scale_layout(a_sf[0])))
+    b_qt, b_sft = T(O.pack_e2m1(b_q)), T(O.e4m3_bytes(O.retile(b_sf)))
+    lib, st = _lib.load(), torch.cuda.current_stream().cuda_stream
+    # group 0 fits, group 1 straddles the end, group 2 starts beyond it (and one negative offset)
+    bad_off, bad_rows = T(np.array([0, 256, 640], np.int32)), T(np.array([200, 700, 300], np.int32))
+    ok_off, ok_rows = T(np.array([0, 256, 0], np.int32)), T(np.array([200, 128, 0], np.int32))
+    cfg = ops.GemmConfig(cta_pair=cta_pair).c()
+    outs = []
+    for off, rows in ((bad_off, bad_rows), (ok_off, ok_rows)):
+        out = torch.full((real, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        _lib.check(lib.msc_grouped_gemm_nvfp4_ragged(a_qt.data_ptr(), a_sft.data_ptr(), b_qt.data_ptr(),
+                                                     b_sft.data_ptr(), None, off.data_ptr(), rows.data_ptr(),
+                                                     None, out.data_ptr(), 3, told, n, k, cfg, st))
+        outs.append(out)
+    assert _lib.status_word() == 0
+    assert bool(torch.isnan(outs[0][told:]).all()), "rows past rows_total were written"
+    assert torch.equal(outs[0][:told].view(torch.int16), outs[1][:told].view(torch.int16))
+    assert int((~torch.isnan(outs[0][:told])).sum()) == (200 + 128) * n
+    if cta_pair == 1:
+        gs = T(np.full(3, 8.0, np.float32))
+        al = T(np.ones(3, np.float32))
+        res = []
+        for off, rows in ((bad_off, bad_rows), (ok_off, ok_rows)):
+            d_q = torch.full((real, n // 4), 0xEE, dtype=torch.uint8, device="cuda")
+            d_sf = torch.full((real // 128, n // 128, 32, 16), 0xEE, dtype=torch.uint8, device="cuda")
+            _lib.check(lib.msc_grouped_gemm_nvfp4_swiglu_ragged(
+                a_qt.data_ptr(), a_sft.data_ptr(), b_qt.data_ptr(), b_sft.data_ptr(), al.data_ptr(), off.data_ptr(),
+                rows.data_ptr(), gs.data_ptr(), d_q.data_ptr(), d_sf.data_ptr(), 3, told, n, k, cfg, st))
+            res.append((d_q, d_sf))
+        assert _lib.status_word() == 0
+        assert bool((res[0][0][told:] == 0xEE).all()) and bool((res[0][1][told // 128:] == 0xEE).all())
+        assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
 
 
 def test_shutdown_drops_cached_tensor_maps_and_the_next_call_rebuilds_them():
