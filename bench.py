@@ -6,10 +6,16 @@ A step is one grouped GEMM over one batch of synthetic operands (A, B ~ N(0,1) q
 e2m1 with e4m3 scales per 16 and a per-group global scale; alpha folds the global scales).
 Prints ONE JSON line (rank 0).  `value` is the whole-job TFLOP/s with operands resident in
 HBM; consecutive steps rotate over more operand sets than fit in L2, so every step reads
-its inputs from HBM.  `e2e` is the same metric through the public Python operator with the
-operands in pinned host memory: host->device copies and the device->host read of the result
-are inside the timed region.  `--impl reference` times the CPU restatement of the
-reference's float64 oracle on the host cores instead.
+its inputs from HBM.  Every timed launch is a CUDA-graph node whatever `--steps` is (a graph
+of one pass over the operand sets, replayed, plus a graph of the remainder); the K-step
+region is measured several times, each time between barriers, and the median is reported.
+`e2e` is the same metric through the public Python operator with the operands in pinned host
+memory: one packed host->device copy and the device->host read of the result are inside the
+timed region.  The line also carries a short measurement of the other benchmark
+configurations (`other_configs`) and of the routed MoE layer on the same ranks (`megamoe`),
+and `parity_sample`: a sampled block of the timed output checked against a float64 product
+of the same operand bytes.  `--impl reference` times the CPU restatement of the reference's
+float64 oracle on the host cores instead.
 """
 
 from __future__ import annotations
@@ -217,7 +223,8 @@ def run_reference(args, rank: int):
         return
     host_ops = host_operands_numpy(0)
     steps = max(1, min(args.steps, 40))       # one pass is ~0.5 s: bound the whole run
-    for _ in range(min(args.warmup, 2)):
+    warmup = max(0, min(args.warmup, 10))
+    for _ in range(warmup):
         cpu_pass(host_ops)
     t0 = time.perf_counter()
     for _ in range(steps):
@@ -226,9 +233,10 @@ def run_reference(args, rank: int):
     value = FLOP / dt / 1e12
     line = {
         "impl": "reference", "metric": "nvfp4_grouped_gemm_tflops", "value": value, "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "where": "host CPU"},
+        "data": "synthetic", "config": {"workload": WORKLOAD, "groups_per_gpu": L},
+        "how": {"where": "host CPU, float64 oracle port, BLAS on all cores"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
                          "sample": f"{steps} full passes of the float64 oracle, one operand set"},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -237,17 +245,75 @@ def run_reference(args, rank: int):
     print(json.dumps(line), flush=True)
 
 
+def parity_sample(operands, out, rows_per_group: int = 24):
+    """Rows of every group of one timed output against the float64 product of the same operand
+    bytes (dequantised on the host), under |err| <= 2^-7 |ref| + 1e-3 rms(ref).  Returns "ok" or
+    raises."""
+    import numpy as np
+    import torch
+
+    from mosaicist_b200.formats import dequant_nvfp4
+
+    a_q, a_sf, b_q, b_sf, alpha = (t.cpu().numpy() for t in operands)
+    rng = np.random.default_rng(5)
+    got_all = out.float().cpu().numpy()
+    worst = 0.0
+    for g in range(L):
+        rows = np.sort(rng.choice(M, rows_per_group, replace=False))
+        a = dequant_nvfp4(a_q[g], a_sf[g])[rows]
+        ref = (a @ dequant_nvfp4(b_q[g], b_sf[g]).T) * float(alpha[g])
+        err = np.abs(got_all[g][rows] - ref)
+        bound = 2.0 ** -7 * np.abs(ref) + 1e-3 * np.sqrt(np.mean(ref ** 2))
+        if np.count_nonzero(ref) < ref.size // 2:
+            raise SystemExit("parity sample is trivial: the reference block is mostly zero")
+        worst = max(worst, float((err / bound).max()))
+    if not worst <= 1.0:
+        raise SystemExit(f"parity sample failed: worst error / bound = {worst}")
+    return "ok"
+
+
+def bind_to_gpu_numa_node(index: int):
+    """Restricts this process to the CPUs of the NUMA node the GPU hangs off, so that pinned
+    host buffers allocated afterwards are local to the GPU's PCIe root.  Silent no-op where the
+    topology cannot be read."""
+    try:
+        import torch
+
+        bus = torch.cuda.get_device_properties(index).pci_bus_id
+        dom = torch.cuda.get_device_properties(index).pci_domain_id
+        dev = torch.cuda.get_device_properties(index).pci_device_id
+        path = pathlib.Path(f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node")
+        node = int(path.read_text())
+        if node < 0:
+            return None
+        cpus = pathlib.Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip()
+        ids = set()
+        for part in cpus.split(","):
+            lo, _, hi = part.partition("-")
+            ids.update(range(int(lo), int(hi or lo) + 1))
+        ids &= os.sched_getaffinity(0)
+        if ids:
+            os.sched_setaffinity(0, ids)
+        return node
+    except Exception:  # noqa: BLE001 - topology files are optional
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20000)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=200)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--cta-pair", type=int, default=0, help="0 auto, 1 CTA pairs, 2 single CTA")
     ap.add_argument("--e2e-steps", type=int, default=60)
+    ap.add_argument("--passes", type=int, default=0,
+                    help="how often the K-step region is measured (0: enough for about a second, at least 5)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true")
+    ap.add_argument("--no-megamoe", action="store_true")
     ap.add_argument("--cpu-baseline-configs", action="store_true",
                     help="only time the CPU oracle on sub-shapes of the other configurations and exit")
     args = ap.parse_args()
@@ -273,6 +339,7 @@ def main():
     _lib.load()
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    numa_node = bind_to_gpu_numa_node(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's banner goes to stderr, not stdout
@@ -282,6 +349,13 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     # Groups are independent, so every rank owns a full batch of 8 groups (weak scaling, no
     # data-path collective).  Rotate over enough operand sets that a step never finds its
@@ -298,43 +372,55 @@ def main():
     if _lib.status_word() != 0:
         raise SystemExit("a kernel reported a bounded-wait timeout")
 
-    # one CUDA graph = one pass over all operand sets (removes host launch gaps)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        for p in plans:
-            p()
-    step_i = 0
+    # Every timed launch is a graph node: one graph = one pass over all operand sets, a second
+    # one holds the steps % nsets launches that are left over, so no step is launched from Python.
+    def capture(count):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(count):
+                plans[i % nsets]()
+        return g
 
-    def run_steps(count):
-        nonlocal step_i
-        while count > 0:
-            if step_i % nsets == 0 and count >= nsets:
-                graph.replay()
-                count -= nsets
-                step_i += nsets
-            else:
-                plans[step_i % nsets]()
-                count -= 1
-                step_i += 1
+    full, rest = divmod(args.steps, nsets)
+    graph_full = capture(nsets)
+    graph_rest = capture(rest) if rest else None
 
-    run_steps(max(args.warmup, 3))
+    def run_steps():
+        for _ in range(full):
+            graph_full.replay()
+        if graph_rest is not None:
+            graph_rest.replay()
+
+    warm = max(args.warmup, 3)
+    for _ in range(-(-warm // nsets)):
+        graph_full.replay()
+    if graph_rest is not None:
+        graph_rest.replay()
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # one untimed pass tells how long a pass is; the K-step region is then measured `passes`
+    # times, each between barriers, with the clock sampler running across all of them
+    start.record()
+    run_steps()
+    stop.record()
+    barrier()
+    est_ms = max(start.elapsed_time(stop), 1e-3)
+    passes = args.passes if args.passes > 0 else int(min(max(5, 1000.0 / est_ms), 1500))
+    pass_ms = []
     with ClockSampler(local) as clocks:
         time.sleep(0.25)
-        barrier()
-        start.record()
-        run_steps(args.steps)
-        stop.record()
-        barrier()
+        for _ in range(passes):
+            barrier()
+            start.record()
+            run_steps()
+            stop.record()
+            barrier()
+            pass_ms.append(start.elapsed_time(stop))
         time.sleep(0.15)
-    ms_total = start.elapsed_time(stop)
-    if world > 1:
-        t = torch.tensor([ms_total], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+    ms_total = max_over_ranks(statistics.median(pass_ms))
     ms_per_step = ms_total / args.steps
     value = world * FLOP / (ms_per_step * 1e-3) / 1e12
+    best_ms_per_step = max_over_ranks(min(pass_ms)) / args.steps
 
     # warm-L2 figure (the reference's convention): the same operand set every launch
     g1 = torch.cuda.CUDAGraph()
@@ -349,16 +435,38 @@ def main():
     stop.record()
     torch.cuda.synchronize()
     warm_us = start.elapsed_time(stop) * 1e3 / (50 * nsets)
+    # what the device-resident path wrote for operand set 0: the end-to-end result must equal it
+    resident_out0 = outs[0].clone()
+    parity = parity_sample(sets[0], resident_out0) if rank == 0 else None
 
     # End to end through the public operator with host buffers: every step copies its packed
-    # operands from pinned host memory, runs the GEMM and copies the bf16 result back to pinned
-    # host memory.  The three phases run on three streams over double-buffered device and host
-    # buffers (copy-in of step i+1 and copy-out of step i-1 overlap the GEMM of step i, as an
-    # application streaming batches through the operator would do), so the steady state is the
-    # slower PCIe direction.
-    host = [tuple(t.cpu().pin_memory() for t in s) for s in sets[:2]]
+    # operands from pinned host memory (ONE buffer, one copy: values, scales and alphas at
+    # 256-byte aligned offsets), runs the GEMM on views of the device copy and copies the bf16
+    # result back to pinned host memory.  The three phases run on three streams over
+    # double-buffered device and host buffers (copy-in of step i+1 and copy-out of step i-1
+    # overlap the GEMM of step i, as an application streaming batches through the operator would
+    # do), so the steady state is the slower PCIe direction.
+    def packed_layout(tensors):
+        offs, at = [], 0
+        for t in tensors:
+            offs.append(at)
+            at = (at + t.numel() * t.element_size() + 255) // 256 * 256
+        return offs, at
+
+    offs, packed_bytes = packed_layout(sets[0])
+    host, dev_in, dev_views = [], [], []
+    for b in range(2):
+        hbuf = torch.empty(packed_bytes, dtype=torch.uint8).pin_memory()
+        for t, o in zip(sets[b], offs):
+            nb = t.numel() * t.element_size()
+            hbuf[o:o + nb].copy_(t.contiguous().view(-1).view(torch.uint8).cpu())
+        dbuf = torch.empty(packed_bytes, dtype=torch.uint8, device=device)
+        host.append(hbuf)
+        dev_in.append(dbuf)
+        dev_views.append([dbuf[o:o + t.numel() * t.element_size()].view(t.dtype).view(t.shape)
+                          for t, o in zip(sets[b], offs)])
     host_out = [torch.empty((L, M, N), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    dev_in = [[torch.empty_like(t, device=device) for t in host[0]] for _ in range(2)]
+    e2e_out = [torch.empty((L, M, N), dtype=torch.bfloat16, device=device) for _ in range(2)]
     s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(2)]      # inputs of the step using buffer b have landed
     ev_run = [torch.cuda.Event() for _ in range(2)]     # its GEMM has finished (inputs reusable, output ready)
@@ -369,15 +477,14 @@ def main():
         with torch.cuda.stream(s_in):
             if i >= 2:
                 s_in.wait_event(ev_run[b])
-            for d, h in zip(dev_in[b], host[b]):
-                d.copy_(h, non_blocking=True)
+            dev_in[b].copy_(host[b], non_blocking=True)
             ev_in[b].record(s_in)
         with torch.cuda.stream(s_run):
             s_run.wait_event(ev_in[b])
             if i >= 2:
                 s_run.wait_event(ev_out[b])
-            o = ops.masked_grouped_gemm(dev_in[b][0], dev_in[b][1], dev_in[b][2], dev_in[b][3], dev_in[b][4],
-                                        None, cfg, out=outs[b])
+            v = dev_views[b]
+            o = ops.masked_grouped_gemm(v[0], v[1], v[2], v[3], v[4], None, cfg, out=e2e_out[b])
             ev_run[b].record(s_run)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_run[b])
@@ -394,27 +501,50 @@ def main():
     for i in range(4):
         e2e_step(i)
     e2e_join()
-    barrier()
-    start.record()
-    for st in (s_in, s_run, s_out):
-        st.wait_stream(torch.cuda.current_stream())
-    for i in range(args.e2e_steps):
-        e2e_step(i)
-    e2e_join()
-    stop.record()
-    barrier()
-    e2e_ms = start.elapsed_time(stop) / args.e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    if not torch.equal(host_out[0], outs[0].cpu()):
+    e2e_passes = []
+    for _ in range(3):
+        barrier()
+        start.record()
+        for st in (s_in, s_run, s_out):
+            st.wait_stream(torch.cuda.current_stream())
+        for i in range(args.e2e_steps):
+            e2e_step(i)
+        e2e_join()
+        stop.record()
+        barrier()
+        e2e_passes.append(start.elapsed_time(stop) / args.e2e_steps)
+    e2e_ms = max_over_ranks(statistics.median(e2e_passes))
+    if not torch.equal(host_out[0], resident_out0.cpu()):
         raise SystemExit("the end-to-end path returned a different result than the device-resident one")
-    h2d = sum(t.numel() * t.element_size() for t in host[0])
+    h2d = packed_bytes
     d2h = host_out[0].numel() * host_out[0].element_size()
 
     if _lib.status_word() != 0:
         raise SystemExit("a kernel reported a bounded-wait timeout")
+    host_ops0 = tuple(t.cpu().numpy() for t in sets[0])
+    del sets, outs, plans, graph_full, graph_rest, g1, dev_in, dev_views, e2e_out, resident_out0
+    torch.cuda.empty_cache()
+
+    # the other benchmark configurations and the routed MoE layer, shortly, on the same ranks
+    other, megamoe = None, None
+    if not args.no_other_configs:
+        from mosaicist_b200 import bench_configs
+
+        try:
+            other = bench_configs.measure(8, rank, world, masked_moe=(world == 1))
+        except Exception as exc:  # noqa: BLE001 - the headline line must still be printed
+            other = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+        torch.cuda.empty_cache()
+    if not args.no_megamoe:
+        from mosaicist_b200 import bench_moe
+
+        try:
+            moe_args = bench_moe.parser().parse_args(["--gpus", str(world), "--steps", "20", "--warmup", "3"])
+            barrier()
+            megamoe = bench_moe.measure(moe_args, rank, world, local, detail=False)
+        except Exception as exc:  # noqa: BLE001
+            megamoe = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+        torch.cuda.empty_cache()
 
     if rank == 0:
         pk = peaks()
@@ -423,15 +553,18 @@ def main():
         per_gpu = value / world
         line = {
             "metric": "nvfp4_grouped_gemm_tflops", "value": value, "unit": "TFLOP/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "e2m1 x e2m1 -> f32 -> bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "groups_per_gpu": L,
-                       "kernel": ("single-CTA tiles 128x%d" % (cfg.tile_n or 128))
-                       if (cfg.cta_pair == 2 or cfg.tile_n) else "CTA-pair tiles 256x256 (cta_group::2)",
+            "config": {"workload": WORKLOAD, "groups_per_gpu": L},
+            "how": {   "kernel": ("single-CTA tiles 128x%d" % (cfg.tile_n or 128))
+                       if (cfg.cta_pair == 2 or cfg.tile_n) else "CTA pairs (cta_group::2), library default",
                        "l2": f"rotating over {nsets} operand sets ({nsets * ALGO_BYTES / 1e6:.0f} MB) "
                              f"> 126 MB L2: every step reads its operands from HBM",
-                       "launch": "CUDA graph of one pass over the operand sets"},
+                       "launch": f"CUDA graphs only: {full} replays of one pass over the operand sets"
+                                 + (f" + one graph of {rest} launches" if rest else ""),
+                       "timing": f"median of {passes} measurements of the {args.steps}-step region, "
+                                 f"each between barriers (best: {best_ms_per_step * 1e3:.2f} us/step)"},
             "per_gpu_tflops": per_gpu,
             "pct_fp4_peak_nominal_9pf": 100.0 * per_gpu / 9000.0,
             "pct_fp4_peak_4x_measured_bf16": 100.0 * per_gpu / fp4_derived,
@@ -441,22 +574,31 @@ def main():
             "roofline": {"bound": "hbm", "achieved": hbm_achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": hbm_achieved / pk["hbm_gbs"],
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this
-                         # workload under ncu (profiles/gemm_pair_nvfp4_c1.md): inputs are read
-                         # once, the output is still in L2 when the launch ends
-                         "traffic": 23.63e6 if not (cfg.cta_pair == 2 or cfg.tile_n) else 23.62e6,
+                         # workload under ncu (profiles/): inputs are read once, the output is
+                         # still in L2 when the launch ends
+                         "traffic": 23.63e6,
                          "peak_source": pk["source"],
                          "algorithmic_bytes_per_launch": ALGO_BYTES,
+                         "note": "achieved = algorithmic bytes (operands read once + output written once) / step "
+                                 "time; the DRAM traffic ncu sees is lower because the output is still in L2 when "
+                                 "a launch ends",
                          "tensor": {"achieved": per_gpu, "peak": fp4_derived, "unit": "TFLOP/s",
                                     "frac": per_gpu / fp4_derived,
                                     "peak_source": f"4 x {pk['source']} bf16 burst (no FP4 peak measured)"}},
             "e2e": {"value": world * FLOP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "overlap": "copy-in, GEMM and copy-out on three streams, double-buffered"},
+                    "overlap": "one packed copy-in, GEMM and copy-out on three streams, double-buffered",
+                    "numa_node_bound": numa_node},
             "gpu_launches": args.steps,
+            "parity_sample": parity,
             "clocks": clocks.summary(),
         }
+        if other is not None:
+            line["other_configs"] = other
+        if megamoe is not None:
+            line["megamoe"] = megamoe
         if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = cpu_baseline(tuple(t.numpy() for t in host[0]))
+            line["cpu_baseline"] = cpu_baseline(host_ops0)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -140,11 +140,22 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--vs-flashinfer", action="store_true")
     args = ap.parse_args()
-    from . import _lib, ops
-
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    out = measure(args.reps, rank, world, args.vs_flashinfer)
+    if rank == 0:
+        for line in out:
+            print(json.dumps(line), flush=True)
+
+
+def measure(reps: int, rank: int = 0, world: int = 1, vs_flashinfer: bool = False, masked_moe: bool = True) -> list:
+    """Times the configurations on the current device; returns one record per configuration."""
+    import types
+
+    from . import _lib, ops
+
+    args = types.SimpleNamespace(reps=reps, vs_flashinfer=vs_flashinfer)
     dev = torch.device("cuda", torch.cuda.current_device())
     pk = pathlib.Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
     bf16_peak = json.loads(pk.read_text())["bf16_tflops"] if pk.exists() else 1590.0
@@ -153,7 +164,7 @@ def main():
     out = []
     if args.vs_flashinfer and rank == 0:
         out.append(headline_vs_flashinfer(args.reps))
-    if rank == 0:
+    if rank == 0 and masked_moe:
         out.append(masked_moe_path(args.reps))
 
     # C2: dense fp16, this rank's column shard
@@ -212,9 +223,7 @@ def main():
                 "ms_two_launches": ms_two, "ms_bf16_gemm_only": ms_gemm, "tflops_bf16_gemm_only": fl / ms_gemm / 1e9,
                 "pct_measured_bf16_peak": 100 * fl / ms_fused / 1e9 / bf16_peak})
     assert _lib.status_word() == 0
-    if rank == 0:
-        for line in out:
-            print(json.dumps(line), flush=True)
+    return out
 
 
 if __name__ == "__main__":

@@ -34,7 +34,7 @@ def rand_weights(E, n, h, dev, seed):
     return w1_q, w1_sf, one * 64, one, w2_q, w2_sf, one * 64, one
 
 
-def main():
+def parser():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--tokens", type=int, default=8192)
@@ -51,23 +51,39 @@ def main():
                     help="peer exchange: synchronise through flags in peer memory / NCCL collectives")
     ap.add_argument("--combine", choices=["push", "pull"], default="push",
                     help="peer exchange: GEMM2 scatters result rows to the home ranks / the home rank pulls them")
-    args = ap.parse_args()
+    return ap
 
+
+def main():
+    import torch.distributed as dist
+
+    args = parser().parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    out = measure(args, rank, world, local)
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def measure(args, rank: int, world: int, local: int, detail: bool = True) -> dict:
+    """One timed run of the layer on `world` ranks (the process group, if any, is the
+    caller's); returns the record rank 0 prints.  detail=False leaves out the per-stage /
+    per-phase timings."""
     import torch.distributed as dist
 
     from . import _lib, ops
     from .moe import MegaMoE
     from .parallel import ExpertParallelMoE, PeerBuffers, PeerExpertParallelMoE
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=dev)
     E, k, h, n = args.experts, args.topk, args.hidden, args.inter
     E_loc, T_loc = E // world, args.tokens // world
     w = rand_weights(E_loc, n, h, dev, 17 + rank)
@@ -131,7 +147,7 @@ def main():
                        ("scattered to the home rank by the GEMM2 epilogue" if args.combine == "push" else
                         "pulled from peer memory") + f", sync by {args.sync}")}}
 
-    if world == 1:
+    if world == 1 and detail:
         # per-stage device times on one GPU
         lib = _lib.load()
         L = layer
@@ -169,7 +185,7 @@ def main():
             per[name] = s.elapsed_time(e) * 1e3 / 5
         out["stage_us"] = per
         out["rows"] = int(L.total_rows[0])
-    if world > 1 and args.exchange == "peer":
+    if world > 1 and args.exchange == "peer" and detail:
         # device time of each phase on this rank (waiting for slower ranks shows up in the barriers)
         L = layer
         from .parallel import SLOT_COUNTS, SLOT_RESULTS_READY, SLOT_ROWS_LANDED
@@ -209,12 +225,9 @@ def main():
         out["phase_us_rank0"] = acc
         out["rows_rank0"] = int(inner.total_rows[0])
         assert _lib.status_word() == 0
-    if rank == 0:
-        print(json.dumps(out), flush=True)
-    if world > 1:
-        if args.exchange == "peer":
-            bufs.close()
-        dist.destroy_process_group()
+    if world > 1 and args.exchange == "peer":
+        bufs.close()
+    return out
 
 
 if __name__ == "__main__":

@@ -59,24 +59,27 @@ def _inputs():
 
 
 def reference():
-    """float64 opinion on the same inputs: the layer with exact (unrounded) intermediates
-    except where the path itself quantises (the two NVFP4 quantisations are part of the
-    definition of the layer, so they are applied here too, on float64 values)."""
-    from ..formats import dequant_nvfp4
+    """float64 opinion on the same inputs, computed on the host from the raw inputs alone: no
+    kernel of this library takes part.  The layer's own definition is followed where it rounds
+    (experiments/flashinfer-megamoe-sm100a/nvfp4.py:91-108): the tokens are quantised to NVFP4
+    (nvfp4.py:39-57), GEMM1's result is a bf16 tensor, SiLU(gate) * up is fp32 (nvfp4.py:81-88)
+    and is quantised again; the two contractions are carried out in float64."""
+    from ..formats import bf16_round, dequant_nvfp4, quantize_nvfp4_values
 
     (hidden, w1_q, w1_sf, w1_gs, w1_alpha, w2_q, w2_sf, w2_gs, w2_alpha, masked_m, in_gs,
-     a2_gs) = _inputs()
-    from .. import ops
-
-    a_q, a_sf = ops.quantize_nvfp4(hidden, in_gs)
-    gateup = ops.masked_grouped_gemm(a_q, a_sf, w1_q, w1_sf, (w1_alpha / (in_gs * w1_gs)).contiguous(),
-                                     masked_m)
-    d_q, d_sf = ops.silu_mul_quantize_nvfp4(gateup, a2_gs, masked_m)
+     a2_gs) = (t.float().cpu().numpy() if t.is_floating_point() else t.cpu().numpy() for t in _inputs())
+    a_q, a_sf = quantize_nvfp4_values(hidden, in_gs)
+    a = a_q * np.repeat(a_sf, 16, axis=-1)
+    alpha1 = w1_alpha.astype(np.float64) / (in_gs.astype(np.float64) * w1_gs)
+    alpha2 = w2_alpha.astype(np.float64) / (a2_gs.astype(np.float64) * w2_gs)
     out = np.empty((L, M, K), np.float64)
-    d_qh, d_sfh, w2_qh, w2_sfh = (t.cpu().numpy() for t in (d_q, d_sf, w2_q, w2_sf))
-    scale = (w2_alpha / (a2_gs * w2_gs)).double().cpu().numpy()
     for g in range(L):
-        out[g] = dequant_nvfp4(d_qh[g], d_sfh[g]) @ dequant_nvfp4(w2_qh[g], w2_sfh[g]).T * scale[g]
+        gateup = bf16_round((a[g] @ dequant_nvfp4(w1_q[g], w1_sf[g]).T) * alpha1[g])
+        gate, up = gateup[:, :N], gateup[:, N:]
+        act = (np.float32(1.0) / (np.float32(1.0) + np.exp(-gate))) * gate * up          # fp32
+        d_q, d_sf = quantize_nvfp4_values(act[None], a2_gs[g:g + 1])
+        d = d_q[0] * np.repeat(d_sf[0], 16, axis=-1)
+        out[g] = (d @ dequant_nvfp4(w2_q[g], w2_sf[g]).T) * alpha2[g]
     return out
 
 

@@ -1,8 +1,9 @@
-"""Byte-level decoders for the narrow formats the library consumes, on numpy.
+"""Byte-level decoders for the narrow formats the library consumes, and the NVFP4 quantiser
+stated on numpy.
 
 Used by the capture modules' `reference()` hooks (the float64 opinion Mosaicist's numerics
 gate asks every module for, src/mosaicist/capture.py:254-264) and by host-side input
-preparation.  Nothing here runs on the hot path.
+preparation.  Nothing here runs on the hot path and no operator falls back to it.
 """
 
 from __future__ import annotations
@@ -55,3 +56,31 @@ def dequant_nvfp4(q_packed: np.ndarray, sf_tiled: np.ndarray) -> np.ndarray:
     rows = q.shape[0]
     sf = E4M3_LUT[from_mma_scale_layout(np.asarray(sf_tiled, np.uint8), rows)]
     return q * np.repeat(sf, 16, axis=-1)
+
+
+def quantize_nvfp4_values(x: np.ndarray, global_scale) -> tuple[np.ndarray, np.ndarray]:
+    """NVFP4 quantisation of (groups, rows, k) values as the layer defines it
+    (experiments/flashinfer-megamoe-sm100a/nvfp4.py:39-57), in float32 with the narrow casts
+    from ml_dtypes: sf = e4m3(clip(blockmax / 6 * gs, 0, 448)), step = f32(sf) / gs,
+    q = e2m1_rne(clip(x / step, -6, 6)), a block whose step is zero quantises to zero.
+    Returns the VALUES, not bytes: q (groups, rows, k) and sf (groups, rows, k/16) as float64,
+    so that q * repeat(sf, 16) is the dequantised operand a float64 reference multiplies."""
+    import ml_dtypes
+
+    f32 = np.float32
+    g, r, k = x.shape
+    xf = np.asarray(x, f32).reshape(g, r, k // 16, 16)
+    gs = np.asarray(global_scale, f32).reshape(g, 1, 1)
+    sf = np.clip(np.max(np.abs(xf), axis=-1) / f32(6.0) * gs, f32(0.0), f32(448.0)).astype(ml_dtypes.float8_e4m3fn)
+    step = sf.astype(f32) / gs
+    safe = np.where(step == 0.0, f32(1.0), step)
+    live = (step > 0.0).astype(f32)
+    q = np.clip(xf / safe[..., None] * live[..., None], f32(-6.0), f32(6.0)).astype(ml_dtypes.float4_e2m1fn)
+    return q.astype(np.float64).reshape(g, r, k), sf.astype(np.float64)
+
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """float64 / float32 values rounded to the nearest bfloat16 (ties to even), as float32."""
+    import ml_dtypes
+
+    return np.asarray(x, np.float32).astype(ml_dtypes.bfloat16).astype(np.float32)

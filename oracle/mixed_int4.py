@@ -4,7 +4,9 @@ Follows ports/hopper_mixed_dtype_grouped_gemm/problems.py:75-87: dequant(B)[n, k
 MmaType(Bq[n, k]) * scale[n, k // c] with the multiply carried out in the MMA type (bf16),
 D_g = alpha_g * A_g @ dequant(B_g)^T accumulated in fp32.  The reference checks its fp8
 variants against this formula bit for bit on small-integer inputs (check_matrix.py:12-22); it
-never ported int4 (README.md:95), so for int4 the formula is pinned, vectors are not.
+never ported int4 (README.md:95); its problems.py is plain torch and runs on the CPU, so
+tests/golden/make_golden.py executes its `dequant` and `reference` on int4-valued weights and
+tests/test_oracle_golden.py pins this file against those vectors (int4_golden.npz).
 """
 
 from __future__ import annotations

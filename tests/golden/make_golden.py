@@ -16,6 +16,11 @@ Two sources are executed, neither is copied:
   file's statement of the sigmoid, not on JAX's; every other arithmetic statement that runs
   is the reference's.
 
+* `ports/hopper_mixed_dtype_grouped_gemm/problems.py` (plain torch, runs on the CPU) is
+  imported as is; its `dequant` and `reference` are run on groups whose quantised weights are
+  int4 values held in int8, with bf16 group scales -> int4_golden.npz.  This pins
+  oracle/mixed_int4.py, which the reference itself never exercised with int4.
+
 The fixtures are small (a few KB) and are what tests/test_oracle_golden.py pins the
 oracle against.
 """
@@ -151,6 +156,37 @@ def gate_golden(ref_root: pathlib.Path) -> dict:
     return out
 
 
+def int4_golden(ref_root: pathlib.Path) -> dict:
+    """dequant() and reference() of the reference's mixed-dtype port on int4-valued weights."""
+    import torch
+
+    sys.path.insert(0, str(ref_root / "ports" / "hopper_mixed_dtype_grouped_gemm"))
+    import problems as P   # the reference module, executed unmodified
+
+    g = torch.Generator(device="cpu").manual_seed(7)
+    out = {}
+    # (m, n, k, scale group): small-integer activations as the reference's own generator draws
+    # them, then N(0,1) activations and |N(0, 0.02)| scales as the benchmark configuration has them
+    cases = [(24, 16, 256, 128, "ints"), (40, 32, 384, 128, "normal"), (8, 16, 128, 64, "normal")]
+    for i, (m, n, k, c, kind) in enumerate(cases):
+        if kind == "ints":
+            A = torch.randint(-2, 3, (m, k), generator=g).to(torch.bfloat16)
+            scale = (torch.randint(1, 5, (n, k // c), generator=g).to(torch.float32) / 4).to(torch.bfloat16)
+        else:
+            A = torch.randn((m, k), generator=g).to(torch.bfloat16)
+            scale = (torch.randn((n, k // c), generator=g) * 0.02).abs().to(torch.bfloat16)
+        Bq = torch.randint(-8, 8, (n, k), generator=g).to(torch.int8)
+        alpha = [1.0, 0.5, 2.0][i]
+        gp = P.Group(m, n, k, alpha, 0.0, A, Bq, scale, torch.zeros((m, n), dtype=torch.float16),
+                     torch.empty((m, n), dtype=torch.float16))
+        out.update({f"c{i}_A": A.float().numpy(), f"c{i}_Bq": Bq.numpy(), f"c{i}_scale": scale.float().numpy(),
+                    f"c{i}_c": np.int32(c), f"c{i}_alpha": np.float32(alpha),
+                    f"c{i}_dequant": P.dequant(gp).float().numpy(),
+                    f"c{i}_reference": P.reference(gp).float().numpy()})
+    out["cases"] = np.int32(len(cases))
+    return out
+
+
 def main():
     import os
 
@@ -160,7 +196,8 @@ def main():
     ref_root = pathlib.Path(where)
     np.savez_compressed(HERE / "nvfp4_golden.npz", **nvfp4_golden(ref_root))
     (HERE / "gate_golden.json").write_text(json.dumps(gate_golden(ref_root), indent=1))
-    print("wrote", HERE / "nvfp4_golden.npz", HERE / "gate_golden.json")
+    np.savez_compressed(HERE / "int4_golden.npz", **int4_golden(ref_root))
+    print("wrote", HERE / "nvfp4_golden.npz", HERE / "gate_golden.json", HERE / "int4_golden.npz")
 
 
 if __name__ == "__main__":

@@ -160,7 +160,9 @@ def test_unpermute_exact():
     assert np.array_equal(out.float().cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("l,m,k,n", [(2, 256, 512, 256), (3, 128, 512, 512)])     # test_kernels.py:94-95
+# the two shapes of test_kernels.py:94-95, then the shape the reference times end to end
+# (experiments/flashinfer-megamoe-sm100a/README.md:45-51)
+@pytest.mark.parametrize("l,m,k,n", [(2, 256, 512, 256), (3, 128, 512, 512), (8, 512, 2048, 1024)])
 def test_moe_masked_matches_reference_layer(l, m, k, n):
     from mosaicist_b200 import _lib
     from mosaicist_b200.moe import moe_masked

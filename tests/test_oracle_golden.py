@@ -190,3 +190,36 @@ def test_gate_verdicts_match_reference_vectors():
             assert got[1] == pytest.approx(w[1]) and got[2] == pytest.approx(w[2])
         seen.add(rep.passed)
     assert seen == {True, False}
+
+
+# --- the bf16 x int4 oracle against the reference's own dequant / reference ----------
+
+def test_int4_oracle_matches_reference_vectors():
+    """oracle/mixed_int4.py against outputs of the reference's
+    ports/hopper_mixed_dtype_grouped_gemm/problems.py (dequant :75-81, reference :84-87) run on
+    int4-valued weights (tests/golden/make_golden.py): the dequantised weights bit for bit, the
+    product within fp16 output rounding of the reference's fp32 accumulation."""
+    import ml_dtypes
+
+    from oracle import mixed_int4 as X4
+
+    gold = np.load(GOLD / "int4_golden.npz")
+    for i in range(int(gold["cases"])):
+        A, Bq, scale = gold[f"c{i}_A"], gold[f"c{i}_Bq"], gold[f"c{i}_scale"]
+        c, alpha = int(gold[f"c{i}_c"]), float(gold[f"c{i}_alpha"])
+        assert Bq.min() == -8 and Bq.max() == 7
+        w = X4.dequant(Bq, scale.astype(ml_dtypes.bfloat16), c)
+        assert np.array_equal(np.asarray(w, np.float32), gold[f"c{i}_dequant"]), i
+        # pack / unpack round trip of the byte layout the library consumes
+        packed = X4.pack_int4(Bq)
+        lo, hi = (packed & 0xF).astype(np.int8), (packed >> 4).astype(np.int8)
+        back = np.stack([lo, hi], axis=-1).reshape(Bq.shape)
+        assert np.array_equal(np.where(back >= 8, back - 16, back), Bq)
+        m = A.shape[0]
+        ref64 = X4.ragged_gemm_f64(A.astype(ml_dtypes.bfloat16), w[None], [0], [m], [alpha])
+        want = gold[f"c{i}_reference"].astype(np.float64)          # fp16(alpha * fp32 accumulation)
+        assert np.count_nonzero(want) > want.size // 2
+        err = np.abs(ref64 - want)
+        assert np.all(err <= 2.0 ** -10 * np.abs(ref64) + 1e-3 * np.sqrt(np.mean(ref64 ** 2)))
+        if i == 0:      # small integers and quarter scales: every product is exact, so are the sums
+            assert np.array_equal(ref64, want)
