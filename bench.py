@@ -104,10 +104,9 @@ def make_operands(seed: int, device):
     g = torch.Generator(device=device).manual_seed(seed)
     a = torch.randn((L, M, K), device=device, generator=g)
     b = torch.randn((L, N, K), device=device, generator=g)
-    a_gs = 2688.0 / a.abs().amax(dim=(1, 2))
-    b_gs = 2688.0 / b.abs().amax(dim=(1, 2))
-    a_q, a_sf = ops.quantize_nvfp4(a, a_gs.float().contiguous())
-    b_q, b_sf = ops.quantize_nvfp4(b, b_gs.float().contiguous())
+    a_gs, b_gs = ops.global_scale_for(a), ops.global_scale_for(b)      # 2688 / amax per group
+    a_q, a_sf = ops.quantize_nvfp4(a, a_gs)
+    b_q, b_sf = ops.quantize_nvfp4(b, b_gs)
     alpha = (1.0 / (a_gs * b_gs)).float().contiguous()
     return a_q, a_sf, b_q, b_sf, alpha
 

@@ -157,6 +157,34 @@ int msc_nvfp4_quantize_ragged(const void* x, int x_dtype, const float* global_sc
                               const int32_t* group_offsets, const int32_t* group_rows, void* q,
                               void* sf, int l, int rows_total, int k, int silu, void* stream);
 
+/* Per-group global scale of the NVFP4 quantiser: global_scale[g] = numerator / max|x[g]| over the
+ * elems_per_group contiguous elements of group g, a maximum of 0 counted as 1.  Replaces
+ * global_scale_for (experiments/flashinfer-megamoe-sm100a/nvfp4.py:29-36; numerator = 6 * 448 =
+ * 2688 there).  x bf16 (x_dtype 0) or fp32 (1), (l, elems_per_group); elems_per_group % 8 == 0.
+ * global_scale (l) fp32 doubles as the reduction's working array: it is cleared, receives the
+ * maxima and is then overwritten with the quotients, all on `stream`. */
+int msc_amax_global_scale(const void* x, int x_dtype, int l, long long elems_per_group, float numerator,
+                          float* global_scale, void* stream);
+
+/* MXFP8 quantisation (OCP Microscaling): q = e4m3, one ue8m0 scale byte per 32 K-elements,
+ *   scale = 2^e, e = the smallest integer with blockmax <= 448 * 2^e, clamped to [-127, 127]
+ *           (byte e + 127; a block of zeros gets byte 0),
+ *   q     = e4m3_rne(clip(x / scale, -448, 448)).
+ * The reference has no MXFP8 code; the structure is that of its block-scaled FP8 quantiser
+ * (experiments/flashinfer-megamoe-sm90a/quant.py:47-75: scale from the block maximum, q = x /
+ * scale clipped to the e4m3 range) with the MX scale rule and block size, and the kernel
+ * parallels the NVFP4 one (experiments/flashinfer-megamoe-sm100a/quantize_kernels.py:119-159).
+ *   x (rows, k) bf16 (x_dtype 0) or fp32 (1); q (rows, k) bytes; sf row-major (rows, k/32)
+ *   (sf_layout 0) or in the MMA tiling (ceil(rows/128), k/128, 32, 16) (sf_layout 1), the form
+ *   msc_grouped_gemm_mxfp8_ragged reads.  k % 128 == 0.
+ * The ragged form quantises only rows inside a group (group_offsets ascending, multiples of 128)
+ * and always writes tiled scales. */
+int msc_mxfp8_quantize(const void* x, int x_dtype, void* q, void* sf, int sf_layout, int rows, int k,
+                       void* stream);
+int msc_mxfp8_quantize_ragged(const void* x, int x_dtype, const int32_t* group_offsets,
+                              const int32_t* group_rows, void* q, void* sf, int l, int rows_total, int k,
+                              void* stream);
+
 /* Scale-factor re-tiling: (groups, mn, k_scales) row-major bytes -> (groups, ceil(mn/128),
  * k_scales/4, 32, 16) with zero padding rows; element (row = 128t + 32a + b, col = 4c + d)
  * lands at [t, c, b, 4a + d].  Replaces to_mma_scale_layout (nvfp4.py:121-131).  Works for

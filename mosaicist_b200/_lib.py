@@ -48,6 +48,9 @@ SIGNATURES = {
     "msc_nvfp4_silu_mul_quantize": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "msc_nvfp4_quantize_ragged": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "msc_sf_swizzle": (_I, [_P, _P, _I, _I, _I, _P]),
+    "msc_amax_global_scale": (_I, [_P, _I, _I, ctypes.c_longlong, ctypes.c_float, _P, _P]),
+    "msc_mxfp8_quantize": (_I, [_P, _I, _P, _P, _I, _I, _I, _P]),
+    "msc_mxfp8_quantize_ragged": (_I, [_P, _I, _P, _P, _P, _P, _I, _I, _I, _P]),
     "msc_gemm_f16": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "msc_int4_dequant_bf16": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
     "msc_grouped_gemm_bf16_ragged": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),

@@ -37,15 +37,11 @@ def _layout(rows):
 
 
 def _quantize(x):
-    """(rows, k) f32 -> e4m3 bytes (rows, k) and ue8m0 bytes (rows, k/32), on the device."""
-    import torch
+    """(rows, k) f32 -> e4m3 bytes (rows, k) and ue8m0 bytes (rows, k/32) row-major, by the
+    library's MXFP8 quantiser."""
+    from .. import ops
 
-    rows, k = x.shape
-    blocks = x.view(rows, k // 32, 32)
-    amax = blocks.abs().amax(dim=2)
-    exp = torch.ceil(torch.log2(torch.clamp(amax, min=2.0 ** -120) / 448.0)).clamp(-127, 127)
-    q = (blocks / torch.exp2(exp)[:, :, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
-    return q.view(rows, k).view(torch.uint8), (exp + 127).to(torch.uint8)
+    return ops.quantize_mxfp8(x.contiguous(), tiled_scales=False)
 
 
 def _inputs():

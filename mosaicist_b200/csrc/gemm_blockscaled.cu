@@ -469,15 +469,12 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   const int tile_n = cfg.tile_n ? cfg.tile_n : 128;
   if (tile_n != 128 && tile_n != 256)
     return fail(MSC_ERR_UNSUPPORTED, "tile_n must be 128 or 256, got %d", tile_n);
-  if (n % tile_n && cfg.cta_pair != 3)
-    return fail(MSC_ERR_BAD_ARG, "n=%d must be a multiple of tile_n=%d", n, tile_n);
+  if (n % tile_n) return fail(MSC_ERR_BAD_ARG, "n=%d must be a multiple of tile_n=%d", n, tile_n);
   const int chunk_elems = (kind == KIND_NVFP4) ? 64 : 128;
   if (k % chunk_elems)
     return fail(MSC_ERR_BAD_ARG, "k=%d must be a multiple of %d", k, chunk_elems);
-  if (cfg.cta_pair < 0 || cfg.cta_pair > 3)
-    return fail(MSC_ERR_BAD_ARG, "cta_pair must be 0 (auto), 1 (pair), 2 (single CTA) or 3 (balanced pair)");
-  if (cfg.cta_pair == 3 && kind != KIND_NVFP4)
-    return fail(MSC_ERR_UNSUPPORTED, "the balanced CTA-pair kernel is built for NVFP4");
+  if (cfg.cta_pair < 0 || cfg.cta_pair > 2)
+    return fail(MSC_ERR_BAD_ARG, "cta_pair must be 0 (auto), 1 (pair) or 2 (single CTA)");
   if (cfg.epilogue != MSC_EPI_PLAIN && cfg.epilogue != MSC_EPI_ROW_SCALE)
     return fail(MSC_ERR_UNSUPPORTED, "unknown epilogue %d", cfg.epilogue);
   if (cfg.epilogue == MSC_EPI_ROW_SCALE && !row_scale)
@@ -525,9 +522,6 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   p.debug_flags = g_debug_flags;
 #endif
 
-  if (cfg.cta_pair == 3)
-    return launch_bal_gemm(a_q, b_q, rows_total, k_bytes, p, cfg.stages, cfg.max_ctas,
-                           static_cast<cudaStream_t>(stream_v));
   // 0 = choose: pairs pay off when whole 256-row tiles are common and n allows 256-wide tiles
   bool pair = cfg.cta_pair == 1;
   if (cfg.cta_pair == 0 && cfg.tile_n == 0)

@@ -107,9 +107,4 @@ int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_
                      const GemmParams& p, int stages, int max_ctas, cudaStream_t stream,
                      bool sf_by_warps);
 
-// Launcher of the balanced CTA-pair kernel (gemm_blockscaled_bal.cu): NVFP4, plain or row-scaled
-// bf16 store.
-int launch_bal_gemm(const void* a_q, const void* b_q, long long rows_total, long long k_bytes,
-                    const GemmParams& p, int stages, int max_ctas, cudaStream_t stream);
-
 }  // namespace msc

@@ -71,8 +71,7 @@ namespace {
 struct TmapKey {
   const void* base;
   uint64_t rows, row_bytes;
-  uint32_t box_rows;  // bits 31-28: 2 bf16 store map, 1 unswizzled scale map, 3 unswizzled 32-byte box,
-                      // 4 bf16 store map with 32-column boxes (64-byte swizzle), 0 operand map
+  uint32_t box_rows;  // bits 31-28: 2 bf16 store map, 1 unswizzled scale map, 3 unswizzled 32-byte box, 0 operand map
   bool operator==(const TmapKey& o) const {
     return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows;
   }
@@ -132,11 +131,6 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
   return cached_tmap(map, base, rows, cols * 2, box_rows, 2);
 }
 
-int make_tmap_bf16_narrow_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                             uint32_t box_rows) {
-  return cached_tmap(map, base, rows, cols * 2, box_rows, 4);
-}
-
 int make_tmap_sf_2d(CUtensorMap* map, const void* base, uint64_t rows128, uint32_t box_rows) {
   return cached_tmap(map, base, rows128, 128, box_rows, 1);
 }
@@ -149,10 +143,9 @@ int make_tmap_narrow_2d(CUtensorMap* map, const void* base, uint64_t rows, uint6
 namespace {
 int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                    uint32_t box_rows, int flavour) {
-  const bool bf16 = flavour == 2 || flavour == 4;
+  const bool bf16 = flavour == 2;
   const bool swizzled = flavour == 0 || flavour == 2;
   const cuuint32_t box_bytes = flavour == 3 ? 32u : 128u;
-  const cuuint32_t bf16_box_cols = flavour == 4 ? 32u : 64u;
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return MSC_ERR_CUDA;
   if (reinterpret_cast<uintptr_t>(base) % 16 || row_bytes % 16)
@@ -161,13 +154,12 @@ int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t r
   // the box is 128 bytes wide (128 byte elements or 64 bf16 elements), 32 for the narrow flavour
   cuuint64_t dims[2] = {bf16 ? row_bytes / 2 : row_bytes, rows};
   cuuint64_t strides[1] = {row_bytes};
-  cuuint32_t box[2] = {bf16 ? bf16_box_cols : box_bytes, box_rows};
+  cuuint32_t box[2] = {bf16 ? 64u : box_bytes, box_rows};
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                    const_cast<void*>(base), dims, strides,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzled ? CU_TENSOR_MAP_SWIZZLE_128B
-                            : (flavour == 4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
+                   swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(MSC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);

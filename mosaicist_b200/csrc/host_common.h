@@ -35,11 +35,6 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
 int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                       uint32_t box_rows);
 
-// The same tensor with a [box_rows][32 columns = 64 B] box and 64-byte swizzle (the store map of
-// the kernel whose tiles are multiples of 64 columns wide).
-int make_tmap_bf16_narrow_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                             uint32_t box_rows);
-
 // 2-D byte tensor [rows][128 B] with a [box_rows][128 B] box, no swizzle: scale-factor chunks
 // (each 512-byte chunk is four such rows).
 int make_tmap_sf_2d(CUtensorMap* map, const void* base, uint64_t rows128, uint32_t box_rows);

@@ -220,6 +220,51 @@ def quantize_nvfp4_ragged(x, global_scale, group_offsets, group_rows, silu: bool
     return q, sf
 
 
+def global_scale_for(x, numerator: float = 2688.0, out=None):
+    """(l, ...) bf16/f32 -> (l,) f32: numerator / max|x[l]|, a maximum of 0 counted as 1 -
+    global_scale_for (nvfp4.py:29-36; 2688 = 6 * 448)."""
+    _need(x, "x", (torch.bfloat16, torch.float32))
+    l = x.shape[0]
+    per = x.numel() // l
+    if out is None:
+        out = torch.empty((l,), dtype=torch.float32, device=x.device)
+    else:
+        _need(out, "out", (torch.float32,), (l,))
+    _lib.check(_lib.load().msc_amax_global_scale(_ptr(x), 0 if x.dtype == torch.bfloat16 else 1, l, per,
+                                                 float(numerator), _ptr(out), _stream()))
+    return out
+
+
+def quantize_mxfp8(x, tiled_scales: bool = True, group_offsets=None, group_rows=None, out=None):
+    """(rows, k) bf16/f32 -> (q (rows, k) e4m3 bytes, sf ue8m0 bytes): one power-of-two scale per
+    32 K-elements, the smallest with blockmax / scale <= 448 (structure of the reference's
+    block-scaled FP8 quantiser, flashinfer-megamoe-sm90a/quant.py:47-75, with the MX scale rule).
+    Scales come out in the MMA tiling (ceil(rows/128), k/128, 32, 16) or row-major (rows, k/32).
+    With group_offsets / group_rows only rows inside a group are written (tiled scales)."""
+    _need(x, "x", (torch.bfloat16, torch.float32))
+    rows, k = x.shape
+    ragged = group_offsets is not None
+    if ragged and not tiled_scales:
+        raise ValueError("the ragged form writes tiled scales")
+    if out is None:
+        q = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+        shape = ((rows + 127) // 128, k // 128, 32, 16) if tiled_scales else (rows, k // 32)
+        sf = torch.zeros(shape, dtype=torch.uint8, device=x.device)
+    else:
+        q, sf = out
+    dt = 0 if x.dtype == torch.bfloat16 else 1
+    if ragged:
+        l = group_offsets.shape[0]
+        _need(group_offsets, "group_offsets", (torch.int32,), (l,))
+        _need(group_rows, "group_rows", (torch.int32,), (l,))
+        _lib.check(_lib.load().msc_mxfp8_quantize_ragged(_ptr(x), dt, _ptr(group_offsets), _ptr(group_rows),
+                                                         _ptr(q), _ptr(sf), l, rows, k, _stream()))
+    else:
+        _lib.check(_lib.load().msc_mxfp8_quantize(_ptr(x), dt, _ptr(q), _ptr(sf), 1 if tiled_scales else 0,
+                                                  rows, k, _stream()))
+    return q, sf
+
+
 def to_mma_scale_layout(sf):
     """(groups, mn, k_scales) row-major scale bytes -> (groups, ceil(mn/128), k_scales/4, 32, 16)
     (a 2-D input is treated as one group and returns 4-D), as to_mma_scale_layout

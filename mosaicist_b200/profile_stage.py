@@ -144,10 +144,8 @@ def run_workload(section: str = "all"):
         ops.quantize_nvfp4(h, gs)
         ops.silu_mul_quantize_nvfp4(h[:, :, :4096].contiguous(), gs)
         ops.to_mma_scale_layout(u8(8, 2048, 448))
-        if hasattr(ops, "global_scale_for"):
-            ops.global_scale_for(h)
-        if hasattr(ops, "quantize_mxfp8"):
-            ops.quantize_mxfp8(h.view(-1, 7168))
+        ops.global_scale_for(h)
+        ops.quantize_mxfp8(h.view(-1, 7168))
 
     # routed MoE layer: route, plan, gather + quantise, fused GEMM1, GEMM2, combine; then the
     # unfused GEMM1 pair

@@ -5,8 +5,9 @@ K-elements) code and no golden vectors for it.  The nearest reference arithmetic
 Hopper analog's block-scaled FP8 quantiser (experiments/flashinfer-megamoe-sm90a/
 quant.py:47-75: e4m3 values, e4m3 scale per 128, `q = x / scale` clipped to the e4m3
 range, dequant `q * scale`); this file keeps that structure and substitutes the OCP MX
-scale rule the benchmark configuration names: scale = 2^ceil(log2(blockmax / 448)) stored
-as ue8m0 (biased exponent byte, 2^(b - 127)).
+scale rule the benchmark configuration names: scale = 2^ceil(log2(blockmax / 448)), i.e. the
+smallest power of two with blockmax / scale <= 448, stored as ue8m0 (biased exponent byte,
+2^(b - 127)).
 """
 
 from __future__ import annotations
@@ -31,9 +32,11 @@ def quantize_mxfp8(x: np.ndarray):
         raise ValueError(f"K={k} must be a multiple of {BLOCK}")
     xb = x.reshape(*x.shape[:-1], k // BLOCK, BLOCK)
     amax = np.max(np.abs(xb), axis=-1)
-    with np.errstate(divide="ignore"):
-        e = np.ceil(np.log2(amax / E4M3_MAX))
-    e = np.where(amax > 0, e, -127.0)
+    # the smallest integer e with amax <= 448 * 2^e, found exactly: amax = m 2^E with
+    # 0.5 <= m < 1 (frexp), 448 = 0.875 * 2^9, so e = E - 9 + (m > 0.875); a logarithm in
+    # floating point would misplace block maxima within an ulp of 448 * 2^e
+    m, E = np.frexp(amax)
+    e = np.where(amax > 0, E - 9 + (m > 0.875), -127)
     e = np.clip(e, -127, 127).astype(np.int32)
     scale = np.ldexp(np.float32(1.0), e)
     q = np.clip(xb / scale[..., None], -E4M3_MAX, E4M3_MAX).astype(E4M3)

@@ -62,16 +62,6 @@ EXACT_CASES = [
     (5, 512, 768, 1280, {"cta_pair": 1, "max_ctas": 6}),
     # scale factors written into TMEM by dedicated warps (tcgen05.st) instead of tcgen05.cp
     (2, 512, 512, 576, {"cta_pair": 1, "sf_warps": 1}),
-    # the balanced CTA-pair kernel: runs of 64-column units, tiles of 64..256 columns that may
-    # start on an odd unit, two accumulators, one scale staging area
-    (1, 256, 256, 64, {"cta_pair": 3}),
-    (2, 512, 512, 576, {"cta_pair": 3}),
-    (3, 384, 384, 1024, {"cta_pair": 3, "stages": 2}),
-    (5, 512, 768, 1280, {"cta_pair": 3, "max_ctas": 6}),
-    (2, 256, 1152, 320, {"cta_pair": 3, "max_ctas": 10}),
-    (4, 640, 640, 192, {"cta_pair": 3, "max_ctas": 14}),
-    (8, 512, 2048, 256, {"cta_pair": 3}),      # the headline's schedule: 7 units per pair
-    (1, 128, 128, 64, {"cta_pair": 3}),
 ]
 
 
@@ -105,7 +95,7 @@ def test_edge_groups_empty_and_single_row():
     assert np.isnan(got[0]).all()
 
 
-@pytest.mark.parametrize("cfg", [{}, {"tile_n": 256}, {"cta_pair": 1}, {"cta_pair": 3}])
+@pytest.mark.parametrize("cfg", [{}, {"tile_n": 256}, {"cta_pair": 1}])
 def test_random_operands_within_tolerance_and_gate(cfg):
     """Seeded N(0,1) operands quantised by the oracle with gs = 64 (test_kernels.py:43-48)."""
     l, m, n, k = 2, 256, 256, 512
@@ -145,9 +135,6 @@ def test_headline_shape_properties():
     assert _lib.status_word() == 0
     assert torch.equal(o1.float() * 2, o2.float())        # power-of-two alpha is exact in bf16
     assert torch.equal(o1, o3)                            # every kernel variant, same bits
-    o4 = ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, one, None, ops.GemmConfig(cta_pair=3))
-    assert _lib.status_word() == 0
-    assert torch.equal(o1, o4)
     gi = 5
     rows = slice(128, 160)
     ref = dequant_nvfp4(a_q[gi].cpu().numpy(), a_sf[gi].cpu().numpy())[rows] @ \
@@ -203,11 +190,7 @@ def test_mxfp8_ragged_bit_exact(rows_list, n, k, cfg):
     assert np.isnan(got[~mask[:, 0]]).all()
 
 
-RAGGED_NVFP4 = RAGGED[1:] + [
-    ([200, 0, 50, 384, 257], 256, 1024, {"cta_pair": 3}),
-    ([1, 127, 129, 300, 5], 640, 640, {"cta_pair": 3, "max_ctas": 4}),
-    ([300, 513, 0, 64], 384, 320, {"cta_pair": 3, "max_ctas": 22}),
-]
+RAGGED_NVFP4 = RAGGED[1:]
 
 
 @pytest.mark.parametrize("rows_list,n,k,cfg", RAGGED_NVFP4)
