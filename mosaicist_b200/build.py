@@ -72,6 +72,30 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     return LIB
 
 
+CUPTI_SHIM = PKG / "cupti_shim" / "libmsc_cupti.so"
+
+
+def build_cupti_shim(force: bool = False) -> pathlib.Path | None:
+    """The small C++ library behind the stand-in `cupti` package (cupti_shim/): kernel activity
+    records from libcupti for the reference's tracer, where cupti-python is not installed.
+    Returns None (and builds nothing) where the toolkit's CUPTI headers or g++ are missing."""
+    src = PKG / "cupti_shim" / "cupti_shim.cpp"
+    if not force and CUPTI_SHIM.exists() and CUPTI_SHIM.stat().st_mtime >= src.stat().st_mtime:
+        return CUPTI_SHIM
+    gxx = shutil.which("g++")
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cuda = pathlib.Path(nvcc).resolve().parents[1]
+    if gxx is None or not (cuda / "include" / "cupti.h").exists():
+        return CUPTI_SHIM if CUPTI_SHIM.exists() else None
+    libdir = cuda / "lib64"
+    cmd = [gxx, "-O2", "-std=c++17", "-shared", "-fPIC", f"-I{cuda / 'include'}", "-o", str(CUPTI_SHIM), str(src),
+           f"-L{libdir}", "-lcupti", f"-Wl,-rpath,{libdir}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed on the CUPTI shim:\n" + res.stderr[-2000:])
+    return CUPTI_SHIM
+
+
 def build_debug(force: bool = False) -> pathlib.Path:
     """The -DMSC_DEBUG build (clock stamps, skip flags); returns its path."""
     deps = list(CSRC.glob("*")) + [PKG.parent / "include" / "mosaicist_sm100a.h"]
@@ -89,5 +113,6 @@ def build_debug(force: bool = False) -> pathlib.Path:
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose=True)
     print("built", path)
+    print("built", build_cupti_shim(force="--force" in sys.argv))
     if "--debug" in sys.argv:
         print("built", build_debug(force="--force" in sys.argv))

@@ -268,3 +268,34 @@ def test_bench_reference_arm_runs_on_the_cpu_and_prints_the_contract_line():
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["cpu_baseline"]["value"] == line["value"] > 0
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+
+
+@pytest.mark.parametrize("kernel,entry", [("pair", "gemm_pair_kernelILi0ELi5ELb0ELb0ELb0E"),
+                                          ("single", "gemm_blockscaled_kernelILi0ELi128ELi5E"),
+                                          ("dense", "gemm_dense_f16_kernelILi6ELb0ELb0E")])
+def test_reference_fingerprinter_accepts_the_dropped_ptx(kernel, entry, tmp_path, monkeypatch, lib):
+    """What a capture module leaves in the dump directory goes through the reference's own PTX
+    parser and fingerprinter (src/mosaicist/ptx/parse.py, features.py:151): it parses, its largest
+    entry is the instantiation that was asked for, and the fingerprint sees tensor-core and TMA
+    instructions."""
+    from oracle.stage_reference import staged_path
+
+    ref = staged_path()
+    if ref is None:
+        pytest.skip("the reference's package is neither staged (oracle/stage_reference.py) nor in MOSAICIST_REFERENCE")
+    monkeypatch.syspath_prepend(str(ref))
+    monkeypatch.setenv("MOSAIC_GPU_DUMP_TO", str(tmp_path))
+    from mosaicist.ptx.features import fingerprint
+    from mosaicist.ptx.parse import parse
+    from mosaicist_b200.candidates._common import drop_artifacts
+
+    drop_artifacts(kernel, entry)
+    files = list(tmp_path.glob("*.ptx"))
+    assert len(files) == 1
+    text = files[0].read_text()
+    mod = parse(text)
+    assert entry in mod.entry(None).name and mod.target == "sm_100a"
+    fp = fingerprint(text, ptxas_log=(tmp_path / "ptxas_mosaicist_sm100a.log").read_text())
+    ops = " ".join(i.opcode for i in mod.entry(None).instrs)
+    assert "tcgen05.mma" in ops and "cp.async.bulk.tensor" in ops
+    assert fp is not None
