@@ -107,6 +107,10 @@ def test_reference_capture_stage_drives_the_module(reference_capture, name, meas
     m = importlib.import_module(entry)
     fn, args = m.build()
     event_us = _event_us(fn, args)
-    # events include the launch gaps and, for the four-kernel layer, the time between kernels
+    # events around eager launches include the gaps between kernels: a lower bound on the CUPTI
+    # figure only makes sense for the single-kernel module (the four-kernel layer is bound by the
+    # host's launch rate when it is not replayed from a graph)
+    print(f"{name}: CUPTI {cupti_us:.2f} us per repetition ({measure}), CUDA events {event_us:.2f} us")
     assert cupti_us <= event_us * 1.10, (cupti_us, event_us)
-    assert cupti_us >= event_us * (0.60 if measure == "dominant" else 0.45), (cupti_us, event_us)
+    if measure == "dominant":
+        assert cupti_us >= event_us * 0.60, (cupti_us, event_us)
