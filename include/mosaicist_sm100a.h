@@ -198,7 +198,10 @@ int msc_sf_swizzle(const void* sf_rowmajor, void* sf_tiled, int groups, int mn, 
  * third-party Hopper wgmma code, this is a tcgen05 CTA-pair kernel with 256x256 tiles).
  * lda / ldb / ldc are row pitches in elements, so a column shard of B and C (the N-sharded
  * multi-GPU form) is the shard's base pointer with the parent's pitch.  k, n and the pitches
- * must be multiples of 8; m, n, k need not be tile multiples.  max_ctas 0 = one CTA per SM. */
+ * must be multiples of 8; m, n, k need not be tile multiples.  max_ctas 0 = one CTA per SM.
+ * Problems with enough columns run 256 x 512 tiles (two MMAs per K step share the A stage, so
+ * the kernel is bounded by the tensor pipe rather than by L2 -> SM traffic); a negative max_ctas
+ * forces the 256 x 256 form on |max_ctas| CTAs. */
 int msc_gemm_f16(const void* a, const void* b, void* c, int m, int n, int k, int lda, int ldb,
                  int ldc, int dtype, int max_ctas, void* stream);
 

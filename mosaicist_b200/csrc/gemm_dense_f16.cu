@@ -12,6 +12,14 @@
 // the main loop of the next.  Edges: TMA zero-fills loads and clips stores outside the
 // matrices, so M, N and K only need 16-byte alignment, not tile multiples.
 //
+// WIDE form (dense only, the default for matrices of at least 512 columns): the two
+// accumulators belong to ONE 256 x 512 tile, each K step is two MMAs that share the A stage.
+// A 256 x 256 tile moves 64 KB per 64-element K stage for 512 tensor-pipe cycles, 62 bytes per
+// clock and SM, which is what an SM can pull out of L2 when all of them do: that form is
+// bounded by the L2 -> SM fabric at about 90 % of the tensor peak.  The wide tile moves 96 KB
+// per 1024 cycles (47 B/clk), so the tensor pipe is the limit again; the price is that a tile's
+// drain is no longer hidden behind the next tile's main loop (1-2 % at K = 8192).
+//
 // The same kernel has a grouped form (GROUPED = true): A is a row-concatenated batch of groups
 // (group g owns rows [group_offsets[g], + group_rows[g]), offsets multiples of 128), B is
 // (groups, n, k) with K contiguous ("NT", what a weight matrix per group looks like), C is
@@ -37,11 +45,12 @@ struct DenseParams {
   GemmParams g;           // grouped form: group_rows / group_offsets / alpha / out / l / n
 };
 
-template <int STAGES, bool INT4 = false>
+template <int STAGES, bool INT4 = false, bool WIDE = false>
 struct DenseSmem {
   static constexpr int kHeader = 1024;
   static constexpr int kA = 128 * 128;       // 128 rows x 64 K-elements
-  static constexpr int kB = 2 * 64 * 128;    // two boxes of 64 K rows x 64 columns
+  static constexpr int kBHalf = 2 * 64 * 128;             // two boxes of 64 K rows x 64 columns
+  static constexpr int kB = WIDE ? 2 * kBHalf : kBHalf;   // wide tiles: this CTA's share of both column blocks
   static constexpr int kP = INT4 ? 128 * 32 : 0;   // packed int4: 128 weight rows x 64 K-elements
   static constexpr int kOffA = kHeader;
   static constexpr int kOffB = kOffA + STAGES * kA;
@@ -67,13 +76,15 @@ __device__ __forceinline__ void dense_tile(const DenseParams& p, int t, int& mt,
   mt = b * p.band + (u - nt * rows);
 }
 
-template <int STAGES, bool GROUPED, bool INT4 = false>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DenseSmem<STAGES, INT4>::kThreads, 1)
+template <int STAGES, bool GROUPED, bool INT4 = false, bool WIDE = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DenseSmem<STAGES, INT4, WIDE>::kThreads, 1)
 gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                       const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_c, const DenseParams p) {
-  using L = DenseSmem<STAGES, INT4>;
+  using L = DenseSmem<STAGES, INT4, WIDE>;
   static_assert(!INT4 || GROUPED, "int4 weights come with the grouped form");
+  static_assert(!WIDE || !GROUPED, "wide tiles are built for the dense form");
+  constexpr int kTileCols = WIDE ? 512 : 256;
   constexpr int kMmaWarp = L::kEpiWarps;
   constexpr int kProducerWarp = L::kEpiWarps + 1;
   constexpr int kFirstConvWarp = L::kEpiWarps + 2;
@@ -159,7 +170,7 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (t >= total_tiles) break;
         dense_tile(p, t, mt, nt);
         row0 = (2 * mt + (int)rank) * 128;                          // rows of A
-        col0 = (nt * 256 + (int)rank * 128) * 2;                    // byte column of B
+        col0 = (nt * kTileCols + (int)rank * 128) * 2;              // byte column of B
       }
       for (int kb = 0; kb < p.k_stages; ++kb) {
         ok = warp_wait(bar_empty + 8 * s, ((bits >> s) & 1u) ^ 1u, abort_flag, p.status, 1);
@@ -178,6 +189,11 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           } else {
             tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, col0, kb * 64);
             tma_load_2d_pair(sbase + L::kOffB + s * L::kB + 8192, &tmap_b, full, col0 + 128, kb * 64);
+            if (WIDE) {   // this CTA's 128 columns of the tile's second 256-column block
+              tma_load_2d_pair(sbase + L::kOffB + s * L::kB + L::kBHalf, &tmap_b, full, col0 + 512, kb * 64);
+              tma_load_2d_pair(sbase + L::kOffB + s * L::kB + L::kBHalf + 8192, &tmap_b, full, col0 + 640,
+                               kb * 64);
+            }
           }
         }
         __syncwarp();
@@ -203,8 +219,10 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         } else if (t >= total_tiles) {
           break;
         }
-        const int buf = tl & 1;
-        ok = warp_wait(bar_acc_empty + 8 * buf, ((uint32_t)(tl >> 1) & 1u) ^ 1u, abort_flag, p.status, 2);
+        // a wide tile fills both accumulators: it uses barrier pair 0 every time
+        const int buf = WIDE ? 0 : (tl & 1);
+        const uint32_t use = WIDE ? (uint32_t)tl : (uint32_t)(tl >> 1);
+        ok = warp_wait(bar_acc_empty + 8 * buf, (use & 1u) ^ 1u, abort_flag, p.status, 2);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t acc = tmem_base + buf * 256;
@@ -220,8 +238,12 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t bdesc = bdesc0 + s * (L::kB >> 4);
           if (elect_one()) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 4; ++j) {
               tc_mma_f16_pair(acc, adesc + 2 * j, bdesc + kBStep * j, idesc, (kb | j) ? 1u : 0u);
+              if (WIDE)
+                tc_mma_f16_pair(acc + 256, adesc + 2 * j, bdesc + (L::kBHalf >> 4) + kBStep * j, idesc,
+                                (kb | j) ? 1u : 0u);
+            }
             tc_commit_pair(bar_empty + 8 * s, 3);
           }
           __syncwarp();
@@ -315,30 +337,33 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (t >= total_tiles) break;
         dense_tile(p, t, mt, nt);
       }
-      const int buf = tl & 1;
+      const int buf = WIDE ? 0 : (tl & 1);
+      const uint32_t use = WIDE ? (uint32_t)tl : (uint32_t)(tl >> 1);
       bool ok = true;
       if (lane == 0)
-        ok = mbar_wait_bounded(bar_acc_full + 8 * buf, (uint32_t)(tl >> 1) & 1u, abort_flag, p.status, 4);
+        ok = mbar_wait_bounded(bar_acc_full + 8 * buf, use & 1u, abort_flag, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
       const int row_in = (2 * mt + (int)rank) * 128 + quad * 32;   // row inside the group / matrix
       const int row0 = (GROUPED ? cur.off : 0) + row_in;
-      const int colb = (nt * 256 + slab * 128) * 2;   // byte column
+      // wide tiles: slab w / 4 drains one whole 256-column accumulator, 128 columns per pass
+      const int colb = WIDE ? (nt * 512 + slab * 256) * 2 : (nt * 256 + slab * 128) * 2;   // byte column
       const float scale = (GROUPED && p.g.alpha) ? __ldg(p.g.alpha + cur.g) : 1.0f;
       const bool ragged = GROUPED && row_in + 32 > cur.rows;
       // The warp's 128 columns are drained in one pass, or in two 64-column passes where the
       // converter warps leave fewer registers per thread; the accumulator is handed back after
       // the last read either way (there are two accumulators, the next tile is not waiting).
-      constexpr int kPasses = INT4 ? 2 : 1;
-      constexpr int kCh = 4 / kPasses;          // 32-column chunks per pass
-      constexpr int kSubs = 2 / kPasses;        // 64-column store boxes per pass
+      constexpr int kPasses = (INT4 || WIDE) ? 2 : 1;
+      constexpr int kCh = WIDE ? 4 : 4 / kPasses;          // 32-column chunks per pass
+      constexpr int kSubs = WIDE ? 2 : 2 / kPasses;        // 64-column store boxes per pass
+      constexpr int kSlabCols = WIDE ? 256 : 128;          // accumulator columns one warp drains
 #pragma unroll
       for (int pass = 0; pass < kPasses; ++pass) {
         uint32_t v[kCh][32];
 #pragma unroll
         for (int c = 0; c < kCh; ++c)
-          tmem_ld_32x32b_x32(tmem_base + lane_base + buf * 256 + slab * 128 + (pass * kCh + c) * 32, v[c]);
+          tmem_ld_32x32b_x32(tmem_base + lane_base + buf * 256 + slab * kSlabCols + (pass * kCh + c) * 32, v[c]);
         tmem_ld_wait();
         if (pass == kPasses - 1) {
           tc_fence_before_sync();
@@ -605,13 +630,32 @@ extern "C" int msc_gemm_f16(const void* a, const void* b, void* c, int m, int n,
   p.g = GemmParams{};
   int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
   if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
+  // 256 x 512 tiles when there are enough of them to keep every pair busy for a few rounds;
+  // otherwise 256 x 256 tiles, which split a small problem into more pieces.  A negative
+  // max_ctas keeps its magnitude as the grid size and forces the 256 x 256 form.
+  const bool force_narrow = max_ctas < 0;
+  if (force_narrow) pairs = (-max_ctas) / 2 > 0 ? (-max_ctas) / 2 : num_sms() / 2;
+  const long long wide_tiles = (long long)p.m_tiles * ((n + 511) / 512);
+  cudaLaunchAttribute attr[1];
+  if (!force_narrow && wide_tiles >= 2LL * pairs) {
+    p.n_tiles = (n + 511) / 512;
+    p.band = 16;   // 8192^3: 0.721 / 0.707 / 0.700 / 0.711 ms with bands of 4 / 8 / 16 / 32 row tiles
+    if (pairs > wide_tiles) pairs = (int)wide_tiles;
+    constexpr int kStages = 4;
+    using L = DenseSmem<kStages, false, true>;
+    auto kern = gemm_dense_f16_kernel<kStages, false, false, true>;
+    if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kAlloc)) return rc;
+    cudaLaunchConfig_t lc =
+        pdl_launch_config(2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream), attr);
+    MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p));
+    return MSC_OK;
+  }
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   if (pairs > tiles) pairs = (int)tiles;
   constexpr int kStages = 6;
   using L = DenseSmem<kStages>;
   auto kern = gemm_dense_f16_kernel<kStages, false>;
   if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kAlloc)) return rc;
-  cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t lc =
       pdl_launch_config(2 * pairs, L::kThreads, L::kAlloc, static_cast<cudaStream_t>(stream), attr);
   MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p));

@@ -40,6 +40,38 @@ def test_dense_exact_integers(m, n, k, dtype):
     assert np.array_equal(out.double().cpu().numpy(), ref)
 
 
+@pytest.mark.parametrize("m,n,k,max_ctas", [(256, 1024, 64, 2), (512, 1024, 512, 4), (384, 520, 200, 2),
+                                            (768, 1600, 1024, 6), (100, 1000, 40, 2), (512, 2048, 4096, 8)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_dense_wide_tiles_exact_and_equal_to_narrow(m, n, k, max_ctas, dtype):
+    """The 256 x 512 tile form (two MMAs per K step sharing the A stage), reached here by
+    shrinking the grid until every CTA pair has at least two wide tiles: exact on integer
+    operands, and bit-identical to the 256 x 256 form (a negative max_ctas forces that one)."""
+    from mosaicist_b200 import _lib, ops
+
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    hi = 4 if dtype == torch.float16 else 2
+    a = torch.randint(1 - hi, hi, (m, k), device="cuda", generator=g).to(dtype)
+    b = torch.randint(1 - hi, hi, (k, n), device="cuda", generator=g).to(dtype)
+    if k > 512:
+        a = a * (torch.rand((m, k), device="cuda", generator=g) < 0.05).to(dtype)
+    assert ((m + 255) // 256) * ((n + 511) // 512) >= max_ctas      # the launcher picks the wide form
+    wide = torch.full((m, n), float("nan"), dtype=dtype, device="cuda")
+    narrow = torch.full((m, n), float("nan"), dtype=dtype, device="cuda")
+    ops.gemm_f16(a, b, out=wide, max_ctas=max_ctas)
+    ops.gemm_f16(a, b, out=narrow, max_ctas=-max_ctas)
+    assert _lib.status_word() == 0
+    ref = a.double().cpu().numpy() @ b.double().cpu().numpy()
+    assert np.count_nonzero(ref) > ref.size // 2
+    assert np.array_equal(wide.double().cpu().numpy(), ref)
+    assert torch.equal(wide, narrow)
+    # random operands: the two forms accumulate in the same order, so they agree bit for bit
+    a = (torch.randn((m, k), device="cuda", generator=g) / k ** 0.5).to(dtype)
+    b = (torch.randn((k, n), device="cuda", generator=g) / k ** 0.5).to(dtype)
+    assert torch.equal(ops.gemm_f16(a, b, max_ctas=max_ctas), ops.gemm_f16(a, b, max_ctas=-max_ctas))
+    assert _lib.status_word() == 0
+
+
 @pytest.mark.parametrize("dtype,rel", [(torch.float16, 2.0 ** -10), (torch.bfloat16, 2.0 ** -7)])
 def test_dense_random_and_column_shards(dtype, rel):
     from mosaicist_b200 import _lib, ops
