@@ -12,6 +12,11 @@
 // the main loop of the next.  Edges: TMA zero-fills loads and clips stores outside the
 // matrices, so M, N and K only need 16-byte alignment, not tile multiples.
 //
+// TALL form (grouped only, the default there): a tile is 512 rows x 256 columns, two 256-row
+// blocks of one group that share the B stage.  Both MMAs of a K step read the same weights, so a
+// group of 257 - 512 rows streams (and, with int4 weights, expands) its weights once instead of
+// twice; a tile whose second block holds no rows of the group neither loads nor multiplies it.
+//
 // WIDE form (dense only, the default for matrices of at least 512 columns): the two
 // accumulators belong to ONE 256 x 512 tile, each K step is two MMAs that share the A stage.
 // A 256 x 256 tile moves 64 KB per 64-element K stage for 512 tensor-pipe cycles, 62 bytes per
@@ -45,10 +50,11 @@ struct DenseParams {
   GemmParams g;           // grouped form: group_rows / group_offsets / alpha / out / l / n
 };
 
-template <int STAGES, bool INT4 = false, bool WIDE = false>
+template <int STAGES, bool INT4 = false, bool WIDE = false, bool TALL = false>
 struct DenseSmem {
   static constexpr int kHeader = 1024;
-  static constexpr int kA = 128 * 128;       // 128 rows x 64 K-elements
+  static constexpr int kABlock = 128 * 128;  // 128 rows x 64 K-elements
+  static constexpr int kA = TALL ? 2 * kABlock : kABlock;   // tall tiles: this CTA's rows of both row blocks
   static constexpr int kBHalf = 2 * 64 * 128;             // two boxes of 64 K rows x 64 columns
   static constexpr int kB = WIDE ? 2 * kBHalf : kBHalf;   // wide tiles: this CTA's share of both column blocks
   static constexpr int kP = INT4 ? 128 * 32 : 0;   // packed int4: 128 weight rows x 64 K-elements
@@ -76,21 +82,25 @@ __device__ __forceinline__ void dense_tile(const DenseParams& p, int t, int& mt,
   mt = b * p.band + (u - nt * rows);
 }
 
-template <int STAGES, bool GROUPED, bool INT4 = false, bool WIDE = false>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DenseSmem<STAGES, INT4, WIDE>::kThreads, 1)
+template <int STAGES, bool GROUPED, bool INT4 = false, bool WIDE = false, bool TALL = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DenseSmem<STAGES, INT4, WIDE, TALL>::kThreads, 1)
 gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                       const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_c, const DenseParams p) {
-  using L = DenseSmem<STAGES, INT4, WIDE>;
+  using L = DenseSmem<STAGES, INT4, WIDE, TALL>;
   static_assert(!INT4 || GROUPED, "int4 weights come with the grouped form");
   static_assert(!WIDE || !GROUPED, "wide tiles are built for the dense form");
+  static_assert(!TALL || GROUPED, "tall tiles are built for the grouped form");
   constexpr int kTileCols = WIDE ? 512 : 256;
+  constexpr int kTileRows = TALL ? 512 : 256;
+  constexpr int kMShift = TALL ? 9 : 8;
+  constexpr bool kOneAcc = WIDE || TALL;     // a tile fills both accumulators: no double buffering
   constexpr int kMmaWarp = L::kEpiWarps;
   constexpr int kProducerWarp = L::kEpiWarps + 1;
   constexpr int kFirstConvWarp = L::kEpiWarps + 2;
   // bytes TMA brings per CTA and stage onto the leader's full barrier: with int4 weights only A
   // (the packed weights land on each CTA's own barrier and reach the MMA through the converters)
-  constexpr uint32_t kStageBytes = INT4 ? L::kA : L::kA + L::kB;
+  constexpr uint32_t kStageBytes = INT4 ? L::kABlock : L::kABlock + L::kB;   // with one row block
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -159,12 +169,12 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t bits = 0, s = 0;
     bool ok = true;
     TileCursor cur;
-    cur.mshift = 8;
+    cur.mshift = kMShift;
     for (int t = pair; ok; t += npairs) {
       int mt, nt, row0, col0;
       if (GROUPED) {
         if (!cur.seek(p.g, ntiles_g, t, mt, nt)) break;
-        row0 = cur.off + (2 * mt + (int)rank) * 128;                // rows of A
+        row0 = cur.off + mt * kTileRows + (int)rank * 128;          // rows of A
         col0 = cur.g * p.g.n + nt * 256 + (int)rank * 128;          // rows of B (K-major)
       } else {
         if (t >= total_tiles) break;
@@ -172,14 +182,18 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         row0 = (2 * mt + (int)rank) * 128;                          // rows of A
         col0 = (nt * kTileCols + (int)rank * 128) * 2;              // byte column of B
       }
+      // tall tiles: the second row block is fetched only if it holds rows of the group
+      const bool has1 = TALL && mt * kTileRows + 256 < cur.rows;
       for (int kb = 0; kb < p.k_stages; ++kb) {
         ok = warp_wait(bar_empty + 8 * s, ((bits >> s) & 1u) ^ 1u, abort_flag, p.status, 1);
         if (!ok) break;
         bits ^= 1u << s;
         const uint32_t full = bar_full + 8 * s;
         if (elect_one()) {
-          if (leader) mbar_arrive_expect_tx(full, 2 * kStageBytes);
+          if (leader) mbar_arrive_expect_tx(full, 2 * (kStageBytes + (has1 ? (uint32_t)L::kABlock : 0u)));
           tma_load_2d_pair(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
+          if (has1)
+            tma_load_2d_pair(sbase + L::kOffA + s * L::kA + L::kABlock, &tmap_a, full, kb * 128, row0 + 256);
           if (INT4) {
             const uint32_t packed = bar_packed + 8 * s;
             mbar_arrive_expect_tx(packed, L::kP);
@@ -211,17 +225,19 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                       : operand_desc_mn_sw128(sbase + L::kOffB, 8192u);
       constexpr int kBStep = GROUPED ? 2 : 128;
       TileCursor cur;
-      cur.mshift = 8;
+      cur.mshift = kMShift;
       for (int t = pair; ok; t += npairs, ++tl) {
+        bool has1 = false;
         if (GROUPED) {
           int mt, nt;
           if (!cur.seek(p.g, ntiles_g, t, mt, nt)) break;
+          has1 = TALL && mt * kTileRows + 256 < cur.rows;
         } else if (t >= total_tiles) {
           break;
         }
-        // a wide tile fills both accumulators: it uses barrier pair 0 every time
-        const int buf = WIDE ? 0 : (tl & 1);
-        const uint32_t use = WIDE ? (uint32_t)tl : (uint32_t)(tl >> 1);
+        // a wide or tall tile fills both accumulators: it uses barrier pair 0 every time
+        const int buf = kOneAcc ? 0 : (tl & 1);
+        const uint32_t use = kOneAcc ? (uint32_t)tl : (uint32_t)(tl >> 1);
         ok = warp_wait(bar_acc_empty + 8 * buf, (use & 1u) ^ 1u, abort_flag, p.status, 2);
         if (!ok) break;
         tc_fence_after_sync();
@@ -242,6 +258,9 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
               tc_mma_f16_pair(acc, adesc + 2 * j, bdesc + kBStep * j, idesc, (kb | j) ? 1u : 0u);
               if (WIDE)
                 tc_mma_f16_pair(acc + 256, adesc + 2 * j, bdesc + (L::kBHalf >> 4) + kBStep * j, idesc,
+                                (kb | j) ? 1u : 0u);
+              if (has1)   // the tile's second row block against the same B stage
+                tc_mma_f16_pair(acc + 256, adesc + (L::kABlock >> 4) + 2 * j, bdesc + kBStep * j, idesc,
                                 (kb | j) ? 1u : 0u);
             }
             tc_commit_pair(bar_empty + 8 * s, 3);
@@ -270,7 +289,7 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t bits = 0, s = 0;
     bool ok = true;
     TileCursor cur;
-    cur.mshift = 8;
+    cur.mshift = kMShift;
     const __nv_bfloat162 k136 = __float2bfloat162_rn(136.0f);
     for (int t = pair; ok; t += npairs) {
       int mt, nt;
@@ -328,7 +347,7 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t lane_base = uint32_t(quad * 32) << 16;
     const uint32_t box = sbase + L::kOffC + warp * L::kCPerWarp;
     TileCursor cur;
-    cur.mshift = 8;
+    cur.mshift = kMShift;
     for (int t = pair;; t += npairs, ++tl) {
       int mt, nt;
       if (GROUPED) {
@@ -337,15 +356,20 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (t >= total_tiles) break;
         dense_tile(p, t, mt, nt);
       }
-      const int buf = WIDE ? 0 : (tl & 1);
-      const uint32_t use = WIDE ? (uint32_t)tl : (uint32_t)(tl >> 1);
+      const int buf = kOneAcc ? 0 : (tl & 1);
+      const uint32_t use = kOneAcc ? (uint32_t)tl : (uint32_t)(tl >> 1);
       bool ok = true;
       if (lane == 0)
         ok = mbar_wait_bounded(bar_acc_full + 8 * buf, use & 1u, abort_flag, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const int row_in = (2 * mt + (int)rank) * 128 + quad * 32;   // row inside the group / matrix
+      // tall tiles: row block 0 sits in accumulator columns 0-255, block 1 (if the group reaches
+      // it) in 256-511; the accumulators are handed back after the last block has been read
+      const int nblk = (TALL && mt * kTileRows + 256 < cur.rows) ? 2 : 1;
+      for (int blk = 0; blk < nblk; ++blk) {
+      const int acc_col = TALL ? blk * 256 : buf * 256;
+      const int row_in = mt * kTileRows + blk * 256 + (int)rank * 128 + quad * 32;   // row inside the group / matrix
       const int row0 = (GROUPED ? cur.off : 0) + row_in;
       // wide tiles: slab w / 4 drains one whole 256-column accumulator, 128 columns per pass
       const int colb = WIDE ? (nt * 512 + slab * 256) * 2 : (nt * 256 + slab * 128) * 2;   // byte column
@@ -363,9 +387,9 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t v[kCh][32];
 #pragma unroll
         for (int c = 0; c < kCh; ++c)
-          tmem_ld_32x32b_x32(tmem_base + lane_base + buf * 256 + slab * kSlabCols + (pass * kCh + c) * 32, v[c]);
+          tmem_ld_32x32b_x32(tmem_base + lane_base + acc_col + slab * kSlabCols + (pass * kCh + c) * 32, v[c]);
         tmem_ld_wait();
-        if (pass == kPasses - 1) {
+        if (pass == kPasses - 1 && blk == nblk - 1) {
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster((bar_acc_empty + 8 * buf) & kLeaderMask);
@@ -429,6 +453,7 @@ gemm_dense_f16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+      }   // row blocks
     }
     if (lane == 0) bulk_wait_group_read0();
   }
@@ -530,6 +555,9 @@ extern "C" int msc_grouped_gemm_bf16_ragged(const void* a, const void* b, const 
   p.g.raster = 0;
   int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
   if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
+  // 256-row tiles with two accumulators in turn: with bf16 weights the tall form (one weight
+  // stage for two row blocks) measured slower here, 0.638 ms against 0.605 ms on 64 groups of
+  // 64 - 512 rows, because its drain is not hidden; it pays where the weights are expanded
   const long long tiles = ((long long)(rows_total + 255) / 256 + l) * (n / 256);
   if (pairs > tiles) pairs = (int)tiles;
   constexpr int kStages = 6;
@@ -587,11 +615,11 @@ extern "C" int msc_grouped_gemm_bf16_int4_ragged(const void* a, const void* b_q,
   p.g.raster = 0;
   int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
   if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
-  const long long tiles = ((long long)(rows_total + 255) / 256 + l) * (n / 256);
+  const long long tiles = ((long long)(rows_total + 511) / 512 + l) * (n / 256);
   if (pairs > tiles) pairs = (int)tiles;
-  constexpr int kStages = 5;
-  using L = DenseSmem<kStages, true>;
-  auto kern = gemm_dense_f16_kernel<kStages, true, true>;
+  constexpr int kStages = 3;
+  using L = DenseSmem<kStages, true, false, true>;
+  auto kern = gemm_dense_f16_kernel<kStages, true, true, false, true>;
   if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kAlloc)) return rc;
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t lc =

@@ -43,7 +43,9 @@ def test_int4_dequant_bit_exact():
 
 
 @pytest.mark.parametrize("rows_list,n,k", [([128], 256, 128), ([64, 512, 0, 300, 17], 256, 1024),
-                                           ([250, 1000, 16], 512, 384)])      # check_matrix.py ragged M
+                                           ([250, 1000, 16], 512, 384),       # check_matrix.py ragged M
+                                           # around the 256- and 512-row edges of the tall tiles
+                                           ([256, 257, 511, 512, 513, 1025, 769], 256, 256)])
 @pytest.mark.parametrize("fused", [True, False], ids=["fused", "two_launches"])
 def test_mixed_int4_exact(rows_list, n, k, fused):
     from mosaicist_b200 import _lib, ops
