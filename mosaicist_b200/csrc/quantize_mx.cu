@@ -54,25 +54,51 @@ __device__ __forceinline__ uint32_t mx_scale_byte(float amax) {
   return (uint32_t)(e + 127);
 }
 
-__global__ void __launch_bounds__(256) mxfp8_quantize_kernel(const MxQuantParams p) {
-  const int per_row = p.k >> 3;                                 // threads per row
-  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long row = unit / per_row;
-  const int seg = (int)(unit - row * per_row);                  // 8-element segment inside the row
-  // whole warps stay alive for the shuffles; k % 128 == 0 keeps 16-lane groups inside a row
-  bool live = row < p.rows;
-  if (live) live = mx_row_live(p, row);
-  float v[8];
+// Four 8-element segments per thread, `stride` threads apart: all four loads are issued before
+// anything is computed (the kernel is bound by the latency of HBM, not by arithmetic), and the
+// lanes of a warp still cover consecutive segments in every round, so loads and stores coalesce
+// and the 4- and 16-lane groups of one scale block / scale word stay together.
+constexpr int kMxRounds = 4;
+
+__global__ void __launch_bounds__(256) mxfp8_quantize_kernel(const MxQuantParams p, long long stride) {
+  const int per_row = p.k >> 3;                                 // segments per row
+  const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long row[kMxRounds];
+  int seg[kMxRounds];
+  bool live[kMxRounds];
+  uint4 raw[kMxRounds][2];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-  if (live) {
+  for (int r = 0; r < kMxRounds; ++r) {
+    const long long unit = first + r * stride;
+    row[r] = unit / per_row;
+    seg[r] = (int)(unit - row[r] * per_row);                    // 8-element segment inside the row
+    // whole warps stay alive for the shuffles; k % 128 == 0 keeps 16-lane groups inside a row
+    live[r] = row[r] < p.rows;
+    if (live[r]) live[r] = mx_row_live(p, row[r]);
+    raw[r][0] = raw[r][1] = make_uint4(0u, 0u, 0u, 0u);
+    if (live[r]) {
+      if (p.f32_in) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const float*>(p.x) + row[r] * p.k + seg[r] * 8);
+        raw[r][0] = __ldg(src);
+        raw[r][1] = __ldg(src + 1);
+      } else {
+        raw[r][0] = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.x) + row[r] * p.k + seg[r] * 8));
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kMxRounds; ++r) {
+    float v[8];
     if (p.f32_in) {
-      const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + row * p.k + seg * 8);
-      const float4 a = __ldg(src), b = __ldg(src + 1);
-      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+      const float* f0 = reinterpret_cast<const float*>(&raw[r][0]);
+      const float* f1 = reinterpret_cast<const float*>(&raw[r][1]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[i] = f0[i];
+        v[4 + i] = f1[i];
+      }
     } else {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.x) + row * p.k + seg * 8));
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[r][0]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 f = __bfloat1622float2(h[j]);
@@ -80,41 +106,41 @@ __global__ void __launch_bounds__(256) mxfp8_quantize_kernel(const MxQuantParams
         v[2 * j + 1] = f.y;
       }
     }
-  }
-  float amax = 0.0f;
+    float amax = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  const uint32_t sfb = mx_scale_byte(amax);
-  if (live) {
-    const int e = (int)sfb - 127;
-    uint32_t w[2];
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t sfb = mx_scale_byte(amax);
+    if (live[r]) {
+      // 1 / scale = 2^(127 - byte) is a normal fp32 number for every byte the rule can produce
+      // (byte <= 247), so x / scale is one exact multiplication (or one rounding into the fp32
+      // subnormals, far below e4m3's reach); the saturating conversion is the clip to +-448
+      // followed by round-to-nearest-even, two values per instruction
+      const float inv = __uint_as_float((254u - sfb) << 23);
+      uint32_t w[2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        // x * 2^-e is exact (or rounds once into the fp32 subnormals, far below e4m3's reach);
-        // the saturating conversion is the clip to +-448 followed by round-to-nearest-even
-        const float y = scalbnf(v[4 * h + j], -e);
-        word |= (uint32_t)(uint8_t)__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * h] * inv, v[4 * h + 1] * inv),
+                                                     __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * h + 2] * inv, v[4 * h + 3] * inv),
+                                                     __NV_SATFINITE, __NV_E4M3);
+        w[h] = lo | (hi << 16);
       }
-      w[h] = word;
+      *reinterpret_cast<uint2*>(p.q + row[r] * p.k + seg[r] * 8) = make_uint2(w[0], w[1]);
     }
-    *reinterpret_cast<uint2*>(p.q + row * p.k + seg * 8) = make_uint2(w[0], w[1]);
-  }
-  // lanes 0, 4, 8, 12 (and 16 ... 28) hold the scale bytes of four consecutive blocks
-  uint32_t word = sfb;
-  word |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
-  word |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
-  word |= __shfl_down_sync(0xffffffffu, sfb, 12) << 24;
-  if (live && (threadIdx.x & 15) == 0) {
-    const int kw = seg >> 4, kwords = p.k >> 7;
-    if (p.tiled)
-      *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word((int)row, kw, kwords)) = word;
-    else
-      *reinterpret_cast<uint32_t*>(p.sf + row * (p.k >> 5) + kw * 4) = word;
+    // lanes 0, 4, 8, 12 (and 16 ... 28) hold the scale bytes of four consecutive blocks
+    uint32_t word = sfb;
+    word |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
+    word |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
+    word |= __shfl_down_sync(0xffffffffu, sfb, 12) << 24;
+    if (live[r] && (threadIdx.x & 15) == 0) {
+      const int kw = seg[r] >> 4, kwords = p.k >> 7;
+      if (p.tiled)
+        *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word((int)row[r], kw, kwords)) = word;
+      else
+        *reinterpret_cast<uint32_t*>(p.sf + row[r] * (p.k >> 5) + kw * 4) = word;
+    }
   }
 }
 
@@ -174,9 +200,10 @@ static int mx_quantize(const void* x, int x_dtype, void* q, void* sf, int sf_lay
   p.group_rows = group_rows; p.group_offsets = group_offsets;
   p.rows = rows; p.k = k; p.l = l; p.tiled = sf_layout; p.f32_in = x_dtype;
   const long long units = rows * (k / 8);
-  const long long blocks = (units + 255) / 256;
+  // a quarter of the segments per round, rounded up to whole blocks
+  const long long blocks = (units + 256LL * kMxRounds - 1) / (256LL * kMxRounds);
   if (blocks > 0x7fffffffLL) return fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
-  mxfp8_quantize_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  mxfp8_quantize_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p, blocks * 256LL);
   MSC_CUDA_OK(cudaGetLastError());
   return MSC_OK;
 }
