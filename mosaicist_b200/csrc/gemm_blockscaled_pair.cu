@@ -5,6 +5,12 @@
 // instruction for both.  Sharing B between two SMs cuts the L2->SM operand stream per MMA
 // by 30 % against a 128 x 256 single-CTA tile, which is what bounds that kernel.
 //
+// A tile whose group ends inside it (the last tile of a ragged group, a masked batch) loads only
+// the A rows that exist, in 32-row boxes, and none at all for a CTA whose 128 rows lie wholly
+// beyond the group's end: the ring is bound by the bytes that reach shared memory, so a short
+// tile then runs at the tensor pipe's pace instead of the loads'.  The rows not loaded keep
+// whatever the stage held before; they only ever reach accumulator rows that are not stored.
+//
 // No load here is multicast: every CTA fetches its own boxes.  The only cluster-wide
 // signalling is tcgen05.commit arriving on both CTAs' barriers and plain remote
 // mbarrier arrives.
@@ -53,7 +59,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa,
                  const __grid_constant__ CUtensorMap tmap_sfb,
-                 const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_c,
+                 const __grid_constant__ CUtensorMap tmap_a32, const GemmParams p) {
   using L = PairSmem<STAGES, SFW, SCATTER>;
   static_assert(!(SWIGLU && SCATTER), "one epilogue at a time");
   constexpr int kTileN = 256;
@@ -65,7 +72,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   static_assert(kSfCol0 + STAGES * kSlotCols <= 512, "scale slots do not fit in TMEM");
   constexpr int kChunksPerStage = (KIND == KIND_NVFP4) ? 4 : 1;
   constexpr uint32_t kSfBoxBytes = kChunksPerStage * 512;
-  constexpr uint32_t kStageBytes = L::kA + L::kB + 3 * kSfBoxBytes;  // per CTA
   constexpr uint32_t kIdescBase =
       (KIND == KIND_NVFP4)
           ? ((1u << 7) | (1u << 10) | (uint32_t(kTileN >> 3) << 17) | (16u << 24))
@@ -113,6 +119,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tma_prefetch_desc(&tmap_sfa);
     tma_prefetch_desc(&tmap_sfb);
     tma_prefetch_desc(&tmap_c);
+    tma_prefetch_desc(&tmap_a32);
   }
   if (warp == 0) {
     tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -148,6 +155,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int mt, nt;
       if (!cur.seek(p, ntiles, t, mt, nt)) break;
       const int row0 = cur.off + (2 * mt + (int)rank) * 128;
+      // 32-row boxes of A that hold rows of the group, for this CTA and for its peer
+      const int left = cur.rows - 2 * mt * 128;
+      const int boxes_own = (min(max(left - (int)rank * 128, 0), 128) + 31) >> 5;
+      const int boxes_peer = (min(max(left - (int)(rank ^ 1u) * 128, 0), 128) + 31) >> 5;
+      const uint32_t sf_own = (boxes_own ? 3u : 2u) * kSfBoxBytes;
+      const uint32_t sf_peer = (boxes_peer ? 3u : 2u) * kSfBoxBytes;
+      const uint32_t ab_both = 2 * L::kB + uint32_t(boxes_own + boxes_peer) * 4096u;
       // plain: the tile's 256 B rows are consecutive, this CTA takes its half.  SwiGLU: the
       // tile pairs 128 gate rows (first half of B) with the 128 up rows of the same output
       // columns (second half); the even CTA feeds the gate rows, the odd CTA the up rows, so
@@ -165,23 +179,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!ok) break;
         bits ^= 1u << s;
         const uint32_t full = bar_full + 8 * s;
+        // scale boxes report to this CTA's own barrier when its scale warps consume them
+        const uint32_t sff = SFW ? bar_sf_full + 8 * s : full;
         const int c4 = kb * kChunksPerStage * 4;
         if (elect_one()) {
           if (SFW) {
-            // scale boxes report to this CTA's own barrier: its scale warps consume them
-            const uint32_t sff = bar_sf_full + 8 * s;
-            if (leader) mbar_arrive_expect_tx(full, 2 * (L::kA + L::kB));
-            mbar_arrive_expect_tx(sff, 3 * kSfBoxBytes);
-            tma_load_2d_pair(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
-            tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, brow0);
-            tma_load_2d(sbase + L::kOffSfa + s * L::kSfa, &tmap_sfa, sff, 0, sfa_row + c4);
+            if (leader) mbar_arrive_expect_tx(full, ab_both);
+            mbar_arrive_expect_tx(sff, sf_own);
+          } else if (leader) {
+            mbar_arrive_expect_tx(full, ab_both + sf_own + sf_peer);
+          }
+          const uint32_t a_dst = sbase + L::kOffA + s * L::kA;
+          if (boxes_own == 4) {
+            tma_load_2d_pair(a_dst, &tmap_a, full, kb * 128, row0);
+          } else {
+            for (int i = 0; i < boxes_own; ++i)
+              tma_load_2d_pair(a_dst + i * 4096, &tmap_a32, full, kb * 128, row0 + 32 * i);
+          }
+          tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, brow0);
+          if (SFW) {
+            if (boxes_own) tma_load_2d(sbase + L::kOffSfa + s * L::kSfa, &tmap_sfa, sff, 0, sfa_row + c4);
             tma_load_2d(sbase + L::kOffSfb + s * L::kSfb, &tmap_sfb, sff, 0, sfb_row + c4);
             tma_load_2d(sbase + L::kOffSfb + s * L::kSfb + 2048, &tmap_sfb, sff, 0, sfb_row1 + c4);
           } else {
-            if (leader) mbar_arrive_expect_tx(full, 2 * kStageBytes);
-            tma_load_2d_pair(sbase + L::kOffA + s * L::kA, &tmap_a, full, kb * 128, row0);
-            tma_load_2d_pair(sbase + L::kOffB + s * L::kB, &tmap_b, full, kb * 128, brow0);
-            tma_load_2d_pair(sbase + L::kOffSfa + s * L::kSfa, &tmap_sfa, full, 0, sfa_row + c4);
+            if (boxes_own)
+              tma_load_2d_pair(sbase + L::kOffSfa + s * L::kSfa, &tmap_sfa, full, 0, sfa_row + c4);
             tma_load_2d_pair(sbase + L::kOffSfb + s * L::kSfb, &tmap_sfb, full, 0, sfb_row + c4);
             tma_load_2d_pair(sbase + L::kOffSfb + s * L::kSfb + 2048, &tmap_sfb, full, 0,
                              sfb_row1 + c4);
@@ -536,7 +558,7 @@ static int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, c
   // before it in the stream (it waits for that kernel before touching global memory)
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t lc = pdl_launch_config(grid, L::kThreads, L::kAlloc, stream, attr);
-  MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, maps[0], maps[1], maps[2], maps[3], maps[4], p));
+  MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p));
   return MSC_OK;
 }
 
@@ -565,8 +587,10 @@ int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_
                      cudaStream_t stream, bool sf_by_warps) {
   if (p.n % 256) return fail(MSC_ERR_BAD_ARG, "the CTA-pair kernel needs n %% 256 == 0, got n=%d", p.n);
   const int chunks_per_stage = (kind == KIND_NVFP4) ? 4 : 1;
-  CUtensorMap maps[5];
+  CUtensorMap maps[6];
   int rc = make_tmap_bytes_2d(&maps[0], a_q, (uint64_t)rows_total, (uint64_t)k_bytes, 128);
+  if (rc) return rc;
+  rc = make_tmap_bytes_2d(&maps[5], a_q, (uint64_t)rows_total, (uint64_t)k_bytes, 32);   // short tiles
   if (rc) return rc;
   rc = make_tmap_bytes_2d(&maps[1], b_q, (uint64_t)p.l * p.n, (uint64_t)k_bytes, 128);
   if (rc) return rc;

@@ -47,84 +47,54 @@ __device__ __forceinline__ int group_of_row(const QuantParams& p, long long row,
   return lo;
 }
 
-// One thread per block of 16 elements and round: a warp reads 1 KB of one row with two fully
-// used 16-byte loads per lane and writes 256 contiguous bytes of e2m1; four neighbouring lanes
-// pool their scale bytes into one aligned 32-bit store.  Every thread takes kQuantRounds blocks,
-// `stride` threads apart, and issues the loads of all of them before it computes anything: the
-// kernel waits on memory latency, not on arithmetic, and the lanes of a warp still cover
-// consecutive blocks in every round.
-constexpr int kQuantRounds = 2;
-
-__global__ void __launch_bounds__(256) nvfp4_quantize_kernel(const QuantParams p, long long stride) {
+// One thread per block of 16 elements: a warp reads 1 KB of one row with two fully used
+// 16-byte loads per lane and writes 256 contiguous bytes of e2m1; four neighbouring lanes
+// pool their scale bytes into one aligned 32-bit store.
+__global__ void __launch_bounds__(256) nvfp4_quantize_kernel(const QuantParams p) {
   const int kblocks = p.k >> 4;
-  const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  long long row[kQuantRounds];
-  int kb[kQuantRounds], g[kQuantRounds];
-  bool valid[kQuantRounds];
-  uint4 raw[kQuantRounds][4];   // bf16: 2 words; f32 or gate + up: 4
+  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = unit / kblocks;
+  const int kb = (int)(unit - row * kblocks);
+  // whole warps stay alive for the shuffle below; k % 64 == 0 keeps a row's lanes in fours
+  bool valid = row < p.rows_total;
+  int g = 0;
+  if (valid) g = group_of_row(p, row, valid);
+  float v[16];
+  uint2 q8 = make_uint2(0, 0);
+  uint32_t sfb = 0;
+  if (valid) {
+    const float gs = __ldg(p.gs + g);
+    if (p.silu) {
+      // row holds [gate (k) | up (k)] in bf16; activation stays fp32 (nvfp4.py:81-88)
+      const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.x) + row * 2 * p.k + kb * 16;
+      float gt[16], up[16];
+      load16_bf16(base, gt);
+      load16_bf16(base + p.k, up);
 #pragma unroll
-  for (int r = 0; r < kQuantRounds; ++r) {
-    const long long unit = first + r * stride;
-    row[r] = unit / kblocks;
-    kb[r] = (int)(unit - row[r] * kblocks);
-    // whole warps stay alive for the shuffle below; k % 64 == 0 keeps a row's lanes in fours
-    valid[r] = row[r] < p.rows_total;
-    g[r] = 0;
-    if (valid[r]) g[r] = group_of_row(p, row[r], valid[r]);
-    if (valid[r]) {
-      if (p.silu) {
-        // row holds [gate (k) | up (k)] in bf16
-        const uint4* base = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.x) + row[r] * 2 * p.k + kb[r] * 16);
-        const uint4* up = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.x) + row[r] * 2 * p.k + p.k + kb[r] * 16);
-        raw[r][0] = __ldg(base); raw[r][1] = __ldg(base + 1);
-        raw[r][2] = __ldg(up); raw[r][3] = __ldg(up + 1);
-      } else if (p.f32_in) {
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const float*>(p.x) + row[r] * p.k + kb[r] * 16);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) raw[r][i] = __ldg(src + i);
-      } else {
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.x) + row[r] * p.k + kb[r] * 16);
-        raw[r][0] = __ldg(src); raw[r][1] = __ldg(src + 1);
+      for (int i = 0; i < 16; ++i) {
+        const float sg = __frcp_rn(__fadd_rn(1.0f, expf(-gt[i])));
+        v[i] = __fmul_rn(__fmul_rn(sg, gt[i]), up[i]);
       }
+    } else if (p.f32_in) {
+      const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + row * p.k + kb * 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 f = __ldg(src + i);
+        v[i * 4] = f.x; v[i * 4 + 1] = f.y; v[i * 4 + 2] = f.z; v[i * 4 + 3] = f.w;
+      }
+    } else {
+      load16_bf16(static_cast<const __nv_bfloat16*>(p.x) + row * p.k + kb * 16, v);
     }
+    quantize_16(v, gs, q8, sfb);
+    *reinterpret_cast<uint2*>(p.q + row * (p.k >> 1) + kb * 8) = q8;
   }
-#pragma unroll
-  for (int r = 0; r < kQuantRounds; ++r) {
-    float v[16];
-    uint2 q8 = make_uint2(0, 0);
-    uint32_t sfb = 0;
-    if (valid[r]) {
-      const float gs = __ldg(p.gs + g[r]);
-      if (p.silu) {
-        // the activation stays fp32 (nvfp4.py:81-88)
-        float gt[16], up[16];
-        unpack16_bf16(raw[r], gt);
-        unpack16_bf16(raw[r] + 2, up);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float sg = __frcp_rn(__fadd_rn(1.0f, expf(-gt[i])));
-          v[i] = __fmul_rn(__fmul_rn(sg, gt[i]), up[i]);
-        }
-      } else if (p.f32_in) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float* f = reinterpret_cast<const float*>(&raw[r][i]);
-          v[i * 4] = f[0]; v[i * 4 + 1] = f[1]; v[i * 4 + 2] = f[2]; v[i * 4 + 3] = f[3];
-        }
-      } else {
-        unpack16_bf16(raw[r], v);
-      }
-      quantize_16(v, gs, q8, sfb);
-      *reinterpret_cast<uint2*>(p.q + row[r] * (p.k >> 1) + kb[r] * 8) = q8;
-    }
-    const uint32_t word = gather_scale_word(sfb);
-    if (valid[r] && (kb[r] & 3) == 0) {
-      const int kw = kb[r] >> 2, kwords = kblocks >> 2;
-      if (p.tiled)
-        *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word((int)row[r], kw, kwords)) = word;
-      else
-        *reinterpret_cast<uint32_t*>(p.sf + row[r] * (p.k >> 4) + kw * 4) = word;
-    }
+  const uint32_t word = gather_scale_word(sfb);
+  if (valid && (kb & 3) == 0) {
+    const int kw = kb >> 2, kwords = kblocks >> 2;
+    if (p.tiled)
+      *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word((int)row, kw, kwords)) = word;
+    else
+      *reinterpret_cast<uint32_t*>(p.sf + row * (p.k >> 4) + kw * 4) = word;
   }
 }
 
@@ -171,9 +141,9 @@ static int quantize_common(const void* x, int x_dtype, const float* gs, const in
   p.tiled = sf_layout; p.silu = silu; p.f32_in = x_dtype;
   const long long units = rows_total * (k / 16);
   const int threads = 256;
-  const long long blocks = (units + (long long)threads * kQuantRounds - 1) / ((long long)threads * kQuantRounds);
+  const long long blocks = (units + threads - 1) / threads;
   if (blocks > 0x7fffffffLL) return fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
-  nvfp4_quantize_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(p, blocks * threads);
+  nvfp4_quantize_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   MSC_CUDA_OK(cudaGetLastError());
   return MSC_OK;
 }

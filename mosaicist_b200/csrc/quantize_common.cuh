@@ -79,20 +79,6 @@ __device__ __forceinline__ uint32_t gather_scale_word(uint32_t sfb) {
   return w;
 }
 
-// 16 bf16 values already in registers (two 16-byte words) as fp32.
-__device__ __forceinline__ void unpack16_bf16(const uint4* raw, float* v) {
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(h[j]);
-      v[i * 8 + j * 2] = f.x;
-      v[i * 8 + j * 2 + 1] = f.y;
-    }
-  }
-}
-
 // Loads 16 consecutive bf16 values (32 bytes, 16-byte aligned) as fp32.
 __device__ __forceinline__ void load16_bf16(const __nv_bfloat16* src, float* v) {
   const uint4* s4 = reinterpret_cast<const uint4*>(src);

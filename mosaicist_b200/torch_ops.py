@@ -8,6 +8,11 @@ that build graphs of torch operators (tracing, FakeTensor shape propagation) ins
     grouped_gemm_nvfp4_ragged  the same arithmetic over row-concatenated groups
     quantize_nvfp4             quantize_nvfp4 (nvfp4.py:39-57) with scales in the MMA tiling
     silu_mul_quantize_nvfp4    silu_mul (nvfp4.py:81-88) + quantize_nvfp4
+    global_scale_for           global_scale_for (nvfp4.py:29-36)
+    quantize_mxfp8             e4m3 values + one ue8m0 scale per 32, scales in the MMA tiling
+    grouped_gemm_mxfp8_ragged  the MXFP8 grouped GEMM over row-concatenated groups
+    gemm_f16                   the dense fp16 / bf16 problem (hopper_gemm/ref_cutedsl.py:50-74)
+    grouped_gemm_bf16_int4_ragged   bf16 x int4 grouped GEMM (problems.py:75-87)
 
 Each is the corresponding C-ABI entry point.  Operators return fresh tensors, so rows a masked
 call leaves untouched come back as zeros.  Importing this module registers the operators; it
@@ -91,3 +96,67 @@ def _(gateup, global_scale, masked_m):
     l, m, n2 = gateup.shape
     qs, ss = _quantized_shapes(l, m, n2 // 2)
     return gateup.new_empty(qs, dtype=torch.uint8), gateup.new_empty(ss, dtype=torch.uint8)
+
+
+@torch.library.custom_op("mosaicist_sm100a::global_scale_for", mutates_args=(), device_types="cuda")
+def global_scale_for(x: torch.Tensor) -> torch.Tensor:
+    """(l, ...) bf16 / f32 -> (l,) f32 = 2688 / max|x[l]| (a maximum of 0 counted as 1)."""
+    return ops.global_scale_for(x)
+
+
+@global_scale_for.register_fake
+def _(x):
+    return x.new_empty((x.shape[0],), dtype=torch.float32)
+
+
+@torch.library.custom_op("mosaicist_sm100a::quantize_mxfp8", mutates_args=(), device_types="cuda")
+def quantize_mxfp8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """(rows, k) bf16 / f32 -> e4m3 bytes (rows, k) and tiled ue8m0 scales (ceil(rows/128), k/128, 32, 16)."""
+    return ops.quantize_mxfp8(x)
+
+
+@quantize_mxfp8.register_fake
+def _(x):
+    rows, k = x.shape
+    return x.new_empty((rows, k), dtype=torch.uint8), x.new_empty(((rows + 127) // 128, k // 128, 32, 16), dtype=torch.uint8)
+
+
+@torch.library.custom_op("mosaicist_sm100a::grouped_gemm_mxfp8_ragged", mutates_args=(), device_types="cuda")
+def grouped_gemm_mxfp8_ragged(a_q: torch.Tensor, a_sf: torch.Tensor, b_q: torch.Tensor, b_sf: torch.Tensor,
+                              group_offsets: torch.Tensor, group_rows: torch.Tensor,
+                              alpha: Optional[torch.Tensor], row_scale: Optional[torch.Tensor]) -> torch.Tensor:
+    """(rows_total, k) x (l, n, k) e4m3 with tiled ue8m0 scales -> (rows_total, n) bf16; rows outside
+    every group come back as zeros."""
+    out = torch.zeros((a_q.shape[0], b_q.shape[1]), dtype=torch.bfloat16, device=a_q.device)
+    return ops.ragged_grouped_gemm_mxfp8(a_q, a_sf, b_q, b_sf, group_offsets, group_rows, alpha, row_scale, out=out)
+
+
+@grouped_gemm_mxfp8_ragged.register_fake
+def _(a_q, a_sf, b_q, b_sf, group_offsets, group_rows, alpha, row_scale):
+    return a_q.new_empty((a_q.shape[0], b_q.shape[1]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("mosaicist_sm100a::gemm_f16", mutates_args=(), device_types="cuda")
+def gemm_f16(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """C = A (m, k) @ B (k, n), fp16 or bf16 in and out, fp32 accumulation."""
+    return ops.gemm_f16(a, b)
+
+
+@gemm_f16.register_fake
+def _(a, b):
+    return a.new_empty((a.shape[0], b.shape[1]))
+
+
+@torch.library.custom_op("mosaicist_sm100a::grouped_gemm_bf16_int4_ragged", mutates_args=(), device_types="cuda")
+def grouped_gemm_bf16_int4_ragged(a: torch.Tensor, b_q: torch.Tensor, scales: torch.Tensor,
+                                  group_offsets: torch.Tensor, group_rows: torch.Tensor,
+                                  alpha: Optional[torch.Tensor], group_size: int) -> torch.Tensor:
+    """bf16 (rows_total, k) x packed int4 (l, n, k/2) with bf16 scales (l, n, k/group_size) ->
+    (rows_total, n) bf16; rows outside every group come back as zeros."""
+    out = torch.zeros((a.shape[0], b_q.shape[1]), dtype=torch.bfloat16, device=a.device)
+    return ops.mixed_grouped_gemm_int4(a, b_q, scales, group_offsets, group_rows, alpha, group_size, out=out)
+
+
+@grouped_gemm_bf16_int4_ragged.register_fake
+def _(a, b_q, scales, group_offsets, group_rows, alpha, group_size):
+    return a.new_empty((a.shape[0], b_q.shape[1]), dtype=torch.bfloat16)

@@ -230,6 +230,22 @@ def test_torch_custom_op_is_registered_and_shape_propagates():
             torch.empty((1024, 1024), **u8), torch.empty((8, 32, 32, 16), **u8), torch.empty((4, 512, 1024), **u8),
             torch.empty((4, 4, 32, 32, 16), **u8), torch.empty((4,), **i32), torch.empty((4,), **i32), None, None)
         assert tuple(y.shape) == (1024, 512) and y.dtype == torch.bfloat16
+        gs = torch.ops.mosaicist_sm100a.global_scale_for(x)
+        assert tuple(gs.shape) == (8,) and gs.dtype == torch.float32
+        q, sf = torch.ops.mosaicist_sm100a.quantize_mxfp8(torch.empty((300, 512), dtype=torch.bfloat16, device="cuda"))
+        assert tuple(q.shape) == (300, 512) and tuple(sf.shape) == (3, 4, 32, 16) and q.dtype == torch.uint8
+        y = torch.ops.mosaicist_sm100a.grouped_gemm_mxfp8_ragged(
+            torch.empty((1024, 1024), **u8), torch.empty((8, 8, 32, 16), **u8), torch.empty((4, 512, 1024), **u8),
+            torch.empty((4, 4, 8, 32, 16), **u8), torch.empty((4,), **i32), torch.empty((4,), **i32), None, None)
+        assert tuple(y.shape) == (1024, 512) and y.dtype == torch.bfloat16
+        h = dict(dtype=torch.float16, device="cuda")
+        c = torch.ops.mosaicist_sm100a.gemm_f16(torch.empty((256, 128), **h), torch.empty((128, 384), **h))
+        assert tuple(c.shape) == (256, 384) and c.dtype == torch.float16
+        y = torch.ops.mosaicist_sm100a.grouped_gemm_bf16_int4_ragged(
+            torch.empty((768, 512), dtype=torch.bfloat16, device="cuda"), torch.empty((3, 256, 256), **u8),
+            torch.empty((3, 256, 4), dtype=torch.bfloat16, device="cuda"), torch.empty((3,), **i32),
+            torch.empty((3,), **i32), None, 128)
+        assert tuple(y.shape) == (768, 256) and y.dtype == torch.bfloat16
 
 
 def test_dropped_ptx_is_reduced_to_the_running_instantiation(lib, tmp_path, monkeypatch):

@@ -151,6 +151,9 @@ RAGGED = [
     ([1, 127, 129, 300, 5], 384, 640, {"max_ctas": 3}),
     ([200, 0, 50, 384, 257], 256, 1024, {"cta_pair": 1}),
     ([1, 127, 129, 300, 5], 512, 640, {"cta_pair": 1, "max_ctas": 4}),
+    # short tiles of the pair kernel: every count of 32-row A boxes in either CTA, next to full tiles
+    ([32, 33, 64, 96, 97, 128, 160, 161, 224, 255, 256, 288, 289, 400, 512, 31], 256, 896, {"cta_pair": 1}),
+    ([289, 161, 33, 544], 512, 384, {"cta_pair": 1, "max_ctas": 2, "stages": 3}),
 ]
 
 
@@ -275,6 +278,26 @@ def test_torch_custom_op_matches_direct_call():
     y_d = ops.ragged_grouped_gemm_nvfp4(a_q.view(l * m, -1), a_sf.view(l * m // 128, k // 64, 32, 16), b_q, b_sf, offs,
                                         rows, out=torch.zeros((l * m, n), dtype=torch.bfloat16, device="cuda"))
     assert torch.equal(y_op, y_d) and int((y_op[200:256] != 0).sum()) == 0
+    # the MXFP8 chain, the dense GEMM and the bf16 x int4 grouped GEMM as operators
+    P = torch.ops.mosaicist_sm100a
+    assert torch.equal(P.global_scale_for(x), ops.global_scale_for(x))
+    xa = torch.randn((l * m, k), device="cuda", generator=g).bfloat16()
+    xb = torch.randn((l * n, k), device="cuda", generator=g).bfloat16()
+    (qa, sa), (qb, sb) = P.quantize_mxfp8(xa), P.quantize_mxfp8(xb)
+    qa_d, sa_d = ops.quantize_mxfp8(xa)
+    assert torch.equal(qa, qa_d) and torch.equal(sa, sa_d)
+    y_op = P.grouped_gemm_mxfp8_ragged(qa, sa, qb.view(l, n, k), sb.view(l, n // 128, k // 128, 32, 16), offs, rows, None, None)
+    y_d = ops.ragged_grouped_gemm_mxfp8(qa, sa, qb.view(l, n, k), sb.view(l, n // 128, k // 128, 32, 16), offs, rows,
+                                        out=torch.zeros((l * m, n), dtype=torch.bfloat16, device="cuda"))
+    assert torch.equal(y_op, y_d) and int((y_op[200:256] != 0).sum()) == 0 and int((y_op[:200] != 0).sum()) > 0
+    bt = xb[:n].t().contiguous()                                   # (k, n)
+    assert torch.equal(P.gemm_f16(xa, bt), ops.gemm_f16(xa, bt))
+    w_q = u8(l, n, k // 2)
+    w_s = (torch.rand((l, n, k // 128), device="cuda", generator=g) * 0.02 + 0.01).bfloat16()
+    y_op = P.grouped_gemm_bf16_int4_ragged(xa, w_q, w_s, offs, rows, None, 128)
+    y_d = ops.mixed_grouped_gemm_int4(xa, w_q, w_s, offs, rows, None, 128,
+                                      out=torch.zeros((l * m, n), dtype=torch.bfloat16, device="cuda"))
+    assert torch.equal(y_op, y_d) and int((y_op[200:256] != 0).sum()) == 0 and int((y_op[:200] != 0).sum()) > 0
 
 
 @pytest.mark.parametrize("rows_list,n,k", [([256], 256, 256), ([300, 0, 77, 512, 129], 512, 640)])
