@@ -272,15 +272,24 @@ int msc_moe_plan_noalloc(const int32_t* ids, int entries, int expert_first, int 
  * with its expert's global scale (arithmetic of quantize_nvfp4, nvfp4.py:39-57) and writes it
  * at row group_offsets[e] + rank: a_q (rows_cap, hidden/2), a_sf tiled
  * (rows_cap/128, hidden/64, 32, 16), plus row_weight (rows_cap) f32 = the pair's routing weight
- * and row_token (rows_cap) i32.  rows_cap is a multiple of 128 >= total_rows.  hidden % 64 == 0. */
+ * and row_token (rows_cap) i32.  rows_cap is a multiple of 128 >= total_rows.  hidden % 64 == 0,
+ * topk <= 64, a_q 16-byte aligned (rows leave shared memory as bulk copies).
+ * sf_rows (rows_cap, hidden/16) u8 or NULL: staging for the scales.  With it (hidden % 256 == 0,
+ * rows_cap a multiple of 128, both scale buffers 16-byte aligned) every row's scale bytes leave
+ * as one bulk copy into sf_rows and a second kernel re-tiles them into a_sf - about 40 % less
+ * time at top-8 than writing the tiling word by word; total_rows (device, i32, or NULL) is
+ * the row count msc_moe_plan produced and bounds that pass, padding rows inside it receive
+ * whatever sf_rows held.  Without it rows_cap and total_rows are ignored. */
 int msc_moe_permute_quantize(const void* tokens_bf16, const int32_t* ids, const float* weights,
                              const int32_t* rank, const int32_t* group_offsets,
                              const float* input_gs, int tokens, int hidden, int topk,
                              int expert_first, int experts_local, void* a_q, void* a_sf,
-                             float* row_weight, int32_t* row_token, void* stream);
+                             float* row_weight, int32_t* row_token, void* sf_rows, int rows_cap,
+                             const int32_t* total_rows, void* stream);
 
 /* out[token] = bf16( sum over k (ascending, fp32) of y[group_offsets[e] + rank] ) over the
- * pairs routed to local experts; y (rows_cap, hidden) bf16, out (tokens, hidden) bf16. */
+ * pairs routed to local experts; y (rows_cap, hidden) bf16, out (tokens, hidden) bf16;
+ * topk <= 64. */
 int msc_moe_unpermute(const void* y, const int32_t* ids, const int32_t* rank,
                       const int32_t* group_offsets, void* out, int tokens, int hidden, int topk,
                       int expert_first, int experts_local, void* stream);
@@ -380,7 +389,8 @@ int msc_ep_combine(const void* const* peer_y, const int32_t* ids, const int32_t*
  * when the second GEMM scattered every pair's result row to the token's home rank.
  * y_pairs (tokens * topk, hidden) bf16, out (tokens, hidden) bf16.  pair_row (tokens, topk) i32
  * or NULL: pairs marked negative by msc_ep_dispatch_quantize (dropped because the owner's
- * buffers were full) are left out of the sum; their row of y_pairs holds stale data. */
+ * buffers were full) are left out of the sum; their row of y_pairs holds stale data.
+ * topk <= 64. */
 int msc_ep_sum_pairs(const void* y_pairs, const int32_t* pair_row, void* out, int tokens, int hidden,
                      int topk, void* stream);
 

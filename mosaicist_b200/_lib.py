@@ -58,7 +58,7 @@ SIGNATURES = {
     "msc_moe_route_topk": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "msc_moe_plan": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "msc_moe_plan_noalloc": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P]),
-    "msc_moe_permute_quantize": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "msc_moe_permute_quantize": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P, _P]),
     "msc_moe_unpermute": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "msc_peer_alloc": (_I, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), _P]),
     "msc_peer_open": (_I, [_P, ctypes.POINTER(ctypes.c_void_p)]),

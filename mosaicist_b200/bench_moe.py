@@ -160,7 +160,8 @@ def measure(args, rank: int, world: int, local: int, detail: bool = True) -> dic
             "gather_quantize": lambda: _lib.check(lib.msc_moe_permute_quantize(
                 tokens.data_ptr(), L.ids.data_ptr(), L.weights.data_ptr(), L.rank.data_ptr(),
                 L.group_offsets.data_ptr(), L.input_gs.data_ptr(), T_loc, h, k, 0, E_loc, L.a_q.data_ptr(),
-                L.a_sf.data_ptr(), L.row_weight.data_ptr(), L.row_token.data_ptr(), st)),
+                L.a_sf.data_ptr(), L.row_weight.data_ptr(), L.row_token.data_ptr(),
+                None if L.sf_rows is None else L.sf_rows.data_ptr(), L.rows_cap, L.total_rows.data_ptr(), st)),
             "gemm1": lambda: ops.ragged_grouped_gemm_nvfp4(L.a_q, L.a_sf, L.w1_q, L.w1_sf, L.group_offsets,
                                                             L.group_rows, L.alpha1, None, L.config, out=L.gateup),
             "silu_mul_quantize": lambda: ops.quantize_nvfp4_ragged(L.gateup, L.a2_gs, L.group_offsets,

@@ -25,6 +25,7 @@
 namespace msc {
 
 constexpr int kMaxPeers = 16;
+constexpr int kMaxSumTopk = 64;   // pairs of one token the final sum stages
 constexpr uint32_t kStatusEpOverflow = 0x00E00000u;   // a destination row beyond rows_cap
 
 // ---- signalling between ranks ----------------------------------------------------------------
@@ -339,30 +340,46 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p
 __global__ void __launch_bounds__(256)
 ep_sum_pairs_kernel(const __nv_bfloat16* __restrict__ y_pairs, const int* __restrict__ pair_row,
                     __nv_bfloat16* __restrict__ out, int tokens, int hidden, int topk) {
+  // one CTA per token: which pairs count is looked up once, then every thread sums 8 columns at a
+  // time with the loads of up to eight pairs issued before the first addition
+  __shared__ int s_have[kMaxSumTopk];
+  const long long token = blockIdx.x;
+  if ((int)threadIdx.x < topk)
+    s_have[threadIdx.x] = pair_row ? (__ldg(pair_row + token * topk + threadIdx.x) >= 0) : 1;
+  __syncthreads();
   const int vecs = hidden >> 3;
-  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long token = unit / vecs;
-  const int vc = (int)(unit - token * vecs);
-  if (token >= tokens) return;
-  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (int k = 0; k < topk; ++k) {
-    if (pair_row && __ldg(pair_row + token * topk + k) < 0) continue;
-    const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(y_pairs + ((size_t)token * topk + k) * hidden) + vc);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  constexpr int kBatch = 8;
+  const uint4* src = reinterpret_cast<const uint4*>(y_pairs + (size_t)token * topk * hidden);
+  for (int vc = threadIdx.x; vc < vecs; vc += blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k0 = 0; k0 < topk; k0 += kBatch) {
+      uint4 raw[kBatch];
+      bool have[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        have[j] = k0 + j < topk && s_have[k0 + j];
+        if (have[j]) raw[j] = __ldcg(src + (size_t)(k0 + j) * vecs + vc);
+      }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        if (!have[j]) continue;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          acc[2 * i] = __fadd_rn(acc[2 * i], f.x);
+          acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], f.y);
+        }
+      }
+    }
+    uint32_t w[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(h[j]);
-      acc[2 * j] = __fadd_rn(acc[2 * j], f.x);
-      acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], f.y);
+      __nv_bfloat162 pr = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&pr);
     }
+    reinterpret_cast<uint4*>(out + (size_t)token * hidden)[vc] = make_uint4(w[0], w[1], w[2], w[3]);
   }
-  uint32_t w[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    __nv_bfloat162 pr = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    w[j] = *reinterpret_cast<uint32_t*>(&pr);
-  }
-  reinterpret_cast<uint4*>(out + (size_t)token * hidden)[vc] = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 static int check_world(int world, int experts_total) {
@@ -555,10 +572,8 @@ int msc_ep_sum_pairs(const void* y_pairs, const int32_t* pair_row, void* out, in
   if (!y_pairs || !out) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
   if (tokens <= 0 || topk <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
   if (hidden <= 0 || hidden % 8) return msc::fail(MSC_ERR_BAD_ARG, "hidden=%d must be a multiple of 8", hidden);
-  const long long units = (long long)tokens * (hidden / 8);
-  const long long blocks = (units + 255) / 256;
-  if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
-  msc::ep_sum_pairs_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (topk > msc::kMaxSumTopk) return msc::fail(MSC_ERR_UNSUPPORTED, "topk=%d exceeds %d", topk, msc::kMaxSumTopk);
+  msc::ep_sum_pairs_kernel<<<(unsigned)tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(y_pairs), pair_row, static_cast<__nv_bfloat16*>(out), tokens, hidden,
       topk);
   MSC_CUDA_OK(cudaGetLastError());

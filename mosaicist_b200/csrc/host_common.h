@@ -55,6 +55,11 @@ void clear_tmap_cache();
 
 int num_sms();
 
+// Scale re-tiling (quantize.cu): (groups, mn, kwords * 4) row-major bytes to the 128-row MMA
+// tiling; rows_used (device, may be null, one group only) bounds the tiles that are written.
+int launch_sf_swizzle(const void* sf_rowmajor, void* sf_tiled, int groups, int mn, int kwords,
+                      const int* rows_used, cudaStream_t stream);
+
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device); safe to call from
 // several host threads.
 int allow_dynamic_smem(const void* kernel, int bytes);

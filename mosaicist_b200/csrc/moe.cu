@@ -10,6 +10,7 @@
 // row-concatenated, 128-aligned group layout the ragged GEMM entry points consume, with the
 // per-row arithmetic of quantize_nvfp4 (nvfp4.py:39-57).
 #include "host_common.h"
+#include "ptx.cuh"
 #include "quantize_common.cuh"
 
 #include <mutex>
@@ -194,101 +195,144 @@ struct PermuteParams {
   const float* gs;               // (experts_local) input global scale per expert
   uint8_t* q;                    // (rows_cap, hidden/2)
   uint8_t* sf;                   // tiled (rows_cap/128, hidden/64, 32, 16)
+  uint8_t* sf_rows;              // (rows_cap, hidden/16) row-major staging for the scales, or null
   float* row_weight;             // (rows_cap)
   int* row_token;                // (rows_cap)
   int entries, hidden, topk, expert_first, experts_local;
 };
 
-// One thread per (token, 16-value block): the block is loaded once and written to the row of
-// every expert the token is routed to.  The quantised bytes depend on the expert only through
-// its global scale, so they are recomputed only when that scale differs from the previous
-// expert's (with one shared input scale a block is quantised once instead of topk times).
-__global__ void __launch_bounds__(256) moe_permute_quantize_kernel(const PermuteParams p) {
+constexpr int kMaxTopk = 64;   // pairs of one token the dispatch and combine kernels stage
+
+// CTAs walk the tokens.  For each token the first warps look its pairs up once (expert, global
+// scale, destination row); the CTA quantises the token's row into shared memory and one thread
+// sends it to the row of every expert the token is routed to as one untiled bulk copy each
+// (3.5 KB at hidden 7168) instead of hundreds of 8-byte stores.  The scale bytes go out either as
+// words of the tiled layout (4 bytes every 512: one L2 transaction per word, which at top-8
+// costs as much as everything else in the kernel) or, given a row-major staging buffer, as a
+// second bulk copy per row that a re-tiling pass turns into the tiled layout afterwards.  Two
+// row buffers alternate, so the copies of one token leave while the
+// next is quantised.  The quantised bytes depend on the expert only through its global scale,
+// so the row is re-quantised only when that scale differs from the one in shared memory (with
+// one shared input scale a token is quantised once instead of topk times).
+__global__ void __launch_bounds__(128) moe_permute_quantize_kernel(const PermuteParams p, int tokens) {
+  extern __shared__ __align__(16) uint8_t row_smem[];   // 2 x ([hidden/2] values, [hidden/16] scales)
+  __shared__ int s_dest[2][kMaxTopk];
+  __shared__ float s_gs[2][kMaxTopk];
   const int kblocks = p.hidden >> 4;
-  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long token = unit / kblocks;
-  const int kb = (int)(unit - token * kblocks);
-  const bool live = token * p.topk < p.entries;
-  float v[16];
-  if (live) load16_bf16(p.tokens + (size_t)token * p.hidden + kb * 16, v);
-  uint2 q8 = make_uint2(0u, 0u);
-  uint32_t sfb = 0;
-  float have_gs = -1.0f;   // global scales are positive: nothing is cached yet
-  // Experts are handled eight at a time: first every lookup of the batch (expert id, then its
-  // global scale, group offset and the pair's rank) is issued, so the dependent loads of the
-  // eight experts overlap instead of forming one chain per expert; then the rows are written.
-  constexpr int kBatch = 8;
-  for (int k0 = 0; k0 < p.topk; k0 += kBatch) {   // trip counts uniform over the warp
-    int dest[kBatch];
-    float gsv[kBatch];
-#pragma unroll
-    for (int j = 0; j < kBatch; ++j) {
-      const int k = k0 + j;
-      int e = -1;
-      if (live && k < p.topk) e = __ldg(p.ids + token * p.topk + k) - p.expert_first;
-      const bool valid = e >= 0 && e < p.experts_local;   // uniform over the 4 lanes of a unit
-      dest[j] = -1;
-      gsv[j] = 0.0f;
-      if (valid) {
-        gsv[j] = __ldg(p.gs + e);
-        dest[j] = __ldg(p.group_offsets + e) + __ldg(p.rank + token * p.topk + k);
+  const int kwords = kblocks >> 2;
+  const int row_bytes = ((p.hidden >> 1) + kblocks + 15) & ~15;   // bulk copies start 16-byte aligned
+  int it = 0;
+  for (long long token = blockIdx.x; token < tokens; token += gridDim.x, ++it) {
+    const int buf = it & 1;
+    uint8_t* s_q = row_smem + buf * row_bytes;
+    uint8_t* s_sf = s_q + (p.hidden >> 1);
+    // the copies of the token before last have read this buffer; the last token's may still run
+    if (threadIdx.x == 0) bulk_wait_group_read1();
+    if ((int)threadIdx.x < p.topk) {
+      const int k = threadIdx.x;
+      const int e = __ldg(p.ids + token * p.topk + k) - p.expert_first;
+      int dest = -1;
+      float g = 0.0f;
+      if (e >= 0 && e < p.experts_local) {
+        g = __ldg(p.gs + e);
+        dest = __ldg(p.group_offsets + e) + __ldg(p.rank + token * p.topk + k);
+        p.row_weight[dest] = __ldg(p.weights + token * p.topk + k);
+        p.row_token[dest] = (int)token;
       }
+      s_dest[buf][k] = dest;
+      s_gs[buf][k] = g;
     }
-#pragma unroll
-    for (int j = 0; j < kBatch; ++j) {
-      if (k0 + j >= p.topk) break;                        // uniform
-      const bool valid = dest[j] >= 0;
-      if (valid) {
-        if (gsv[j] != have_gs) {
-          quantize_16(v, gsv[j], q8, sfb);
-          have_gs = gsv[j];
+    __syncthreads();
+    float have_gs = -1.0f;   // global scales are positive: nothing is quantised yet
+    for (int k = 0; k < p.topk; ++k) {            // CTA-uniform control flow throughout
+      const int dest = s_dest[buf][k];
+      if (dest < 0) continue;
+      const float g = s_gs[buf][k];
+      if (g != have_gs) {
+        if (have_gs >= 0.0f) {                    // this token's earlier copies still read the row
+          if (threadIdx.x == 0) {
+            bulk_commit_group();
+            bulk_wait_group_read0();
+          }
+          __syncthreads();
         }
-        *reinterpret_cast<uint2*>(p.q + (size_t)dest[j] * (p.hidden >> 1) + kb * 8) = q8;
-        if (kb == 0) {
-          p.row_weight[dest[j]] = __ldg(p.weights + token * p.topk + k0 + j);
-          p.row_token[dest[j]] = (int)token;
+        for (int kb = threadIdx.x; kb < kblocks; kb += blockDim.x) {
+          float v[16];
+          load16_bf16(p.tokens + (size_t)token * p.hidden + kb * 16, v);
+          uint2 q8;
+          uint32_t sfb;
+          quantize_16(v, g, q8, sfb);
+          *reinterpret_cast<uint2*>(s_q + kb * 8) = q8;
+          s_sf[kb] = (uint8_t)sfb;
         }
+        fence_proxy_async_smem();
+        __syncthreads();
+        have_gs = g;
       }
-      const uint32_t word = gather_scale_word(sfb);
-      if (valid && (kb & 3) == 0)
-        *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word(dest[j], kb >> 2, kblocks >> 2)) = word;
+      if (threadIdx.x == 0) {
+        bulk_store_1d(p.q + (size_t)dest * (p.hidden >> 1), smem_u32(s_q), (uint32_t)(p.hidden >> 1));
+        if (p.sf_rows) bulk_store_1d(p.sf_rows + (size_t)dest * kblocks, smem_u32(s_sf), (uint32_t)kblocks);
+      }
+      if (!p.sf_rows)
+        for (int w = threadIdx.x; w < kwords; w += blockDim.x)
+          *reinterpret_cast<uint32_t*>(p.sf + tiled_sf_word(dest, w, kwords)) =
+              reinterpret_cast<const uint32_t*>(s_sf)[w];
     }
+    if (threadIdx.x == 0) bulk_commit_group();    // one group per token (empty ones count too)
   }
+  if (threadIdx.x == 0) bulk_wait_group_read0();  // the rows are read before the CTA retires
 }
 
 // ---- combine -----------------------------------------------------------------------------
+// One CTA per token: the rows holding the token's expert outputs are looked up once, then
+// every thread sums 8 columns at a time over those rows, in the order of the token's pairs,
+// with the loads of up to eight rows issued before the first addition.
 __global__ void __launch_bounds__(256)
 moe_unpermute_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ ids,
                      const int* __restrict__ rank, const int* __restrict__ group_offsets,
                      __nv_bfloat16* __restrict__ out, int tokens, int hidden, int topk,
                      int expert_first, int experts_local) {
-  const int vecs = hidden >> 3;  // 8 bf16 per thread
-  const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long token = unit / vecs;
-  const int vc = (int)(unit - token * vecs);
-  if (token >= tokens) return;
-  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (int k = 0; k < topk; ++k) {
-    const long long entry = token * topk + k;
+  __shared__ int s_row[kMaxTopk];
+  const long long token = blockIdx.x;
+  if ((int)threadIdx.x < topk) {
+    const long long entry = token * topk + threadIdx.x;
     const int e = __ldg(ids + entry) - expert_first;
-    if (e < 0 || e >= experts_local) continue;
-    const int row = __ldg(group_offsets + e) + __ldg(rank + entry);
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(y + (size_t)row * hidden) + vc);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    s_row[threadIdx.x] = (e < 0 || e >= experts_local) ? -1 : __ldg(group_offsets + e) + __ldg(rank + entry);
+  }
+  __syncthreads();
+  const int vecs = hidden >> 3;  // 8 bf16 per thread and step
+  constexpr int kBatch = 8;
+  for (int vc = threadIdx.x; vc < vecs; vc += blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k0 = 0; k0 < topk; k0 += kBatch) {
+      uint4 raw[kBatch];
+      bool have[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int row = (k0 + j < topk) ? s_row[k0 + j] : -1;
+        have[j] = row >= 0;
+        if (have[j]) raw[j] = __ldg(reinterpret_cast<const uint4*>(y + (size_t)row * hidden) + vc);
+      }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        if (!have[j]) continue;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          acc[2 * i] = __fadd_rn(acc[2 * i], f.x);
+          acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], f.y);
+        }
+      }
+    }
+    uint32_t w[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(h[j]);
-      acc[2 * j] = __fadd_rn(acc[2 * j], f.x);
-      acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], f.y);
+      __nv_bfloat162 pr = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&pr);
     }
+    reinterpret_cast<uint4*>(out + (size_t)token * hidden)[vc] = make_uint4(w[0], w[1], w[2], w[3]);
   }
-  uint32_t w[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    __nv_bfloat162 pr = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    w[j] = *reinterpret_cast<uint32_t*>(&pr);
-  }
-  reinterpret_cast<uint4*>(out + (size_t)token * hidden)[vc] = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 static int launch_plan(const int32_t* ids, int entries, int expert_first, int experts_local,
@@ -390,7 +434,8 @@ int msc_moe_permute_quantize(const void* tokens_bf16, const int32_t* ids, const 
                              const int32_t* rank, const int32_t* group_offsets,
                              const float* input_gs, int tokens, int hidden, int topk,
                              int expert_first, int experts_local, void* a_q, void* a_sf,
-                             float* row_weight, int32_t* row_token, void* stream) {
+                             float* row_weight, int32_t* row_token, void* sf_rows, int rows_cap,
+                             const int32_t* total_rows, void* stream) {
   if (!tokens_bf16 || !ids || !weights || !rank || !group_offsets || !input_gs || !a_q || !a_sf ||
       !row_weight || !row_token)
     return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
@@ -401,13 +446,34 @@ int msc_moe_permute_quantize(const void* tokens_bf16, const int32_t* ids, const 
   p.ids = ids; p.weights = weights; p.rank = rank; p.group_offsets = group_offsets; p.gs = input_gs;
   p.q = static_cast<uint8_t*>(a_q); p.sf = static_cast<uint8_t*>(a_sf);
   p.row_weight = row_weight; p.row_token = row_token;
+  // the staged form needs scale rows that bulk copies can carry (a multiple of 16 bytes)
+  const bool staged = sf_rows != nullptr;
+  if (staged) {
+    if (hidden % 256) return msc::fail(MSC_ERR_BAD_ARG, "sf_rows needs hidden %% 256 == 0, got %d", hidden);
+    if (rows_cap <= 0 || rows_cap % 128) return msc::fail(MSC_ERR_BAD_ARG, "rows_cap=%d must be a positive multiple of 128", rows_cap);
+    if (reinterpret_cast<uintptr_t>(sf_rows) % 16 || reinterpret_cast<uintptr_t>(a_sf) % 16)
+      return msc::fail(MSC_ERR_BAD_ARG, "sf_rows and a_sf must be 16-byte aligned");
+  }
+  p.sf_rows = static_cast<uint8_t*>(sf_rows);
   p.entries = tokens * topk; p.hidden = hidden; p.topk = topk;
   p.expert_first = expert_first; p.experts_local = experts_local;
-  const long long units = (long long)tokens * (hidden / 16);
-  const long long blocks = (units + 255) / 256;
-  if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
-  msc::moe_permute_quantize_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  if (topk > msc::kMaxTopk) return msc::fail(MSC_ERR_UNSUPPORTED, "topk=%d exceeds %d", topk, msc::kMaxTopk);
+  if (reinterpret_cast<uintptr_t>(a_q) % 16)
+    return msc::fail(MSC_ERR_BAD_ARG, "a_q must be 16-byte aligned");
+  const int smem = 2 * ((hidden / 2 + hidden / 16 + 15) & ~15);
+  if (smem > 200 * 1024) return msc::fail(MSC_ERR_UNSUPPORTED, "hidden=%d: two rows do not fit in shared memory", hidden);
+  if (smem > 48 * 1024)
+    if (int rc = msc::allow_dynamic_smem(reinterpret_cast<const void*>(msc::moe_permute_quantize_kernel), 200 * 1024))
+      return rc;
+  // enough CTAs to fill every SM (16 x 128 threads), each walking its share of the tokens
+  const int sms = msc::num_sms();
+  if (sms <= 0) return msc::fail(MSC_ERR_CUDA, "could not query the SM count");
+  const int grid = tokens < 16 * sms ? tokens : 16 * sms;
+  msc::moe_permute_quantize_kernel<<<grid, 128, smem, static_cast<cudaStream_t>(stream)>>>(p, tokens);
   MSC_CUDA_OK(cudaGetLastError());
+  if (staged)
+    return msc::launch_sf_swizzle(sf_rows, a_sf, 1, rows_cap, hidden / 64, total_rows,
+                                  static_cast<cudaStream_t>(stream));
   return MSC_OK;
 }
 
@@ -417,10 +483,8 @@ int msc_moe_unpermute(const void* y, const int32_t* ids, const int32_t* rank,
   if (!y || !ids || !rank || !group_offsets || !out) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
   if (tokens <= 0 || topk <= 0 || experts_local <= 0) return msc::fail(MSC_ERR_BAD_ARG, "sizes must be positive");
   if (hidden <= 0 || hidden % 8) return msc::fail(MSC_ERR_BAD_ARG, "hidden=%d must be a multiple of 8", hidden);
-  const long long units = (long long)tokens * (hidden / 8);
-  const long long blocks = (units + 255) / 256;
-  if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
-  msc::moe_unpermute_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (topk > msc::kMaxTopk) return msc::fail(MSC_ERR_UNSUPPORTED, "topk=%d exceeds %d", topk, msc::kMaxTopk);
+  msc::moe_unpermute_kernel<<<(unsigned)tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(y), ids, rank, group_offsets,
       static_cast<__nv_bfloat16*>(out), tokens, hidden, topk, expert_first, experts_local);
   MSC_CUDA_OK(cudaGetLastError());

@@ -122,6 +122,63 @@ sf_swizzle_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, in
   reinterpret_cast<uint32_t*>(dst)[w] = val;
 }
 
+// The same re-tiling through shared memory: a CTA takes 32 bytes (8 words) of each of a tile's
+// 128 rows - two lanes read one full sector of a row - and writes eight 512-byte chunks of the
+// tiling with one 16-byte store per thread.  The tile's rows sit at a 9-word pitch, so the
+// column reads of the second phase fall in 32 different banks.  With rows_used (device, one
+// group only) tiles at or beyond that row are left alone.  Needs kwords % 4 == 0 and 16-byte
+// aligned pointers.
+__global__ void __launch_bounds__(256)
+sf_swizzle_tile_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int groups, int mn,
+                       int kwords, const int* __restrict__ rows_used) {
+  __shared__ uint32_t tile[128 * 9];
+  const int tiles = (mn + 127) >> 7;
+  const int cgroups = (kwords + 7) >> 3;
+  const int cg = blockIdx.x % cgroups;
+  const int rest = blockIdx.x / cgroups;
+  const int t = rest % tiles, g = rest / tiles;
+  if (rows_used && t * 128 >= __ldg(rows_used)) return;   // uniform over the CTA
+  {
+    const int row_l = threadIdx.x >> 1, half = threadIdx.x & 1;
+    const int row = t * 128 + row_l, c0 = cg * 8 + half * 4;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < mn && c0 < kwords)
+      v = __ldg(reinterpret_cast<const uint4*>(src + ((size_t)g * mn + row) * kwords * 4 + (size_t)c0 * 4));
+    uint32_t* d = tile + row_l * 9 + half * 4;
+    d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+  }
+  __syncthreads();
+  const int cc = threadIdx.x >> 5, b = threadIdx.x & 31;
+  const int c = cg * 8 + cc;
+  if (c < kwords) {
+    const uint4 o = make_uint4(tile[b * 9 + cc], tile[(32 + b) * 9 + cc], tile[(64 + b) * 9 + cc],
+                               tile[(96 + b) * 9 + cc]);
+    *reinterpret_cast<uint4*>(dst + ((((size_t)g * tiles + t) * kwords + c) * 32 + b) * 16) = o;
+  }
+}
+
+int launch_sf_swizzle(const void* sf_rowmajor, void* sf_tiled, int groups, int mn, int kwords,
+                      const int* rows_used, cudaStream_t stream) {
+  const long long tiles = (mn + 127) / 128;
+  const bool by_tiles = kwords % 4 == 0 && reinterpret_cast<uintptr_t>(sf_rowmajor) % 16 == 0 &&
+                        reinterpret_cast<uintptr_t>(sf_tiled) % 16 == 0;
+  if (by_tiles) {
+    const long long blocks = (long long)groups * tiles * ((kwords + 7) / 8);
+    if (blocks > 0x7fffffffLL) return fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
+    sf_swizzle_tile_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+        static_cast<const uint8_t*>(sf_rowmajor), static_cast<uint8_t*>(sf_tiled), groups, mn, kwords,
+        groups == 1 ? rows_used : nullptr);
+  } else {
+    const long long total = (long long)groups * tiles * kwords * 128;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) return fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
+    sf_swizzle_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+        static_cast<const uint8_t*>(sf_rowmajor), static_cast<uint8_t*>(sf_tiled), groups, mn, kwords);
+  }
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
 static int quantize_common(const void* x, int x_dtype, const float* gs, const int32_t* group_offsets,
                            const int32_t* group_rows, void* q, void* sf, int sf_layout, int l,
                            long long rows_total, int m_stride, int k, int silu, void* stream) {
@@ -188,14 +245,8 @@ int msc_sf_swizzle(const void* sf_rowmajor, void* sf_tiled, int groups, int mn, 
   if (k_scales % 4) return msc::fail(MSC_ERR_BAD_ARG, "k_scales=%d must be a multiple of 4", k_scales);
   if (reinterpret_cast<uintptr_t>(sf_rowmajor) % 4 || reinterpret_cast<uintptr_t>(sf_tiled) % 4)
     return msc::fail(MSC_ERR_BAD_ARG, "scale pointers must be 4-byte aligned");
-  const int kwords = k_scales / 4;
-  const long long total = (long long)groups * ((mn + 127) / 128) * kwords * 128;
-  const long long blocks = (total + 255) / 256;
-  if (blocks > 0x7fffffffLL) return msc::fail(MSC_ERR_UNSUPPORTED, "problem too large for one launch");
-  msc::sf_swizzle_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint8_t*>(sf_rowmajor), static_cast<uint8_t*>(sf_tiled), groups, mn, kwords);
-  MSC_CUDA_OK(cudaGetLastError());
-  return MSC_OK;
+  return msc::launch_sf_swizzle(sf_rowmajor, sf_tiled, groups, mn, k_scales / 4, nullptr,
+                                static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -119,6 +119,10 @@ class MegaMoE:
         self.a_q = buf("a_q", (cap, self.h // 2), torch.uint8, False)
         self.a_sf = buf("a_sf", (cap // 128, self.h // 64, 32, 16), torch.uint8, True)
         self.row_weight = buf("row_weight", (cap,), torch.float32, True)
+        # row-major staging for the dispatch's scale bytes (the tiled layout is written by a
+        # re-tiling pass); layers fed by an expert-parallel exchange never dispatch themselves
+        self.sf_rows = (torch.zeros((cap, self.h // 16), dtype=torch.uint8, device=dev)
+                        if workspace is None and self.h % 256 == 0 else None)
         self.row_token = torch.zeros((cap,), **i32)
         self.gateup = torch.empty((cap, 2 * self.n), dtype=torch.bfloat16, device=dev)
         self.d_q = torch.empty((cap, self.n // 2), dtype=torch.uint8, device=dev)
@@ -153,7 +157,9 @@ class MegaMoE:
             tokens.data_ptr(), self.ids.data_ptr(), self.weights.data_ptr(), self.rank.data_ptr(),
             self.group_offsets.data_ptr(), self.input_gs.data_ptr(), T, self.h, K,
             self.expert_first, E, self.a_q.data_ptr(), self.a_sf.data_ptr(),
-            self.row_weight.data_ptr(), self.row_token.data_ptr(), st))
+            self.row_weight.data_ptr(), self.row_token.data_ptr(),
+            None if self.sf_rows is None else self.sf_rows.data_ptr(), self.rows_cap,
+            self.total_rows.data_ptr(), st))
         self.run_experts()
         if out is None:
             out = torch.empty((T, self.h), dtype=torch.bfloat16, device=tokens.device)

@@ -78,11 +78,14 @@ def test_route_ties_go_to_lower_index():
     assert got[0].tolist() == [0, 1, 2] and got[1].tolist() == [7, 40, 0]
 
 
-@pytest.mark.parametrize("first,local", [(0, 32), (8, 8), (0, 4)])
-def test_plan_and_gather_quantise_bit_exact(first, local):
+@pytest.mark.parametrize("first,local,h,staged", [(0, 32, 256, False), (8, 8, 256, True), (0, 4, 320, False),
+                                                  (0, 32, 768, True)])
+def test_plan_and_gather_quantise_bit_exact(first, local, h, staged):
+    """staged: the scale bytes leave as one bulk copy per row into a row-major buffer and a second
+    kernel tiles them; otherwise they are written word by word.  Same bytes either way."""
     from mosaicist_b200 import _lib
 
-    T_, E, k, h = 200, 32, 4, 256
+    T_, E, k = 200, 32, 4
     rng = np.random.default_rng([first, local])
     logits = rng.standard_normal((T_, E)).astype(np.float32)
     logits[:, 5] = -30.0                              # an expert nobody picks: an empty group
@@ -117,10 +120,13 @@ def test_plan_and_gather_quantise_bit_exact(first, local):
     rt = torch.full((cap,), -1, dtype=torch.int32, device="cuda")
     tk = T(np.asarray(tokens, np.float32)).to(torch.bfloat16)
     gst = T(gs)
+    sf_rows = torch.zeros((cap, h // 16), dtype=torch.uint8, device="cuda") if staged else None
     _lib.check(lib.msc_moe_permute_quantize(tk.data_ptr(), d_ids.data_ptr(), d_w.data_ptr(),
                                             rank.data_ptr(), offs.data_ptr(), gst.data_ptr(), T_, h, k,
                                             first, local, a_q.data_ptr(), a_sf.data_ptr(),
-                                            rw.data_ptr(), rt.data_ptr(), st))
+                                            rw.data_ptr(), rt.data_ptr(),
+                                            sf_rows.data_ptr() if staged else None, cap,
+                                            tot.data_ptr() if staged else None, st))
     qh, rth, rwh = a_q.cpu().numpy(), rt.cpu().numpy(), rw.cpu().numpy()
     sfh = np.asarray(__import__("mosaicist_b200.formats", fromlist=["x"]).from_mma_scale_layout(
         a_sf.cpu().numpy(), cap))
