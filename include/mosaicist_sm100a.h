@@ -48,7 +48,10 @@ typedef struct msc_gemm_cfg {
   int epilogue;  /* MSC_EPI_*                                                            */
   int cta_pair;  /* 1: two CTAs share one 256x256 tile (tcgen05 cta_group::2; needs n % 256 == 0,
                     ignores tile_n); 2: one CTA per tile; 0: the library chooses (pairs when
-                    tile_n is 0, n % 256 == 0 and groups have >= 256 rows).  The counterpart
+                    tile_n is 0, n % 256 == 0 and groups have >= 256 rows); 3 (NVFP4 over
+                    row-concatenated groups only): CTA pairs with the weights on the MMA's M side
+                    and the tokens on N, so that one tile takes up to 320 rows of a group - the
+                    form for groups of a few hundred rows (a routed MoE layer).  The counterpart
                     of the reference's `collective` knob (cand_pallas_gemm.py:31)          */
   int sf_warps;  /* CTA-pair kernel only. 1: four extra warps write the scale factors into tensor
                     memory (tcgen05.st) instead of the MMA warp copying them (tcgen05.cp);
@@ -109,7 +112,9 @@ int msc_grouped_gemm_nvfp4_ragged(const void* a_q, const void* a_sf, const void*
  * with out_global_scale[g].  Replaces gemm1_silu_quantize
  * (experiments/flashinfer-megamoe-sm100a/gemm1_silu_quantize.py:94-241) and produces exactly
  * the bytes of msc_grouped_gemm_nvfp4_ragged followed by msc_nvfp4_quantize_ragged(silu=1),
- * without the (rows_total, n2) bf16 round trip.  CTA-pair kernel; n2 % 256 == 0, k % 64 == 0. */
+ * without the (rows_total, n2) bf16 round trip.  CTA-pair kernel; n2 % 256 == 0, k % 64 == 0.
+ * With cfg->cta_pair == 3 (tokens on N) w1_q / w1_sf must be the interleaved copy made by
+ * msc_swiglu_interleave_w1; the result is the same bytes. */
 int msc_grouped_gemm_nvfp4_swiglu_ragged(const void* a_q, const void* a_sf, const void* w1_q,
                                          const void* w1_sf, const float* alpha,
                                          const int32_t* group_offsets, const int32_t* group_rows,
@@ -293,6 +298,14 @@ int msc_moe_permute_quantize(const void* tokens_bf16, const int32_t* ids, const 
 int msc_moe_unpermute(const void* y, const int32_t* ids, const int32_t* rank,
                       const int32_t* group_offsets, void* out, int tokens, int hidden, int topk,
                       int expert_first, int experts_local, void* stream);
+
+/* w1 for the tokens-on-N form of msc_grouped_gemm_nvfp4_swiglu_ragged: gate and up rows
+ * interleaved in blocks of 64, so that every 128 consecutive rows hold both halves of 64 output
+ * columns - out row 128 i + j is gate row 64 i + j for j < 64, up row n2/2 + 64 i + j - 64
+ * otherwise - and the tiled scales permuted alike.  Done once when the weights are loaded; not
+ * in place.  w1_q / out_q (l, n2, k/2), w1_sf / out_sf (l, n2/128, k/64, 32, 16). */
+int msc_swiglu_interleave_w1(const void* w1_q, const void* w1_sf, void* out_q, void* out_sf, int l,
+                             int n2, int k, void* stream);
 
 /* msc_grouped_gemm_nvfp4_ragged whose result rows are scattered instead of stored in place:
  * row r (times alpha and, if given, row_scale[r]) goes to

@@ -55,6 +55,7 @@ SIGNATURES = {
     "msc_int4_dequant_bf16": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
     "msc_grouped_gemm_bf16_ragged": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "msc_grouped_gemm_bf16_int4_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "msc_swiglu_interleave_w1": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "msc_moe_route_topk": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "msc_moe_plan": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "msc_moe_plan_noalloc": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P]),

@@ -46,6 +46,8 @@ def parser():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--cta-pair", type=int, default=0)
     ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--gemm1-tokens-on-n", action="store_true",
+                    help="fused GEMM1 with the tokens on the MMA's N side (one GPU)")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer")
     ap.add_argument("--sync", choices=["flags", "nccl"], default="flags",
                     help="peer exchange: synchronise through flags in peer memory / NCCL collectives")
@@ -95,7 +97,8 @@ def measure(args, rank: int, world: int, local: int, detail: bool = True) -> dic
 
     cfg = ops.GemmConfig(tile_n=args.tile_n, cta_pair=args.cta_pair)
     if world == 1:
-        layer = MegaMoE(*w, gs_in, gs_a2, topk=k, max_tokens=T_loc, config=cfg)
+        layer = MegaMoE(*w, gs_in, gs_a2, topk=k, max_tokens=T_loc, config=cfg,
+                        gemm1_tokens_on_n=args.gemm1_tokens_on_n)
         run = lambda: layer.forward(tokens, logits)
     elif args.exchange == "nccl":
         # a rank can receive up to 2x its even share before the workspace is exceeded
@@ -168,7 +171,7 @@ def measure(args, rank: int, world: int, local: int, detail: bool = True) -> dic
                                                                     L.group_rows, silu=True, out=(L.d_q, L.d_sf)),
             "gemm1_swiglu_quantize_fused": lambda: ops.ragged_gemm1_swiglu_quantize(
                 L.a_q, L.a_sf, L.w1_q, L.w1_sf, L.group_offsets, L.group_rows, L.alpha1, L.a2_gs,
-                out=(L.d_q, L.d_sf)),
+                L.gemm1_config, out=(L.d_q, L.d_sf)),
             "gemm2": lambda: ops.ragged_grouped_gemm_nvfp4(L.d_q, L.d_sf, L.w2_q, L.w2_sf, L.group_offsets,
                                                             L.group_rows, L.alpha2, L.row_weight, L.config, out=L.y),
             "combine": lambda: _lib.check(lib.msc_moe_unpermute(

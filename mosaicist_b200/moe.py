@@ -77,7 +77,8 @@ class MegaMoE:
     def __init__(self, w1_q, w1_sf, w1_gs, w1_alpha, w2_q, w2_sf, w2_gs, w2_alpha, input_gs, a2_gs,
                  topk: int, max_tokens: int, expert_first: int = 0,
                  config: ops.GemmConfig = ops.GemmConfig(), fuse_gemm1: bool = True,
-                 rows_cap: int | None = None, workspace: dict | None = None):
+                 rows_cap: int | None = None, workspace: dict | None = None,
+                 gemm1_tokens_on_n: bool = False):
         """`rows_cap` overrides the row capacity of the grouped buffers (default: room for
         max_tokens * topk rows plus 127 padding rows per expert); `workspace` may provide the
         buffers other GPUs access under expert parallelism (a_q, a_sf, row_weight, y)."""
@@ -88,6 +89,14 @@ class MegaMoE:
         # two-kernel path, which stays available for comparison
         self.fuse_gemm1 = fuse_gemm1 and (n2 % 256 == 0)
         self.w1_q, self.w1_sf, self.w2_q, self.w2_sf = w1_q, w1_sf, w2_q, w2_sf
+        # the fused GEMM1 with the tokens on the MMA's N side (GemmConfig(cta_pair=3)) reads w1
+        # with gate and up rows interleaved in blocks of 64: the layer then keeps that copy only
+        self.gemm1_config = ops.GemmConfig()
+        if gemm1_tokens_on_n:
+            if not self.fuse_gemm1:
+                raise ValueError("gemm1_tokens_on_n needs the fused GEMM1 (2n % 256 == 0)")
+            self.w1_q, self.w1_sf = ops.swiglu_interleave_w1(w1_q, w1_sf)
+            self.gemm1_config = ops.GemmConfig(cta_pair=3)
         self.input_gs, self.a2_gs = input_gs.contiguous(), a2_gs.contiguous()
         self.alpha1 = (w1_alpha / (input_gs * w1_gs)).float().contiguous()
         self.alpha2 = (w2_alpha / (a2_gs * w2_gs)).float().contiguous()
@@ -181,7 +190,7 @@ class MegaMoE:
         if self.fuse_gemm1:
             ops.ragged_gemm1_swiglu_quantize(self.a_q, self.a_sf, self.w1_q, self.w1_sf,
                                              self.group_offsets, self.group_rows, self.alpha1,
-                                             self.a2_gs, out=(self.d_q, self.d_sf))
+                                             self.a2_gs, self.gemm1_config, out=(self.d_q, self.d_sf))
         else:
             ops.ragged_grouped_gemm_nvfp4(self.a_q, self.a_sf, self.w1_q, self.w1_sf, self.group_offsets,
                                           self.group_rows, self.alpha1, None, self.config, out=self.gateup)

@@ -370,6 +370,18 @@ def mixed_grouped_gemm_int4(a, b_q, scales, group_offsets, group_rows, alpha=Non
     return out
 
 
+def swiglu_interleave_w1(w1_q, w1_sf):
+    """w1 (l, 2n, k/2) + tiled scales -> the copy the tokens-on-N fused GEMM1 reads
+    (GemmConfig(cta_pair=3)): gate and up rows interleaved in blocks of 64."""
+    _need(w1_q, "w1_q", _BYTES)
+    l, n2, kh = w1_q.shape
+    _need(w1_sf, "w1_sf", _BYTES, (l, n2 // 128, kh // 32, 32, 16))
+    out_q, out_sf = torch.empty_like(w1_q), torch.empty_like(w1_sf)
+    _lib.check(_lib.load().msc_swiglu_interleave_w1(_ptr(w1_q), _ptr(w1_sf), _ptr(out_q), _ptr(out_sf), l, n2,
+                                                    kh * 2, _stream()))
+    return out_q, out_sf
+
+
 def ragged_gemm1_swiglu_quantize(a_q, a_sf, w1_q, w1_sf, group_offsets, group_rows, alpha, out_global_scale,
                                  config: GemmConfig = GemmConfig(), out=None):
     """GEMM1 + SiLU(gate) * up + NVFP4 requantisation in one kernel (the reference's

@@ -193,7 +193,13 @@ def test_mxfp8_ragged_bit_exact(rows_list, n, k, cfg):
     assert np.isnan(got[~mask[:, 0]]).all()
 
 
-RAGGED_NVFP4 = RAGGED[1:]
+RAGGED_NVFP4 = RAGGED[1:] + [
+    # tokens on the MMA's N side (cta_pair=3): tiles of one MMA (<= 256 rows), of two (257 - 320), several
+    # token tiles per group (the last one taking a remainder of up to 64), empty and one-row groups
+    ([200, 0, 50, 384, 257], 256, 1024, {"cta_pair": 3}),
+    ([272, 1, 16, 17, 320, 321, 576, 640, 129, 255, 256], 512, 640, {"cta_pair": 3}),
+    ([305, 240, 1000], 256, 896, {"cta_pair": 3, "max_ctas": 4}),
+]
 
 
 @pytest.mark.parametrize("rows_list,n,k,cfg", RAGGED_NVFP4)

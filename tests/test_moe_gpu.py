@@ -227,11 +227,22 @@ def test_megamoe_layer(T_, E, k, h, n, first, local):
     assert np.array_equal(layer.ids.cpu().numpy(), ids)
     # with 8 of 32 experts local most tokens get no contribution: expect about 1 - (3/4)^2 non-zero
     _close(got, want, nonzero_fraction=0.5 if local == E else 0.25)
+    # the same layer with the fused GEMM1 on the tokens-on-N kernel: the very same bits
+    swapped = MegaMoE(d["w1_q"], d["w1_sf"], d["w1_gs"], d["w1_alpha"], d["w2_q"], d["w2_sf"], d["w2_gs"],
+                      d["w2_alpha"], T(input_gs), T(a2_gs), topk=k, max_tokens=T_, expert_first=first,
+                      gemm1_tokens_on_n=True)
+    assert np.array_equal(swapped.forward(tk, T(logits)).float().cpu().numpy(), got)
+    assert _lib.status_word() == 0
 
 
-@pytest.mark.parametrize("rows_list,n,k", [([256], 128, 256), ([300, 0, 77, 512, 129], 256, 640)])
-def test_fused_gemm1_swiglu_quantize_equals_two_kernel_path(rows_list, n, k):
-    """The fused epilogue must produce the very bytes of GEMM1 -> bf16 -> SiLU*up -> quantise."""
+@pytest.mark.parametrize("rows_list,n,k,swap", [([256], 128, 256, False), ([300, 0, 77, 512, 129], 256, 640, False),
+                                                # tokens on the MMA's N side: one and two MMAs per tile,
+                                                # several token tiles, every width of the narrow MMA
+                                                ([256], 128, 256, True), ([300, 0, 77, 576, 129, 257, 320, 321, 16], 256, 640, True),
+                                                ([272, 1, 240, 305], 512, 896, True)])
+def test_fused_gemm1_swiglu_quantize_equals_two_kernel_path(rows_list, n, k, swap):
+    """The fused epilogue must produce the very bytes of GEMM1 -> bf16 -> SiLU*up -> quantise;
+    swap: the tokens-on-N kernel on the interleaved copy of w1."""
     from mosaicist_b200 import _lib, ops
     from mosaicist_b200.formats import from_mma_scale_layout
 
@@ -253,8 +264,13 @@ def test_fused_gemm1_swiglu_quantize_equals_two_kernel_path(rows_list, n, k):
     o_t, r_t = T(np.array(offs, np.int32)), T(np.array(rows_list, np.int32))
     gateup = ops.ragged_grouped_gemm_nvfp4(dev["a_q"], dev["a_sf"], dev["w1_q"], dev["w1_sf"], o_t, r_t, T(alpha))
     want_q, want_sf = ops.quantize_nvfp4_ragged(gateup, T(a2_gs), o_t, r_t, silu=True)
-    got_q, got_sf = ops.ragged_gemm1_swiglu_quantize(dev["a_q"], dev["a_sf"], dev["w1_q"], dev["w1_sf"], o_t, r_t,
-                                                     T(alpha), T(a2_gs))
+    if swap:
+        wi_q, wi_sf = ops.swiglu_interleave_w1(dev["w1_q"], dev["w1_sf"])
+        got_q, got_sf = ops.ragged_gemm1_swiglu_quantize(dev["a_q"], dev["a_sf"], wi_q, wi_sf, o_t, r_t, T(alpha),
+                                                         T(a2_gs), ops.GemmConfig(cta_pair=3))
+    else:
+        got_q, got_sf = ops.ragged_gemm1_swiglu_quantize(dev["a_q"], dev["a_sf"], dev["w1_q"], dev["w1_sf"], o_t, r_t,
+                                                         T(alpha), T(a2_gs))
     assert _lib.status_word() == 0
     wq, gq = want_q.cpu().numpy(), got_q.cpu().numpy()
     wsf = from_mma_scale_layout(want_sf.cpu().numpy(), tot)
