@@ -283,19 +283,38 @@ def bind_to_gpu_numa_node(index: int):
         dev = torch.cuda.get_device_properties(index).pci_device_id
         path = pathlib.Path(f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node")
         node = int(path.read_text())
-        if node < 0:
-            return None
-        cpus = pathlib.Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip()
-        ids = set()
-        for part in cpus.split(","):
-            lo, _, hi = part.partition("-")
-            ids.update(range(int(lo), int(hi or lo) + 1))
-        ids &= os.sched_getaffinity(0)
-        if ids:
-            os.sched_setaffinity(0, ids)
-        return node
+        if node >= 0:
+            cpus = pathlib.Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip()
+            ids = set()
+            for part in cpus.split(","):
+                lo, _, hi = part.partition("-")
+                ids.update(range(int(lo), int(hi or lo) + 1))
+            ids &= os.sched_getaffinity(0)
+            if ids:
+                os.sched_setaffinity(0, ids)
+                return node
     except Exception:  # noqa: BLE001 - topology files are optional
-        return None
+        pass
+    try:
+        # where sysfs does not say (virtualised PCI topology), NVML's ideal CPU set for the GPU
+        import pynvml
+
+        pynvml.nvmlInit()
+        import torch
+
+        pr = torch.cuda.get_device_properties(index)
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(
+            ("%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)).encode())
+        words = 16   # 1024 CPUs: the host may have more than this process is allowed to use
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        ids = {64 * w + b for w, word in enumerate(mask) for b in range(64) if (word >> b) & 1}
+        ids &= os.sched_getaffinity(0)
+        if ids and ids != os.sched_getaffinity(0):
+            os.sched_setaffinity(0, ids)
+            return "nvml:%d-%d" % (min(ids), max(ids))
+    except Exception:  # noqa: BLE001 - NVML is optional
+        pass
+    return None
 
 
 def main():
