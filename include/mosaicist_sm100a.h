@@ -383,14 +383,30 @@ int msc_ep_wait(const int32_t* flags, int world, int slot, int epoch, void* stre
  * device pointers.  pair_row (tokens, topk) i32 receives that row for msc_ep_combine.  With
  * peer_row_dest (host array of `world` pointers to (rows_cap) i32, or NULL) the owner also
  * learns where the row's result belongs: code (rank << 26) | (token * topk + k), the form
- * msc_grouped_gemm_nvfp4_scatter_ragged takes. */
+ * msc_grouped_gemm_nvfp4_scatter_ragged takes.  With peer_row_next as well (same shape, or
+ * NULL; needs peer_row_dest, hidden % 256 == 0, topk <= 32) a token's rows on one owner are
+ * chained in pair order for msc_ep_presum_push: row_next holds the next row of the chain or -1,
+ * only the chain's first row keeps its code, the others get -2 there and in pair_row. */
 int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const float* weights,
                              const int32_t* rank_in_group, const int32_t* send_base,
                              const float* input_gs, int tokens, int hidden, int topk,
                              int experts_total, int world, void* const* peer_a_q,
                              void* const* peer_sf_rows, float* const* peer_row_weight,
-                             int32_t* const* peer_row_dest, int rank, int rows_cap,
-                             int32_t* pair_row, void* stream);
+                             int32_t* const* peer_row_dest, int32_t* const* peer_row_next, int rank,
+                             int rows_cap, int32_t* pair_row, void* stream);
+
+/* The combine with a token's results pre-summed on every rank they were computed on: for each
+ * local row r whose row_dest[r] >= 0 (the first row of a chain), bf16( sum in fp32, in chain
+ * order, of y[r], y[row_next[r]], ... ) is written to dest_bases[code >> 26] at row
+ * code & 0x3ffffff (codes outside dest_count / dest_rows are refused with status bit
+ * 0x00C00000).  y (rows, hidden) bf16 is what the second GEMM stored locally (routing weights
+ * applied); msc_ep_sum_pairs on the home rank then adds one row per rank the token visited.
+ * About a third fewer rows cross NVLink than with msc_grouped_gemm_nvfp4_scatter_ragged under
+ * uniform top-8 routing over 8 ranks; the transfer does not overlap the GEMM, and the result
+ * differs from the single-GPU layer by one extra bf16 rounding per rank. */
+int msc_ep_presum_push(const void* y, const int32_t* row_dest, const int32_t* row_next,
+                       void* const* dest_bases, int dest_count, int dest_rows, int rows, int hidden,
+                       void* stream);
 
 /* out[token] = bf16( sum over k (ascending, fp32) of y_owner[pair_row] ), reading each owner's
  * y (rows_cap, hidden) bf16 through `peer_y` (host array of `world` device pointers). */

@@ -68,7 +68,8 @@ SIGNATURES = {
     "msc_ep_offsets": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _P]),
     "msc_ep_signal": (_I, [_P, _I, _I, _I, _I, _P, _P, _I, _P]),
     "msc_ep_wait": (_I, [_P, _I, _I, _I, _P]),
-    "msc_ep_dispatch_quantize": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P]),
+    "msc_ep_dispatch_quantize": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _P, _P]),
+    "msc_ep_presum_push": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "msc_ep_sum_pairs": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "msc_grouped_gemm_nvfp4_scatter_ragged": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _CFG, _P]),
     "msc_ep_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),

@@ -51,7 +51,7 @@ def parser():
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer")
     ap.add_argument("--sync", choices=["flags", "nccl"], default="flags",
                     help="peer exchange: synchronise through flags in peer memory / NCCL collectives")
-    ap.add_argument("--combine", choices=["push", "pull"], default="push",
+    ap.add_argument("--combine", choices=["push", "pull", "presum"], default="push",
                     help="peer exchange: GEMM2 scatters result rows to the home ranks / the home rank pulls them")
     return ap
 
@@ -108,9 +108,11 @@ def measure(args, rank: int, world: int, local: int, detail: bool = True) -> dic
         run = lambda: layer.forward(tokens, logits)
     else:
         rows_cap = (2 * T_loc * k + 127 * E_loc + 127) // 128 * 128
-        push = args.combine == "push"
+        push = args.combine in ("push", "presum")
         bufs = PeerBuffers(rows_cap, h, T_loc * k if push else 0, E)
         extra = dict(row_dest=bufs.tensors["row_dest"], recv_y=bufs.tensors["recv_y"]) if push else {}
+        if args.combine == "presum":
+            extra.update(row_next=bufs.tensors["row_next"])
         if args.sync == "flags":
             extra.update(flags=bufs.tensors["flags"], counts_all=bufs.tensors["counts_all"])
         inner = MegaMoE(*w, gs_in, gs_a2, topk=1, max_tokens=1, expert_first=rank * E_loc, config=cfg,
@@ -148,6 +150,7 @@ def measure(args, rank: int, world: int, local: int, detail: bool = True) -> dic
                       (f"ep{world}, all-to-all bf16 dispatch + combine" if args.exchange == "nccl" else
                        f"ep{world}, NVFP4 dispatch into peer memory, bf16 results " +
                        ("scattered to the home rank by the GEMM2 epilogue" if args.combine == "push" else
+                        "summed per rank after GEMM2, one row per (token, rank) sent home" if args.combine == "presum" else
                         "pulled from peer memory") + f", sync by {args.sync}")}}
 
     if world == 1 and detail:

@@ -159,6 +159,7 @@ struct EpDispatchParams {
   uint8_t* sf[kMaxPeers];        // per rank: row-major (rows_cap, hidden/16)
   float* row_weight[kMaxPeers];  // per rank: (rows_cap)
   int* row_dest[kMaxPeers];      // per rank: (rows_cap) where the row's result goes, or all null
+  int* row_next[kMaxPeers];      // per rank: (rows_cap) next row of the same token there, or all null
   int entries, hidden, topk, experts_total, experts_local, rows_cap, rank;
 };
 
@@ -255,6 +256,27 @@ __global__ void __launch_bounds__(256) ep_dispatch_bulk_kernel(const EpDispatchP
     s_gs[k] = gs;
   }
   __syncthreads();
+  if (p.row_next[0] && (int)threadIdx.x < p.topk) {
+    // Same-rank pre-sum: the token's rows on one owner form a chain in pair order.  The first
+    // one keeps its destination code (the owner sends the chain's sum there); the others are
+    // marked absorbed on the owner (-2) and left out of this rank's final sum.
+    const int k = threadIdx.x, owner = s_owner[k];
+    if (owner >= 0) {
+      int next = -1;
+      bool first = true;
+      for (int j = 0; j < p.topk; ++j) {
+        if (j == k || s_owner[j] != owner) continue;
+        if (j < k) first = false;
+        else if (next < 0) next = s_dest[j];
+      }
+      const int dest = s_dest[k];
+      p.row_next[owner][dest] = next;
+      if (!first) {
+        p.row_dest[owner][dest] = -2;
+        p.pair_row[(long long)token * p.topk + k] = -2;
+      }
+    }
+  }
   float have_gs = -1.0f;
   for (int k = 0; k < p.topk; ++k) {          // block-uniform control flow throughout
     const int owner = s_owner[k];
@@ -382,6 +404,68 @@ ep_sum_pairs_kernel(const __nv_bfloat16* __restrict__ y_pairs, const int* __rest
   }
 }
 
+// ---- same-rank pre-sum ------------------------------------------------------------------------
+// After the second GEMM has stored its rows locally: one CTA per local row that heads a chain
+// (row_dest >= 0) adds the chain's rows in fp32, in chain order, rounds once to bf16 and writes
+// the sum into the home rank's recv_y at the row the code names.  A token's k experts sit on
+// about 5.3 of 8 ranks under uniform routing, so a third fewer rows cross NVLink than when
+// every row is scattered by the GEMM's epilogue; the price is that the transfer no longer
+// overlaps the GEMM, and one more rounding per rank the token visits.
+struct EpPresumParams {
+  const __nv_bfloat16* y;        // (rows, hidden) this rank's results, routing weight applied
+  const int* row_dest;           // (rows)
+  const int* row_next;           // (rows)
+  uint8_t* dest[kMaxPeers];      // every rank's recv_y
+  uint32_t* status;
+  int rows, hidden, dest_count, dest_rows;
+};
+
+__global__ void __launch_bounds__(256) ep_presum_push_kernel(const EpPresumParams p) {
+  const int row = blockIdx.x;
+  const int code = __ldg(p.row_dest + row);
+  if (code < 0) return;                                   // not a chain head (uniform over the CTA)
+  const int drank = code >> 26, drow = code & 0x03ffffff;
+  if (drank >= p.dest_count || drow >= p.dest_rows) {     // never turned into an address
+    if (threadIdx.x == 0) atomicOr(p.status, 0x00C00000u);
+    return;
+  }
+  __shared__ int s_chain[kMaxSumTopk];
+  __shared__ int s_len;
+  if (threadIdx.x == 0) {
+    int n = 0, r = row;
+    while (r >= 0 && r < p.rows && n < kMaxSumTopk) {     // bounded: a broken link cannot loop
+      s_chain[n++] = r;
+      r = __ldg(p.row_next + r);
+    }
+    s_len = n;
+  }
+  __syncthreads();
+  const int len = s_len, vecs = p.hidden >> 3;
+  uint4* dst = reinterpret_cast<uint4*>(p.dest[drank] + (size_t)drow * p.hidden * 2);
+  for (int vc = threadIdx.x; vc < vecs; vc += blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int i = 0; i < len; ++i) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.y + (size_t)s_chain[i] * p.hidden) + vc);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] = __fadd_rn(acc[2 * j], f.x);
+        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], f.y);
+      }
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 pr = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&pr);
+    }
+    dst[vc] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  // the rows went to other GPUs: make them visible before the grid's completion is signalled
+  __threadfence_system();
+}
+
 static int check_world(int world, int experts_total) {
   if (world < 1 || world > kMaxPeers)
     return fail(MSC_ERR_UNSUPPORTED, "world=%d must be in [1, %d]", world, kMaxPeers);
@@ -459,8 +543,8 @@ int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const 
                              const float* input_gs, int tokens, int hidden, int topk,
                              int experts_total, int world, void* const* peer_a_q,
                              void* const* peer_sf_rows, float* const* peer_row_weight,
-                             int32_t* const* peer_row_dest, int rank, int rows_cap,
-                             int32_t* pair_row, void* stream) {
+                             int32_t* const* peer_row_dest, int32_t* const* peer_row_next, int rank,
+                             int rows_cap, int32_t* pair_row, void* stream) {
   if (!tokens_bf16 || !ids || !weights || !rank_in_group || !send_base || !input_gs || !peer_a_q ||
       !peer_sf_rows || !peer_row_weight || !pair_row)
     return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
@@ -472,6 +556,9 @@ int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const 
   if (rank < 0 || rank >= world) return msc::fail(MSC_ERR_BAD_ARG, "rank=%d outside [0, %d)", rank, world);
   if ((long long)tokens * topk > 0x03ffffffLL)
     return msc::fail(MSC_ERR_UNSUPPORTED, "tokens * topk exceeds the 26 bits of a row destination code");
+  if (peer_row_next && !peer_row_dest) return msc::fail(MSC_ERR_BAD_ARG, "row_next needs row_dest");
+  if (peer_row_next && !(hidden % 256 == 0 && topk <= 32 && hidden <= 65536))
+    return msc::fail(MSC_ERR_UNSUPPORTED, "the pre-summed combine needs hidden %% 256 == 0, hidden <= 65536, topk <= 32");
   msc::EpDispatchParams p;
   p.tokens = static_cast<const __nv_bfloat16*>(tokens_bf16);
   p.ids = ids; p.weights = weights; p.rank_in_group = rank_in_group; p.send_base = send_base;
@@ -486,6 +573,8 @@ int msc_ep_dispatch_quantize(const void* tokens_bf16, const int32_t* ids, const 
     p.sf[r] = in ? static_cast<uint8_t*>(peer_sf_rows[r]) : nullptr;
     p.row_weight[r] = in ? peer_row_weight[r] : nullptr;
     p.row_dest[r] = (in && peer_row_dest) ? peer_row_dest[r] : nullptr;
+    p.row_next[r] = (in && peer_row_next) ? peer_row_next[r] : nullptr;
+    if (in && peer_row_next && !peer_row_next[r]) return msc::fail(MSC_ERR_BAD_ARG, "NULL row_next for rank %d", r);
     if (in && peer_row_dest && !peer_row_dest[r]) return msc::fail(MSC_ERR_BAD_ARG, "NULL row_dest for rank %d", r);
   }
   p.rank = rank;
@@ -563,6 +652,30 @@ int msc_ep_wait(const int32_t* flags, int world, int slot, int epoch, void* stre
   uint32_t* status = reinterpret_cast<uint32_t*>(msc::status_word());
   if (!status) return MSC_ERR_CUDA;
   msc::ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, slot, epoch, status);
+  MSC_CUDA_OK(cudaGetLastError());
+  return MSC_OK;
+}
+
+int msc_ep_presum_push(const void* y, const int32_t* row_dest, const int32_t* row_next,
+                       void* const* dest_bases, int dest_count, int dest_rows, int rows, int hidden,
+                       void* stream) {
+  if (!y || !row_dest || !row_next || !dest_bases) return msc::fail(MSC_ERR_BAD_ARG, "NULL pointer");
+  if (dest_count < 1 || dest_count > msc::kMaxPeers)
+    return msc::fail(MSC_ERR_BAD_ARG, "dest_count=%d must be in [1, %d]", dest_count, msc::kMaxPeers);
+  if (dest_rows <= 0 || dest_rows > 0x04000000) return msc::fail(MSC_ERR_BAD_ARG, "dest_rows out of range");
+  if (rows <= 0) return msc::fail(MSC_ERR_BAD_ARG, "rows must be positive");
+  if (hidden <= 0 || hidden % 8) return msc::fail(MSC_ERR_BAD_ARG, "hidden=%d must be a multiple of 8", hidden);
+  msc::EpPresumParams p;
+  p.y = static_cast<const __nv_bfloat16*>(y);
+  p.row_dest = row_dest; p.row_next = row_next;
+  for (int r = 0; r < msc::kMaxPeers; ++r) {
+    if (r < dest_count && !dest_bases[r]) return msc::fail(MSC_ERR_BAD_ARG, "NULL destination %d", r);
+    p.dest[r] = r < dest_count ? static_cast<uint8_t*>(dest_bases[r]) : nullptr;
+  }
+  p.status = reinterpret_cast<uint32_t*>(msc::status_word());
+  if (!p.status) return MSC_ERR_CUDA;
+  p.rows = rows; p.hidden = hidden; p.dest_count = dest_count; p.dest_rows = dest_rows;
+  msc::ep_presum_push_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   MSC_CUDA_OK(cudaGetLastError());
   return MSC_OK;
 }

@@ -147,7 +147,7 @@ class _DeviceBytes:
                                          "version": 3, "strides": None}
 
 
-EXCHANGE_BUFFERS = ("a_q", "sf_rows", "row_weight", "y", "row_dest", "recv_y", "flags", "counts_all")
+EXCHANGE_BUFFERS = ("a_q", "sf_rows", "row_weight", "y", "row_dest", "recv_y", "flags", "counts_all", "row_next")
 FLAG_SLOTS, FLAG_PEERS = 4, 16     # a flag table: slots x peers int32 (msc_ep_signal / msc_ep_wait)
 SLOT_COUNTS, SLOT_ROWS_LANDED, SLOT_RESULTS_READY = 0, 1, 2
 
@@ -159,7 +159,8 @@ def exchange_layout(rows_cap: int, hidden: int, pairs_cap: int = 0, world: int =
     second GEMM delivers this rank's results (0: no such buffer, the combine pulls from y).
     world * experts_total sizes the table the peers write their per-expert counts into."""
     sizes = (rows_cap * (hidden // 2), rows_cap * (hidden // 16), rows_cap * 4, rows_cap * hidden * 2,
-             rows_cap * 4, pairs_cap * hidden * 2, FLAG_SLOTS * FLAG_PEERS * 4, world * experts_total * 4)
+             rows_cap * 4, pairs_cap * hidden * 2, FLAG_SLOTS * FLAG_PEERS * 4, world * experts_total * 4,
+             rows_cap * 4)
     offs, at = [], 0
     for n in sizes:
         offs.append(at)
@@ -186,6 +187,7 @@ def exchange_views(base: torch.Tensor, rows_cap: int, hidden: int, pairs_cap: in
         "recv_y": cut(5, pairs_cap * hidden * 2).view(torch.bfloat16).view(pairs_cap, hidden),
         "flags": cut(6, FLAG_SLOTS * FLAG_PEERS * 4).view(torch.int32),
         "counts_all": cut(7, world * experts_total * 4).view(torch.int32).view(world, experts_total),
+        "row_next": cut(8, rows_cap * 4).view(torch.int32),
     }
 
 
@@ -258,12 +260,17 @@ class PeerExpertParallelMoE:
 
     def __init__(self, layer, pointers: dict, sf_rows, input_gs_all, experts_total: int, topk: int,
                  max_tokens: int, rank: int, world: int, group=None, row_dest=None, recv_y=None,
-                 flags=None, counts_all=None):
+                 flags=None, counts_all=None, row_next=None):
         """With `row_dest` (rows_cap,) i32 and `recv_y` (>= max_tokens * topk, h) bf16 — this
         rank's buffers of those names, whose addresses on every rank are in `pointers` — the
         combine is pushed: the second GEMM scatters each result row into the home rank's recv_y
         while it runs, and `combine` only sums k local rows per token.  Without them `combine`
         pulls the rows from the owners' y after the GEMM.
+        With `row_next` (rows_cap,) i32 as well, a token's result rows that live on the same rank
+        are summed there before they cross NVLink (about a third fewer rows under uniform
+        routing): the second GEMM stores locally and msc_ep_presum_push sends one row per
+        (token, rank).  The sum is then rounded once per rank the token visits, so the result is
+        no longer bit-identical to the single-GPU layer, only within the layer's tolerance.
         With `flags` and `counts_all` (this rank's buffers of those names) the ranks synchronise
         through flags in each other's memory (msc_ep_signal / msc_ep_wait) and exchange the
         counts the same way; without them `forward` uses an NCCL all-gather and two all-reduces."""
@@ -294,6 +301,14 @@ class PeerExpertParallelMoE:
             self._rd, self._ry = arr(*pointers["row_dest"]), arr(*pointers["recv_y"])
         else:
             self._rd = None
+        self.presum = row_next is not None
+        self._rn = None
+        if self.presum:
+            if not self.push:
+                raise ValueError("row_next (the pre-summed combine) needs row_dest and recv_y")
+            if row_next.data_ptr() != pointers["row_next"][rank] or tuple(row_next.shape) != (layer.rows_cap,):
+                raise ValueError("row_next is not the (rows_cap,) buffer the other ranks were given")
+            self.row_next, self._rn = row_next, arr(*pointers["row_next"])
         dev = layer.a_q.device
         i32 = dict(dtype=torch.int32, device=dev)
         T, K = max_tokens, topk
@@ -379,7 +394,7 @@ class PeerExpertParallelMoE:
         _lib.check(_lib.load().msc_ep_dispatch_quantize(
             tokens.data_ptr(), self.ids.data_ptr(), self.weights.data_ptr(), self.rank_in_group.data_ptr(),
             self.send_base.data_ptr(), self.input_gs_all.data_ptr(), T, self.layer.h, self.topk, self.E,
-            self.world, self._q, self._sf, self._rw, self._rd, self.rank, self.rows_cap,
+            self.world, self._q, self._sf, self._rw, self._rd, self._rn, self.rank, self.rows_cap,
             self.pair_row.data_ptr(), self._stream()))
 
     def experts(self):
@@ -391,6 +406,14 @@ class PeerExpertParallelMoE:
                                               L.h // 16, self._stream()))
         if not self.push:
             L.run_experts()
+            return
+        if self.presum:
+            L.run_experts()
+            _lib.check(_lib.load().msc_ep_presum_push(L.y.data_ptr(), self.row_dest.data_ptr(),
+                                                      self.row_next.data_ptr(), self._ry, self.world,
+                                                      self.max_tokens * self.topk, self.rows_cap, L.h,
+                                                      self._stream()))
+            self.row_dest.fill_(-1)
             return
         L.run_gemm1()
         _lib.check(_lib.load().msc_grouped_gemm_nvfp4_scatter_ragged(

@@ -176,12 +176,17 @@ def test_expert_parallel_entry_points_reject_bad_arguments(lib):
     assert rc == _lib.ERR_BAD_ARG and b"rows_cap" in lib.msc_last_error()
     rc = lib.msc_ep_offsets(one, 17, 0, 34, 1024, one, one, one, one, None, 0, 0, None)
     assert rc == _lib.ERR_UNSUPPORTED and b"world=17" in lib.msc_last_error()
-    rc = lib.msc_ep_dispatch_quantize(one, one, one, one, one, one, 8, 100, 2, 32, 2, two, two, two, None, 0,
+    rc = lib.msc_ep_dispatch_quantize(one, one, one, one, one, one, 8, 100, 2, 32, 2, two, two, two, None, None, 0,
                                       1024, one, None)
     assert rc == _lib.ERR_BAD_ARG and b"hidden=100" in lib.msc_last_error()
     rc = lib.msc_ep_dispatch_quantize(one, one, one, one, one, one, 1 << 24, 256, 8, 32, 2, two, two, two, None,
-                                      0, 1024, one, None)
+                                      None, 0, 1024, one, None)
     assert rc == _lib.ERR_UNSUPPORTED and b"26 bits" in lib.msc_last_error()
+    rc = lib.msc_ep_dispatch_quantize(one, one, one, one, one, one, 8, 256, 2, 32, 2, two, two, two, None, two, 0,
+                                      1024, one, None)
+    assert rc == _lib.ERR_BAD_ARG and b"row_next needs row_dest" in lib.msc_last_error()
+    rc = lib.msc_ep_presum_push(one, one, one, two, 17, 64, 128, 256, None)
+    assert rc == _lib.ERR_BAD_ARG and b"dest_count=17" in lib.msc_last_error()
     rc = lib.msc_ep_combine(None, one, one, one, 8, 256, 2, 32, 2, 1024, None)
     assert rc == _lib.ERR_BAD_ARG and b"NULL" in lib.msc_last_error()
     rc = lib.msc_ep_sum_pairs(one, None, one, 8, 100, 2, None)
