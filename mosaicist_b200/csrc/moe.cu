@@ -99,7 +99,8 @@ __global__ void __launch_bounds__(256)
 moe_plan_kernel(const int* __restrict__ ids, int entries, int expert_first, int experts_local,
                 int* __restrict__ rank, int* __restrict__ group_rows, int* __restrict__ group_offsets,
                 int* __restrict__ total_rows, int* __restrict__ scratch) {
-  __shared__ int warp_tot[2][8];
+  constexpr int kSub = 4;                 // 1024-pair pieces handled between two block barriers
+  __shared__ int warp_tot[2][kSub][8];
   __shared__ int is_last;
   const int e = blockIdx.x;
   const int want = expert_first + e;
@@ -107,42 +108,59 @@ moe_plan_kernel(const int* __restrict__ ids, int entries, int expert_first, int 
   const unsigned below = (1u << lane) - 1u;
   const bool vec = (reinterpret_cast<uintptr_t>(ids) & 15) == 0;
   int running = 0;
-  // Each thread owns four consecutive pairs per round (one 16-byte load when the round is
-  // full); the per-warp totals are double-buffered so a round costs one block barrier.
-  for (int base = 0, round = 0; base < entries; base += 1024, ++round) {
-    const int i0 = base + threadIdx.x * 4;
-    int4 v = make_int4(-1, -1, -1, -1);
-    if (vec && i0 + 3 < entries) {
-      v = __ldg(reinterpret_cast<const int4*>(ids + i0));
-    } else {
-      if (i0 < entries) v.x = __ldg(ids + i0);
-      if (i0 + 1 < entries) v.y = __ldg(ids + i0 + 1);
-      if (i0 + 2 < entries) v.z = __ldg(ids + i0 + 2);
-      if (i0 + 3 < entries) v.w = __ldg(ids + i0 + 3);
-    }
-    const bool h0 = v.x == want, h1 = v.y == want, h2 = v.z == want, h3 = v.w == want;
-    const unsigned b0 = __ballot_sync(0xffffffffu, h0), b1 = __ballot_sync(0xffffffffu, h1);
-    const unsigned b2 = __ballot_sync(0xffffffffu, h2), b3 = __ballot_sync(0xffffffffu, h3);
-    int* tot = warp_tot[round & 1];
-    if (lane == 0) tot[warp] = __popc(b0) + __popc(b1) + __popc(b2) + __popc(b3);
-    __syncthreads();
-    int before = 0, total = 0;
+  // Each thread owns four consecutive pairs of every 1024-pair piece (one 16-byte load when the
+  // piece is full) and a round covers kSub pieces, so the loads of a round are all in flight
+  // together and a block barrier is paid once per 4096 pairs; the per-warp totals are
+  // double-buffered.
+  for (int base = 0, round = 0; base < entries; base += 1024 * kSub, ++round) {
+    int4 v[kSub];
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      const int c = tot[w];
-      if (w < warp) before += c;
-      total += c;
+    for (int j = 0; j < kSub; ++j) {
+      const int i0 = base + j * 1024 + threadIdx.x * 4;
+      v[j] = make_int4(-1, -1, -1, -1);
+      if (vec && i0 + 3 < entries) {
+        v[j] = __ldg(reinterpret_cast<const int4*>(ids + i0));
+      } else {
+        if (i0 < entries) v[j].x = __ldg(ids + i0);
+        if (i0 + 1 < entries) v[j].y = __ldg(ids + i0 + 1);
+        if (i0 + 2 < entries) v[j].z = __ldg(ids + i0 + 2);
+        if (i0 + 3 < entries) v[j].w = __ldg(ids + i0 + 3);
+      }
     }
-    int r = running + before + __popc(b0 & below) + __popc(b1 & below) + __popc(b2 & below) +
-            __popc(b3 & below);
-    if (h0) rank[i0] = r;
-    r += h0;
-    if (h1) rank[i0 + 1] = r;
-    r += h1;
-    if (h2) rank[i0 + 2] = r;
-    r += h2;
-    if (h3) rank[i0 + 3] = r;
-    running += total;
+    unsigned b[kSub][4];
+#pragma unroll
+    for (int j = 0; j < kSub; ++j) {
+      b[j][0] = __ballot_sync(0xffffffffu, v[j].x == want);
+      b[j][1] = __ballot_sync(0xffffffffu, v[j].y == want);
+      b[j][2] = __ballot_sync(0xffffffffu, v[j].z == want);
+      b[j][3] = __ballot_sync(0xffffffffu, v[j].w == want);
+      if (lane == 0)
+        warp_tot[round & 1][j][warp] = __popc(b[j][0]) + __popc(b[j][1]) + __popc(b[j][2]) + __popc(b[j][3]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kSub; ++j) {
+      const int* tot = warp_tot[round & 1][j];
+      int before = 0, total = 0;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const int c = tot[w];
+        if (w < warp) before += c;
+        total += c;
+      }
+      const int i0 = base + j * 1024 + threadIdx.x * 4;
+      const bool h0 = v[j].x == want, h1 = v[j].y == want, h2 = v[j].z == want, h3 = v[j].w == want;
+      int r = running + before + __popc(b[j][0] & below) + __popc(b[j][1] & below) +
+              __popc(b[j][2] & below) + __popc(b[j][3] & below);
+      if (h0) rank[i0] = r;
+      r += h0;
+      if (h1) rank[i0 + 1] = r;
+      r += h1;
+      if (h2) rank[i0 + 2] = r;
+      r += h2;
+      if (h3) rank[i0 + 3] = r;
+      running += total;
+    }
   }
   if (threadIdx.x == 0) {
     group_rows[e] = running;

@@ -27,11 +27,34 @@ __device__ __forceinline__ size_t tiled_sf_word(int row, int kword, int kwords) 
 // (q = RN(a rb); r = a - q b exactly; q' = RN(q + r rb)), which is the correctly rounded
 // quotient whenever rb is the correctly rounded reciprocal and nothing overflows; the block
 // quantiser divides 16 values by the same step, so the reciprocal is shared.
+template <bool GUARD = true>
 __device__ __forceinline__ float div_rn_shared_rcp(float a, float b, float rb) {
   const float q = __fmul_rn(a, rb);
   const float r = __fmaf_rn(-q, b, a);
   const float qc = __fmaf_rn(r, rb, q);
-  return (fabsf(q) <= 3.0e38f) ? qc : q;   // keep +-inf (and NaN) instead of inf - inf
+  // keep +-inf instead of inf - inf; a block whose largest quotient is finite needs no guard
+  // (a NaN element comes out NaN either way)
+  return (!GUARD || fabsf(q) <= 3.0e38f) ? qc : q;
+}
+
+// 16 values / step -> 8 bytes of e2m1.  The reference's clip to [-6, 6] is what the saturating
+// conversion does to finite and infinite values alike, so it is not repeated here.
+template <bool GUARD>
+__device__ __forceinline__ void pack_block(const float* v, float safe, float rsafe, uint32_t* w) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int pr = 0; pr < 4; ++pr) {
+      const int i = h * 8 + pr * 2;
+      const float x0 = div_rn_shared_rcp<GUARD>(v[i], safe, rsafe);
+      const float x1 = div_rn_shared_rcp<GUARD>(v[i + 1], safe, rsafe);
+      const __nv_fp4x2_storage_t b2 =
+          __nv_cvt_float2_to_fp4x2(make_float2(x0, x1), __NV_E2M1, cudaRoundNearest);
+      word |= (uint32_t)b2 << (8 * pr);
+    }
+    w[h] = word;
+  }
 }
 
 // Quantises one block of 16 fp32 values into 8 bytes of e2m1 and its e4m3 scale byte.
@@ -49,23 +72,11 @@ __device__ __forceinline__ void quantize_16(const float* v, float gs, uint2& q8,
   const bool dead = step == 0.0f;
   const float safe = dead ? 1.0f : step;
   const float rsafe = dead ? 0.0f : __frcp_rn(step);
+  // the largest quotient of the block bounds all of them: only a block where it overflows (an
+  // infinite element, a step that underflowed) takes the per-element overflow guard
   uint32_t w[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int pr = 0; pr < 4; ++pr) {
-      const int i = h * 8 + pr * 2;
-      // the reference's clip to [-6, 6] is what the saturating conversion does to finite and
-      // infinite values alike, so it is not repeated here
-      const float x0 = div_rn_shared_rcp(v[i], safe, rsafe);
-      const float x1 = div_rn_shared_rcp(v[i + 1], safe, rsafe);
-      const __nv_fp4x2_storage_t b2 =
-          __nv_cvt_float2_to_fp4x2(make_float2(x0, x1), __NV_E2M1, cudaRoundNearest);
-      word |= (uint32_t)b2 << (8 * pr);
-    }
-    w[h] = word;
-  }
+  if (__fmul_rn(amax, rsafe) <= 3.0e38f) pack_block<false>(v, safe, rsafe, w);
+  else pack_block<true>(v, safe, rsafe, w);
   q8 = make_uint2(w[0], w[1]);
 }
 

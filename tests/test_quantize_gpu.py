@@ -15,11 +15,13 @@ def T(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def _data(l, m, k, seed):
+def _data(l, m, k, seed, inf=False):
     x = np.random.default_rng([seed, 0]).standard_normal((l, m, k)).astype(np.float32)
     x[0, 0, :16] = 0.0              # an all-zero block: scale 0, values 0
     x[0, 1, 16:32] *= 1e-6          # a block whose scale underflows e4m3
     x[-1, 2, 5] = 40.0              # an outlier that dominates its block
+    if inf:                         # infinite values saturate to +-6, their block's scale to 448
+        x[0, 3, 40], x[0, 3, 41] = np.inf, -np.inf
     return x
 
 
@@ -29,7 +31,7 @@ def _data(l, m, k, seed):
 def test_quantize_bit_exact(l, m, k, tiled, dtype):
     from mosaicist_b200 import ops
 
-    x = _data(l, m, k, 11)
+    x = _data(l, m, k, 11, inf=True)    # group 0 gets a fixed global scale below
     if dtype == "bf16":
         x = x.astype(ml_dtypes.bfloat16).astype(np.float32)
     gs = O.global_scale_for(x)
