@@ -110,6 +110,20 @@ def run_workload(section: str = "all"):
         for cfg in cfgs:
             ops.masked_grouped_gemm(a_q, a_sf, b_q, b_sf, None, None, cfg)
 
+    # NVFP4 over row-concatenated groups of 240 - 305 rows (a routed layer's experts): the
+    # row-major pair kernel with short tiles, and the tokens-on-N kernel
+    if want("gemm"):
+        rows = [272, 240, 305, 256, 257, 250, 288, 264]
+        pad = [(r + 127) // 128 * 128 for r in rows]
+        offs = np.concatenate([[0], np.cumsum(pad)[:-1]]).astype(np.int32)
+        tot, nn, kk = int(sum(pad)), 4096, 7168
+        a_q, a_sf = u8(tot, kk // 2), u8(tot // 128, kk // 64, 32, 16, lo=0x30, hi=0x40)
+        b_q, b_sf = u8(len(rows), nn, kk // 2), u8(len(rows), nn // 128, kk // 64, 32, 16, lo=0x30, hi=0x40)
+        for pair in (1, 3):
+            ops.ragged_grouped_gemm_nvfp4(a_q, a_sf, b_q, b_sf, torch.from_numpy(offs).to(dev),
+                                          torch.tensor(rows, dtype=torch.int32, device=dev), None, None,
+                                          ops.GemmConfig(cta_pair=pair))
+
     # MXFP8 grouped GEMM, ragged rows
     rows = [1024, 512, 256, 128, 640, 384, 896, 256]
     offs = np.concatenate([[0], np.cumsum(rows)[:-1]]).astype(np.int32)

@@ -13,6 +13,8 @@ that build graphs of torch operators (tracing, FakeTensor shape propagation) ins
     grouped_gemm_mxfp8_ragged  the MXFP8 grouped GEMM over row-concatenated groups
     gemm_f16                   the dense fp16 / bf16 problem (hopper_gemm/ref_cutedsl.py:50-74)
     grouped_gemm_bf16_int4_ragged   bf16 x int4 grouped GEMM (problems.py:75-87)
+    moe_masked                 the masked MoE layer, arguments of the reference's moe_masked
+                               (experiments/flashinfer-megamoe-sm100a/moe.py:47-79)
 
 Each is the corresponding C-ABI entry point.  Operators return fresh tensors, so rows a masked
 call leaves untouched come back as zeros.  Importing this module registers the operators; it
@@ -160,3 +162,24 @@ def grouped_gemm_bf16_int4_ragged(a: torch.Tensor, b_q: torch.Tensor, scales: to
 @grouped_gemm_bf16_int4_ragged.register_fake
 def _(a, b_q, scales, group_offsets, group_rows, alpha, group_size):
     return a.new_empty((a.shape[0], b_q.shape[1]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("mosaicist_sm100a::moe_masked", mutates_args=(), device_types="cuda")
+def moe_masked(hidden: torch.Tensor, w1_q: torch.Tensor, w1_sf: torch.Tensor, w1_gs: torch.Tensor,
+               w1_alpha: torch.Tensor, w2_q: torch.Tensor, w2_sf: torch.Tensor, w2_gs: torch.Tensor,
+               w2_alpha: torch.Tensor, masked_m: torch.Tensor, input_global_scale: torch.Tensor,
+               a2_global_scale: torch.Tensor) -> torch.Tensor:
+    """(l, m, k) bf16 -> (l, m, k) bf16: quantise, GEMM1, SiLU(gate) * up + quantise, GEMM2 per
+    expert batch; rows at or beyond masked_m[l] come back as zeros."""
+    from . import moe
+
+    out = moe.moe_masked(hidden, w1_q, w1_sf, w1_gs, w1_alpha, w2_q, w2_sf, w2_gs, w2_alpha, masked_m,
+                         input_global_scale, a2_global_scale)
+    rows = torch.arange(hidden.shape[1], device=hidden.device)[None, :, None] < masked_m[:, None, None]
+    return torch.where(rows, out, torch.zeros_like(out))
+
+
+@moe_masked.register_fake
+def _(hidden, w1_q, w1_sf, w1_gs, w1_alpha, w2_q, w2_sf, w2_gs, w2_alpha, masked_m, input_global_scale,
+      a2_global_scale):
+    return hidden.new_empty(hidden.shape, dtype=torch.bfloat16)

@@ -251,6 +251,13 @@ def test_torch_custom_op_is_registered_and_shape_propagates():
             torch.empty((3, 256, 4), dtype=torch.bfloat16, device="cuda"), torch.empty((3,), **i32),
             torch.empty((3,), **i32), None, 128)
         assert tuple(y.shape) == (768, 256) and y.dtype == torch.bfloat16
+        f32 = dict(dtype=torch.float32, device="cuda")
+        y = torch.ops.mosaicist_sm100a.moe_masked(
+            torch.empty((2, 256, 512), dtype=torch.bfloat16, device="cuda"), torch.empty((2, 512, 256), **u8),
+            torch.empty((2, 4, 8, 32, 16), **u8), torch.empty((2,), **f32), torch.empty((2,), **f32),
+            torch.empty((2, 512, 128), **u8), torch.empty((2, 4, 4, 32, 16), **u8), torch.empty((2,), **f32),
+            torch.empty((2,), **f32), torch.empty((2,), **i32), torch.empty((2,), **f32), torch.empty((2,), **f32))
+        assert tuple(y.shape) == (2, 256, 512) and y.dtype == torch.bfloat16
 
 
 def test_dropped_ptx_is_reduced_to_the_running_instantiation(lib, tmp_path, monkeypatch):

@@ -200,6 +200,11 @@ def test_moe_masked_matches_reference_layer(l, m, k, n):
     rows_t = torch.from_numpy(np.broadcast_to(rows, (l, m, k)).copy()).cuda()
     assert torch.equal(torch.where(rows_t, got, torch.zeros_like(got)),
                        torch.where(rows_t, three, torch.zeros_like(three)))
+    # the layer as a torch operator: the same bits in the rows that count, zeros elsewhere
+    import mosaicist_b200.torch_ops  # noqa: F401
+
+    op = torch.ops.mosaicist_sm100a.moe_masked(*args)
+    assert torch.equal(op, torch.where(rows_t, moe_masked(*args), torch.zeros_like(got)))
 
 
 @pytest.mark.parametrize("T_,E,k,h,n,first,local", [(256, 32, 4, 256, 128, 0, 32),
