@@ -46,8 +46,8 @@ def parser():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--cta-pair", type=int, default=0)
     ap.add_argument("--tile-n", type=int, default=0)
-    ap.add_argument("--gemm1-tokens-on-n", action="store_true",
-                    help="fused GEMM1 with the tokens on the MMA's N side (one GPU)")
+    ap.add_argument("--gemm1-row-major", action="store_true",
+                    help="fused GEMM1 on the row-major pair kernel instead of the tokens-on-N kernel (one GPU)")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer")
     ap.add_argument("--sync", choices=["flags", "nccl"], default="flags",
                     help="peer exchange: synchronise through flags in peer memory / NCCL collectives")
@@ -98,7 +98,7 @@ def measure(args, rank: int, world: int, local: int, detail: bool = True) -> dic
     cfg = ops.GemmConfig(tile_n=args.tile_n, cta_pair=args.cta_pair)
     if world == 1:
         layer = MegaMoE(*w, gs_in, gs_a2, topk=k, max_tokens=T_loc, config=cfg,
-                        gemm1_tokens_on_n=args.gemm1_tokens_on_n)
+                        gemm1_tokens_on_n=False if args.gemm1_row_major else None)
         run = lambda: layer.forward(tokens, logits)
     elif args.exchange == "nccl":
         # a rank can receive up to 2x its even share before the workspace is exceeded

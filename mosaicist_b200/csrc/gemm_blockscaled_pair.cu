@@ -410,8 +410,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const int c = blk >> 1, e = (blk & 1) * 16 + i;
               const float gt = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[c][e]) * scale));
               const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[2 + c][e]) * scale));
-              const float sg = __frcp_rn(__fadd_rn(1.0f, expf(-gt)));
-              act[i] = __fmul_rn(__fmul_rn(sg, gt), up);
+              act[i] = silu_mul(gt, up);
             }
             uint2 q2;
             uint32_t sfb;

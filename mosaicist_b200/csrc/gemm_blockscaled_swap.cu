@@ -168,6 +168,9 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
   grid_dependency_wait();
   grid_launch_dependents();
+#ifdef MSC_DEBUG
+  if (p.trace && threadIdx.x == 0) p.trace[(size_t)gridDim.x * 48 + blockIdx.x * 2] = clock64();
+#endif
 
   if (warp == kProducerWarp) {
     // ------------------------------ producer (both CTAs) ------------------------
@@ -175,11 +178,13 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
     uint32_t bits = 0;  // per-stage use parity
     bool ok = true;
     uint32_t s = 0;
-    for (int t = pair; ok; t += npairs) {
+    int tl = 0;
+    for (int t = pair; ok; t += npairs, ++tl) {
       int tt, nt;
       if (!cur.seek(p, ntiles, t, tt, nt)) break;
       int tn, n0, n1;
       cur.widths(tt, tn, n0, n1);
+      MSC_STAMP(0, tl, 0);
       const int wrow0 = cur.g * p.n + nt * 256 + (int)rank * 128;
       // this CTA's tokens: half of each MMA's, 32-row boxes, the second MMA's behind the first's
       const int trow0 = cur.off + tt * 256 + (int)rank * (n0 >> 1);
@@ -216,6 +221,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
         __syncwarp();
         s = (s + 1 == STAGES) ? 0u : s + 1;
       }
+      if (!SWIGLU) MSC_STAMP(0, tl, 1);
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer (leader only) --------------------
@@ -239,6 +245,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
         ok = warp_wait(bar_acc_empty, (uint32_t)(tl & 1) ^ 1u, abort_flag, p.status, 2);
         if (!ok) break;
         tc_fence_after_sync();
+        MSC_STAMP(1, tl, 0);
         for (int kb = 0; kb < p.k_stages; ++kb) {
           ok = warp_wait(bar_full + 8 * s, (bits >> s) & 1u, abort_flag, p.status, 3);
           if (!ok) break;
@@ -294,6 +301,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         if (ok && elect_one()) tc_commit_pair(bar_acc_full, 3);
         __syncwarp();
+        MSC_STAMP(1, tl, 1);
       }
     }
   } else {
@@ -317,16 +325,12 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (warp == 0) MSC_STAMP(2, tl, 0);
       const float alpha = p.alpha ? __ldg(p.alpha + cur.g) : 1.0f;
       const size_t row0 = (size_t)cur.off + (size_t)tt * 256;   // first token row of the tile
-      // 32 tokens of this lane's row, as read from TMEM: applies alpha (and the tokens' row
-      // scales), rounds to bf16 and packs two tokens per register, so that a fifth of an
-      // accumulator stays in 16 registers while the tensor pipe moves on.
-      auto load_pack = [&](int ci, uint32_t* pk) {   // chunk ci: tokens [32 ci, +32) = columns alike
-        uint32_t tmp[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_base + ci * 32, tmp);
-        tmem_ld_wait();
-        const int tok_first = ci * 32;
+      // 32 tokens of this lane's row, as read from TMEM -> alpha (and the tokens' row scales)
+      // applied, rounded to bf16, two tokens per register
+      auto pack = [&](const uint32_t* raw, int tok_first, uint32_t* pk) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float s0 = alpha, s1 = alpha;
@@ -335,37 +339,43 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
             if (tok < tn) s0 *= __ldg(p.row_scale + row0 + tok);
             if (tok + 1 < tn) s1 *= __ldg(p.row_scale + row0 + tok + 1);
           }
-          const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(tmp[2 * i]) * s0,
-                                                         __uint_as_float(tmp[2 * i + 1]) * s1);
+          const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(raw[2 * i]) * s0,
+                                                         __uint_as_float(raw[2 * i + 1]) * s1);
           pk[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
       };
       const int nchunks = (tn + 31) >> 5;   // 32-token chunks of the tile, up to 10
 
-      // token t of the tile sits in accumulator column t; the warps of half h take the 32-token
-      // chunks h, h + 2, ... (five each cover the 320 columns), one after the other: reading
-      // four at once before packing was measured slower (it spills)
-      uint32_t pk[5][16];
-#pragma unroll
-      for (int i = 0; i < 5; ++i) {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) pk[i][e] = 0u;
-        if (2 * i + half < nchunks) load_pack(2 * i + half, pk[i]);
+      // Token t of the tile sits in accumulator column t; the warps of half h take the 32-token
+      // chunks h, h + 2, ... (five each cover the 320 columns).  The accumulator must be free
+      // again quickly - the next tile's MMAs wait for it - and 160 raw registers do not fit: a
+      // fifth chunk, which only a two-MMA tile has, is read and packed first (16 registers),
+      // then the other four are read with one wait, as 128 raw registers, and the accumulator is
+      // released; they are packed one by one where they are used.
+      uint32_t pk4[16];
+      const bool have4 = 8 + half < nchunks;
+      if (have4) {
+        uint32_t tmp[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_base + (8 + half) * 32, tmp);
+        tmem_ld_wait();
+        pack(tmp, (8 + half) * 32, pk4);
       }
+      uint32_t raw[4][32];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (2 * i + half < nchunks) tmem_ld_32x32b_x32(tmem_base + lane_base + (2 * i + half) * 32, raw[i]);
+      tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(bar_acc_empty & kLeaderMask);
+      if (warp == 0) MSC_STAMP(2, tl, 1);
 
       if (!SWIGLU) {
         if (MSC_FLAG(1)) continue;
         const int colw = nt * 256 + (int)rank * 128 + quad * 32;   // first output column of this warp
         uint16_t* outc = reinterpret_cast<uint16_t*>(p.out) + colw + lane;
         const uint32_t box0 = sbase + L::kOffC + warp * 4096;
-#pragma unroll
-        for (int i = 0; i < 5; ++i) {
-          const int ci = 2 * i + half;
-          if (ci >= nchunks) break;
-          const int tok_first = ci * 32;
+        auto store_chunk = [&](const uint32_t* pk, int tok_first) {
           if (tok_first + 32 <= tn) {
             // a whole chunk: turn it around in shared memory ([token][column], 64-byte rows) and
             // store the 32 x 32 box with one tiled bulk copy
@@ -376,9 +386,9 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
               asm volatile("st.shared.b16 [%0], %1;" ::"r"(box + (2 * e) * 64 + lane * 2),
-                           "h"((uint16_t)(pk[i][e] & 0xffffu)) : "memory");
+                           "h"((uint16_t)(pk[e] & 0xffffu)) : "memory");
               asm volatile("st.shared.b16 [%0], %1;" ::"r"(box + (2 * e + 1) * 64 + lane * 2),
-                           "h"((uint16_t)(pk[i][e] >> 16)) : "memory");
+                           "h"((uint16_t)(pk[e] >> 16)) : "memory");
             }
             fence_proxy_async_smem();
             __syncwarp();
@@ -391,11 +401,20 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
               const int tok = tok_first + 2 * e;   // validity is uniform over the warp
-              if (tok < tn) outc[(row0 + tok) * p.n] = (uint16_t)(pk[i][e] & 0xffffu);
-              if (tok + 1 < tn) outc[(row0 + tok + 1) * p.n] = (uint16_t)(pk[i][e] >> 16);
+              if (tok < tn) outc[(row0 + tok) * p.n] = (uint16_t)(pk[e] & 0xffffu);
+              if (tok + 1 < tn) outc[(row0 + tok + 1) * p.n] = (uint16_t)(pk[e] >> 16);
             }
           }
+        };
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int ci = 2 * i + half;
+          if (ci >= nchunks) break;
+          uint32_t pk[16];
+          pack(raw[i], ci * 32, pk);
+          store_chunk(pk, ci * 32);
         }
+        if (have4) store_chunk(pk4, (8 + half) * 32);
         continue;
       }
 
@@ -419,12 +438,21 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const uint32_t buf = cbase + (pass_no & 1) * (64 * L::kPitch);
         ++pass_no;
         const uint32_t dst = buf + (half * 32) * L::kPitch + (quad * 32 + lane) * 2;
+        if (2 * ps + half < nchunks) {                  // tokens beyond the tile are never read back
+          uint32_t pk[16];
+          if (ps < 4) {
+            pack(raw[ps < 4 ? ps : 0], (2 * ps + half) * 32, pk);
+          } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst + (2 * i) * L::kPitch),
-                       "h"((uint16_t)(pk[ps][i] & 0xffffu)) : "memory");
-          asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst + (2 * i + 1) * L::kPitch),
-                       "h"((uint16_t)(pk[ps][i] >> 16)) : "memory");
+            for (int i = 0; i < 16; ++i) pk[i] = pk4[i];
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst + (2 * i) * L::kPitch),
+                         "h"((uint16_t)(pk[i] & 0xffffu)) : "memory");
+            asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst + (2 * i + 1) * L::kPitch),
+                         "h"((uint16_t)(pk[i] >> 16)) : "memory");
+          }
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         const int tok = tok_first + p_tok;
@@ -449,10 +477,8 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
             for (int e = 0; e < 4; ++e) {
               const float2 gt = __bfloat1622float2(gh[e]);
               const float2 up = __bfloat1622float2(uh[e]);
-              const float s0 = __frcp_rn(__fadd_rn(1.0f, expf(-gt.x)));
-              const float s1 = __frcp_rn(__fadd_rn(1.0f, expf(-gt.y)));
-              act[i * 8 + e * 2] = __fmul_rn(__fmul_rn(s0, gt.x), up.x);
-              act[i * 8 + e * 2 + 1] = __fmul_rn(__fmul_rn(s1, gt.y), up.y);
+              act[i * 8 + e * 2] = silu_mul(gt.x, up.x);
+              act[i * 8 + e * 2 + 1] = silu_mul(gt.y, up.y);
             }
           }
           uint2 q2;
@@ -464,12 +490,16 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
           p.out_sf[tiled_sf_word((int)orow, col >> 6, width >> 6) + ((col >> 4) & 3)] = (uint8_t)sfb;
         }
       }
+      if (warp == 0) MSC_STAMP(0, tl, 1);   // debug builds: end of this tile's epilogue
     }
   }
 
   if (!SWIGLU && warp < L::kEpiWarps && lane == 0) bulk_wait_group_read0();
   tc_fence_before_sync();
   __syncthreads();
+#ifdef MSC_DEBUG
+  if (p.trace && threadIdx.x == 0) p.trace[(size_t)gridDim.x * 48 + blockIdx.x * 2 + 1] = clock64();
+#endif
   if (*abort_flag) {
     // a wait gave up somewhere: give loads still in flight time to land before the shared
     // memory they target is released

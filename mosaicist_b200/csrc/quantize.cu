@@ -72,8 +72,7 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_kernel(const QuantParams p
       load16_bf16(base + p.k, up);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float sg = __frcp_rn(__fadd_rn(1.0f, expf(-gt[i])));
-        v[i] = __fmul_rn(__fmul_rn(sg, gt[i]), up[i]);
+        v[i] = silu_mul(gt[i], up[i]);
       }
     } else if (p.f32_in) {
       const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) + row * p.k + kb * 16);

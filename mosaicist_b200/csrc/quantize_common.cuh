@@ -23,6 +23,19 @@ __device__ __forceinline__ size_t tiled_sf_word(int row, int kword, int kwords) 
   return (((size_t)t * kwords + kword) * 32 + b) * 16 + 4 * a;
 }
 
+// silu(gate) * up = gate / (1 + 2^(-gate log2 e)) * up in fp32 (nvfp4.py:81-88), with the
+// approximate exponential and reciprocal the reference's own kernel uses
+// (quantize_kernels.py:50-69): the result only feeds the e2m1 / e4m3 quantiser, a few ulp are
+// far below its steps, and the accurate expf + IEEE reciprocal cost five times the
+// instructions.  Every kernel that activates goes through this one function, so the fused and
+// the stand-alone paths keep producing the same bytes.
+__device__ __forceinline__ float silu_mul(float gate, float up) {
+  float e, s;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(gate, -1.4426950408889634f)));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(__fadd_rn(1.0f, e)));
+  return __fmul_rn(__fmul_rn(s, gate), up);
+}
+
 // a / b rounded to nearest, given rb = RN(1 / b): one multiply and two fused multiply-adds
 // (q = RN(a rb); r = a - q b exactly; q' = RN(q + r rb)), which is the correctly rounded
 // quotient whenever rb is the correctly rounded reciprocal and nothing overflows; the block

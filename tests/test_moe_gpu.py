@@ -232,11 +232,14 @@ def test_megamoe_layer(T_, E, k, h, n, first, local):
     assert np.array_equal(layer.ids.cpu().numpy(), ids)
     # with 8 of 32 experts local most tokens get no contribution: expect about 1 - (3/4)^2 non-zero
     _close(got, want, nonzero_fraction=0.5 if local == E else 0.25)
-    # the same layer with the fused GEMM1 on the tokens-on-N kernel: the very same bits
-    swapped = MegaMoE(d["w1_q"], d["w1_sf"], d["w1_gs"], d["w1_alpha"], d["w2_q"], d["w2_sf"], d["w2_gs"],
-                      d["w2_alpha"], T(input_gs), T(a2_gs), topk=k, max_tokens=T_, expert_first=first,
-                      gemm1_tokens_on_n=True)
-    assert np.array_equal(swapped.forward(tk, T(logits)).float().cpu().numpy(), got)
+    # the layer's fused GEMM1 runs on the tokens-on-N kernel by default; on the row-major pair
+    # kernel, and as separate GEMM + activation kernels, it produces the very same bits
+    assert layer.gemm1_config.cta_pair == 3
+    for kw in (dict(gemm1_tokens_on_n=False), dict(fuse_gemm1=False)):
+        other = MegaMoE(d["w1_q"], d["w1_sf"], d["w1_gs"], d["w1_alpha"], d["w2_q"], d["w2_sf"], d["w2_gs"],
+                        d["w2_alpha"], T(input_gs), T(a2_gs), topk=k, max_tokens=T_, expert_first=first, **kw)
+        assert other.gemm1_config.cta_pair == 0
+        assert np.array_equal(other.forward(tk, T(logits)).float().cpu().numpy(), got)
     assert _lib.status_word() == 0
 
 
