@@ -10,8 +10,8 @@
 //
 // The accumulator is the transpose of the output: TMEM lane = weight row = output column,
 // TMEM column = token (token t of the tile in column t, whichever MMA produced it).  The plain
-// epilogue turns 32 tokens x 32 columns per warp around in shared memory and stores them as one
-// tiled bulk copy; the fused SwiGLU epilogue transposes 64 tokens at a time through shared
+// epilogue turns 32 tokens x 32 columns per warp around in shared memory and writes them out
+// with 16-byte stores; the fused SwiGLU epilogue transposes 64 tokens at a time through shared
 // memory and then activates and quantises one 16-column block per thread.
 //
 // The fused form reads w1 with gate and up rows interleaved in blocks of 64 (rows [128 i, +64)
@@ -43,10 +43,10 @@ struct SwapSmem {
   static constexpr int kEpiWarps = 8;
   static constexpr int kThreads = (kEpiWarps + 2) * 32;
   // SwiGLU: two buffers of 64 tokens x 128 bf16 at a 272-byte pitch (16-byte reads of
-  // consecutive tokens then fall in different banks).  Plain: two [32 tokens][32 columns] store
-  // boxes per epilogue warp.
+  // consecutive tokens then fall in different banks).  Plain: one [32 tokens][32 columns] box
+  // per epilogue warp.
   static constexpr int kPitch = 272;
-  static constexpr int kC = SWIGLU ? 2 * 64 * kPitch : kEpiWarps * 2 * 2048;
+  static constexpr int kC = SWIGLU ? 2 * 64 * kPitch : kEpiWarps * 2048;
   static constexpr int kTotal = kOffC + kC;
   static constexpr int kAlloc = kTotal + 1024;
   static_assert(kAlloc <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
@@ -108,8 +108,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
                  const __grid_constant__ CUtensorMap tmap_t,
                  const __grid_constant__ CUtensorMap tmap_t32,
                  const __grid_constant__ CUtensorMap tmap_sfw,
-                 const __grid_constant__ CUtensorMap tmap_sft,
-                 const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_sft, const GemmParams p) {
   using L = SwapSmem<STAGES, SWIGLU>;
   constexpr int kMmaWarp = L::kEpiWarps;
   constexpr int kProducerWarp = L::kEpiWarps + 1;
@@ -155,7 +154,6 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
     tma_prefetch_desc(&tmap_t32);
     tma_prefetch_desc(&tmap_sfw);
     tma_prefetch_desc(&tmap_sft);
-    tma_prefetch_desc(&tmap_c);
   }
   if (warp == 0) {
     tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -221,7 +219,6 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
         __syncwarp();
         s = (s + 1 == STAGES) ? 0u : s + 1;
       }
-      if (!SWIGLU) MSC_STAMP(0, tl, 1);
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer (leader only) --------------------
@@ -311,7 +308,6 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
     SwapCursor cur;
     int tl = 0;
     int pass_no = 0;   // SwiGLU: passes so far, over all tiles (selects the staging buffer)
-    int store_no = 0;  // plain: boxes stored so far by this warp (selects the staging box)
     const int quad = warp & 3;
     const int half = warp >> 2;
     const uint32_t lane_base = uint32_t(quad * 32) << 16;
@@ -373,37 +369,34 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
       if (!SWIGLU) {
         if (MSC_FLAG(1)) continue;
         const int colw = nt * 256 + (int)rank * 128 + quad * 32;   // first output column of this warp
-        uint16_t* outc = reinterpret_cast<uint16_t*>(p.out) + colw + lane;
-        const uint32_t box0 = sbase + L::kOffC + warp * 4096;
+        const uint32_t box0 = sbase + L::kOffC + warp * 2048;
+        // A chunk (32 tokens x this warp's 32 columns) is turned around in the warp's shared box
+        // ([token][column], 64-byte rows); then four lanes write a token's 64 bytes - two full
+        // sectors - with 16-byte stores, eight tokens per instruction.  Tiled bulk stores were
+        // slower here: they queue behind the ring's loads in the copy engine, and with a tile
+        // only eight stages long the epilogue then outlasts the K loop.
         auto store_chunk = [&](const uint32_t* pk, int tok_first) {
-          if (tok_first + 32 <= tn) {
-            // a whole chunk: turn it around in shared memory ([token][column], 64-byte rows) and
-            // store the 32 x 32 box with one tiled bulk copy
-            const uint32_t box = box0 + (store_no & 1) * 2048;
-            ++store_no;
-            if (lane == 0) bulk_wait_group_read1();   // the copy before last, which used this box, has read it
-            __syncwarp();
+          __syncwarp();   // the previous chunk has been read out of the box
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              asm volatile("st.shared.b16 [%0], %1;" ::"r"(box + (2 * e) * 64 + lane * 2),
-                           "h"((uint16_t)(pk[e] & 0xffffu)) : "memory");
-              asm volatile("st.shared.b16 [%0], %1;" ::"r"(box + (2 * e + 1) * 64 + lane * 2),
-                           "h"((uint16_t)(pk[e] >> 16)) : "memory");
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&tmap_c, box, colw * 2, (int)row0 + tok_first);
-              bulk_commit_group();
-            }
-          } else {
-            // the group ends inside this chunk: 2-byte stores, a warp writing 64 contiguous bytes
+          for (int e = 0; e < 16; ++e) {
+            asm volatile("st.shared.b16 [%0], %1;" ::"r"(box0 + (2 * e) * 64 + lane * 2),
+                         "h"((uint16_t)(pk[e] & 0xffffu)) : "memory");
+            asm volatile("st.shared.b16 [%0], %1;" ::"r"(box0 + (2 * e + 1) * 64 + lane * 2),
+                         "h"((uint16_t)(pk[e] >> 16)) : "memory");
+          }
+          __syncwarp();
+          const int piece = lane & 3;
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const int tok = tok_first + 2 * e;   // validity is uniform over the warp
-              if (tok < tn) outc[(row0 + tok) * p.n] = (uint16_t)(pk[e] & 0xffffu);
-              if (tok + 1 < tn) outc[(row0 + tok + 1) * p.n] = (uint16_t)(pk[e] >> 16);
-            }
+          for (int r = 0; r < 4; ++r) {
+            const int tl_ = r * 8 + (lane >> 2);
+            const int tok = tok_first + tl_;
+            uint4 v;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(box0 + tl_ * 64 + piece * 16) : "memory");
+            if (tok < tn)
+              *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.out) +
+                                        ((row0 + tok) * (size_t)p.n + colw) * 2 + piece * 16) = v;
           }
         };
 #pragma unroll
@@ -415,6 +408,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
           store_chunk(pk, ci * 32);
         }
         if (have4) store_chunk(pk4, (8 + half) * 32);
+        if (warp == 0) MSC_STAMP(0, tl, 1);   // debug builds: end of this tile's epilogue
         continue;
       }
 
@@ -494,7 +488,6 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
   }
 
-  if (!SWIGLU && warp < L::kEpiWarps && lane == 0) bulk_wait_group_read0();
   tc_fence_before_sync();
   __syncthreads();
 #ifdef MSC_DEBUG
@@ -519,7 +512,7 @@ static int launch_swap(const CUtensorMap* maps, const GemmParams& p, int grid, c
   if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kAlloc)) return rc;
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t lc = pdl_launch_config(grid, L::kThreads, L::kAlloc, stream, attr);
-  MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p));
+  MSC_CUDA_OK(cudaLaunchKernelEx(&lc, kern, maps[0], maps[1], maps[2], maps[3], maps[4], p));
   return MSC_OK;
 }
 
@@ -529,7 +522,7 @@ int launch_swap_gemm(const void* a_q, const void* b_q, long long rows_total, lon
   if (!p.group_rows || !p.group_offsets)
     return fail(MSC_ERR_BAD_ARG, "the tokens-on-N kernel takes row-concatenated groups");
   if (p.row_dest) return fail(MSC_ERR_UNSUPPORTED, "the tokens-on-N kernel has no row-scatter epilogue");
-  CUtensorMap maps[6];
+  CUtensorMap maps[5];
   int rc = make_tmap_bytes_2d(&maps[0], b_q, (uint64_t)p.l * p.n, (uint64_t)k_bytes, 128);
   if (rc) return rc;
   rc = make_tmap_bytes_2d(&maps[1], a_q, (uint64_t)rows_total, (uint64_t)k_bytes, 128);
@@ -541,12 +534,6 @@ int launch_swap_gemm(const void* a_q, const void* b_q, long long rows_total, lon
   const uint64_t row_tiles = (uint64_t)(rows_total + 127) / 128;
   rc = make_tmap_sf_2d(&maps[4], p.sfa, row_tiles * p.sf_chunks * 4, 16);
   if (rc) return rc;
-  if (p.out_q) {
-    maps[5] = maps[0];   // the fused epilogue stores with plain writes: no store map needed
-  } else {
-    rc = make_tmap_box64_2d(&maps[5], p.out, (uint64_t)rows_total, (uint64_t)p.n * 2, 32);
-    if (rc) return rc;
-  }
   const long long max_tiles = ((rows_total + 255) / 256 + p.l) * (long long)(p.n / 256);
   int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
   if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");

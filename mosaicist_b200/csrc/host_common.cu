@@ -71,7 +71,7 @@ namespace {
 struct TmapKey {
   const void* base;
   uint64_t rows, row_bytes;
-  uint32_t box_rows;  // bits 31-28: 2 bf16 store map, 1 unswizzled scale map, 3 / 4 unswizzled 32- / 64-byte box, 0 operand map
+  uint32_t box_rows;  // bits 31-28: 2 bf16 store map, 1 unswizzled scale map, 3 unswizzled 32-byte box, 0 operand map
   bool operator==(const TmapKey& o) const {
     return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows;
   }
@@ -140,17 +140,12 @@ int make_tmap_narrow_2d(CUtensorMap* map, const void* base, uint64_t rows, uint6
   return cached_tmap(map, base, rows, row_bytes, box_rows, 3);
 }
 
-int make_tmap_box64_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
-                       uint32_t box_rows) {
-  return cached_tmap(map, base, rows, row_bytes, box_rows, 4);
-}
-
 namespace {
 int encode_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                    uint32_t box_rows, int flavour) {
   const bool bf16 = flavour == 2;
   const bool swizzled = flavour == 0 || flavour == 2;
-  const cuuint32_t box_bytes = flavour == 3 ? 32u : flavour == 4 ? 64u : 128u;
+  const cuuint32_t box_bytes = flavour == 3 ? 32u : 128u;
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return MSC_ERR_CUDA;
   if (reinterpret_cast<uintptr_t>(base) % 16 || row_bytes % 16)

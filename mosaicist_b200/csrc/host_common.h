@@ -43,9 +43,7 @@ int make_tmap_sf_2d(CUtensorMap* map, const void* base, uint64_t rows128, uint32
 // weights: 64 K-elements of box_rows rows).
 int make_tmap_narrow_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                         uint32_t box_rows);
-// The same with a box of [box_rows][64 B] (32 bf16 values), unswizzled; coordinates in bytes.
-int make_tmap_box64_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
-                       uint32_t box_rows);
+
 
 // 2-D byte tensor [rows][row_bytes] whose rows are `pitch_bytes` apart, with a
 // [box_rows][128 B] box and 128-byte swizzle (operands and outputs of the dense GEMM, where a
