@@ -319,6 +319,20 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
       bool ok = true;
       if (lane == 0) ok = mbar_wait_bounded(bar_acc_full, tl & 1, abort_flag, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
+      if (SWIGLU) {
+        // the passes below meet at a named barrier: all eight warps go on or none does, or a
+        // warp whose wait gave up would leave the others waiting there for good
+        uint32_t all_ok;
+        asm volatile(
+            "{\n"
+            " .reg .pred p, q;\n"
+            " setp.ne.u32 p, %1, 0;\n"
+            " bar.red.and.pred q, 1, 256, p;\n"
+            " selp.u32 %0, 1, 0, q;\n"
+            "}\n"
+            : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+        ok = all_ok != 0;
+      }
       if (!ok) break;
       tc_fence_after_sync();
       if (warp == 0) MSC_STAMP(2, tl, 0);
