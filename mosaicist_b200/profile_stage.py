@@ -369,6 +369,85 @@ def in_kernel_clock():
     assert _lib.status_word() == 0
 
 
+def _trace_child():
+    """Runs under MSC_LIB_PATH = the debug build: per-tile clock stamps of the row-major pair
+    kernel and the tokens-on-N kernel on expert-shaped groups (64 groups of 256 or 272 rows,
+    plain epilogue).  One JSON line per (shape, rows, kernel) with the median CTA body and, for
+    the third and fourth tile of CTA 0, the K loop, the time the epilogue holds the accumulator
+    and the epilogue as a whole, all in SM cycles."""
+    import ctypes
+
+    import numpy as np
+    import torch
+
+    from . import _lib, ops
+
+    lib = _lib.load()
+    lib.msc_debug_config.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def u8(*shape, lo=0, hi=256):
+        return torch.randint(lo, hi, shape, dtype=torch.uint8, device=dev, generator=g)
+
+    ncta = torch.cuda.get_device_properties(0).multi_processor_count
+    trace = torch.zeros(ncta * 50 + ncta * 32, dtype=torch.int64, device=dev)
+    E = 64
+    for nn, kk in ((4096, 7168), (7168, 2048)):
+        b_q, b_sf = u8(E, nn, kk // 2), u8(E, nn // 128, kk // 64, 32, 16, lo=0x30, hi=0x40)
+        for rows_each in (256, 272):
+            pad = (rows_each + 127) // 128 * 128
+            tot = E * pad
+            a_q, a_sf = u8(tot, kk // 2), u8(tot // 128, kk // 64, 32, 16, lo=0x30, hi=0x40)
+            offs = torch.arange(E, dtype=torch.int32, device=dev) * pad
+            rows = torch.full((E,), rows_each, dtype=torch.int32, device=dev)
+            out = torch.empty((tot, nn), dtype=torch.bfloat16, device=dev)
+            for pair, name in ((1, "row-major pair"), (3, "tokens on N")):
+                cfg = ops.GemmConfig(cta_pair=pair)
+
+                def run():
+                    ops.ragged_grouped_gemm_nvfp4(a_q, a_sf, b_q, b_sf, offs, rows, None, None, cfg, out=out)
+
+                lib.msc_debug_config(None, 0)
+                run(), run()
+                torch.cuda.synchronize()
+                trace.zero_()
+                lib.msc_debug_config(trace.data_ptr(), 0)
+                run()
+                torch.cuda.synchronize()
+                lib.msc_debug_config(None, 0)
+                t = trace.cpu().numpy()
+                tiles, ends = t[:ncta * 48].reshape(ncta, 8, 3, 2), t[ncta * 48:ncta * 50].reshape(ncta, 2)
+                body = ends[:, 1] - ends[:, 0]
+                rec = {"n": nn, "k": kk, "rows_per_group": rows_each, "kernel": name,
+                       "cta_body_cycles_median": int(np.median(body)), "tiles": []}
+                for tl in (2, 3):
+                    r = tiles[0, tl]
+                    if r[1, 0] == 0:
+                        break
+                    rec["tiles"].append({"k_loop": int(r[1, 1] - r[1, 0]), "accumulator_held": int(r[2, 1] - r[2, 0]),
+                                         "epilogue": int(r[0, 1] - r[2, 0]) if pair == 3 else None})
+                print("TRACE " + json.dumps(rec), flush=True)
+            del a_q, a_sf, out
+    assert _lib.status_word() == 0
+
+
+def tile_trace():
+    from . import build
+
+    debug_lib = build.build_debug()
+    env = dict(os.environ, MSC_LIB_PATH=str(debug_lib))
+    out = subprocess.run([sys.executable, "-m", "mosaicist_b200.profile_stage", "--trace-child"], env=env,
+                         capture_output=True, text=True, check=True, timeout=600).stdout
+    recs = [json.loads(ln[6:]) for ln in out.splitlines() if ln.startswith("TRACE ")]
+    print("| n | k | rows per group | kernel | CTA body, median (cycles) | K loop of a tile | accumulator held by the epilogue | whole epilogue |")
+    print("|---|---|---|---|---|---|---|---|")
+    for r in recs:
+        tl = r["tiles"][-1] if r["tiles"] else {"k_loop": None, "accumulator_held": None, "epilogue": None}
+        print(f"| {r['n']} | {r['k']} | {r['rows_per_group']} | {r['kernel']} | {r['cta_body_cycles_median']} | "
+              f"{tl['k_loop']} | {tl['accumulator_held']} | {tl['epilogue'] if tl['epilogue'] is not None else '-'} |")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--run", action="store_true", help="only launch the workload (what gets profiled)")
@@ -386,9 +465,18 @@ def main():
     ap.add_argument("--timeout", type=int, default=600, help="seconds each run may take")
     ap.add_argument("--in-kernel-clock", action="store_true", help="SM clock inside the GEMM (debug build, no profiler)")
     ap.add_argument("--clock-child", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--tile-trace", action="store_true",
+                    help="per-tile clock stamps of the pair and tokens-on-N kernels (debug build, no profiler)")
+    ap.add_argument("--trace-child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.clock_child:
         _clock_child()
+        return
+    if args.trace_child:
+        _trace_child()
+        return
+    if args.tile_trace:
+        tile_trace()
         return
     if args.in_kernel_clock:
         in_kernel_clock()
