@@ -437,7 +437,10 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const int width = p.n >> 1;                       // columns of the activation
       const int col0 = (nt * 2 + (int)rank) * 64;       // first activation column of this CTA
       const uint32_t cbase = sbase + L::kOffC;
-      const int p_tok = threadIdx.x & 63, p_blk = threadIdx.x >> 6;   // epilogue warps are warps 0-7
+      // phase 2: thread (token, 16-column block) with the four blocks of a token in adjacent
+      // lanes, so that a warp's 8-byte stores fill whole 32-byte sectors and the four scale bytes
+      // of a token's 64 columns leave as one word (the epilogue warps are warps 0-7)
+      const int p_tok = threadIdx.x >> 2, p_blk = threadIdx.x & 3;
       const int npasses = (tn + 63) >> 6;
 #pragma unroll
       for (int ps = 0; ps < 5; ++ps) {
@@ -464,7 +467,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         const int tok = tok_first + p_tok;
-        if (tok < tn) {
+        {   // tokens beyond the tile compute on stale bytes and store nothing: the lanes of a warp stay together
           const uint32_t src = buf + p_tok * L::kPitch + p_blk * 32;
           uint4 graw[2], uraw[2];
 #pragma unroll
@@ -492,10 +495,14 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
           uint2 q2;
           uint32_t sfb;
           quantize_16(act, gs, q2, sfb);
+          const uint32_t sfw = gather_scale_word(sfb);   // valid in the lane of block 0
           const size_t orow = row0 + tok;
           const int col = col0 + p_blk * 16;
-          *reinterpret_cast<uint2*>(p.out_q + orow * (width >> 1) + (col >> 1)) = q2;
-          p.out_sf[tiled_sf_word((int)orow, col >> 6, width >> 6) + ((col >> 4) & 3)] = (uint8_t)sfb;
+          if (tok < tn) {
+            *reinterpret_cast<uint2*>(p.out_q + orow * (width >> 1) + (col >> 1)) = q2;
+            if (p_blk == 0)
+              *reinterpret_cast<uint32_t*>(p.out_sf + tiled_sf_word((int)orow, col0 >> 6, width >> 6)) = sfw;
+          }
         }
       }
       if (warp == 0) MSC_STAMP(0, tl, 1);   // debug builds: end of this tile's epilogue
