@@ -369,7 +369,7 @@ def test_scatter_epilogue_equals_store_then_permute(rows_list, n, k):
     assert torch.equal(dest[0].view(torch.int16), want0.view(torch.int16))
 
 
-@pytest.mark.parametrize("cta_pair", [1, 2])
+@pytest.mark.parametrize("cta_pair", [1, 2, 3])
 def test_group_table_beyond_the_buffers_is_cut_not_followed(cta_pair):
     """A group table that reaches past rows_total (what an overflowing expert-parallel step or a
     stale table hands the GEMM): the kernels are told rows_total = 384 while every buffer really
@@ -400,7 +400,9 @@ def test_group_table_beyond_the_buffers_is_cut_not_followed(cta_pair):
     assert bool(torch.isnan(outs[0][told:]).all()), "rows past rows_total were written"
     assert torch.equal(outs[0][:told].view(torch.int16), outs[1][:told].view(torch.int16))
     assert int((~torch.isnan(outs[0][:told])).sum()) == (200 + 128) * n
-    if cta_pair == 1:
+    if cta_pair in (1, 3):
+        if cta_pair == 3:      # the tokens-on-N form reads the interleaved copy of the weights
+            b_qt, b_sft = ops.swiglu_interleave_w1(b_qt, b_sft)
         gs = T(np.full(3, 8.0, np.float32))
         al = T(np.ones(3, np.float32))
         res = []
