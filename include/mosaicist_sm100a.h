@@ -47,11 +47,12 @@ typedef struct msc_gemm_cfg {
   int max_ctas;  /* persistent grid size; 0 = one CTA per SM                            */
   int epilogue;  /* MSC_EPI_*                                                            */
   int cta_pair;  /* 1: two CTAs share one 256x256 tile (tcgen05 cta_group::2; needs n % 256 == 0,
-                    ignores tile_n); 2: one CTA per tile; 0: the library chooses (pairs when
-                    tile_n is 0, n % 256 == 0 and groups have >= 256 rows); 3 (NVFP4 over
-                    row-concatenated groups only): CTA pairs with the weights on the MMA's M side
-                    and the tokens on N, so that one tile takes up to 320 rows of a group - the
-                    form for groups of a few hundred rows (a routed MoE layer).  The counterpart
+                    ignores tile_n); 2: one CTA per tile; 3 (row-concatenated groups only): CTA
+                    pairs with the weights on the MMA's M side and the tokens on N, so that one
+                    tile takes up to 320 rows of a group - the form for groups of a few hundred
+                    rows (a routed MoE layer); 0: the library chooses (3 for row-concatenated
+                    groups averaging <= 640 rows with n % 256 == 0 and >= 4 KB of K per row, else
+                    pairs when n % 256 == 0 and groups have >= 256 rows).  The counterpart
                     of the reference's `collective` knob (cand_pallas_gemm.py:31)          */
   int sf_warps;  /* CTA-pair kernel only. 1: four extra warps write the scale factors into tensor
                     memory (tcgen05.st) instead of the MMA warp copying them (tcgen05.cp);

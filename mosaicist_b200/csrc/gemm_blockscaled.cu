@@ -475,8 +475,8 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
     return fail(MSC_ERR_BAD_ARG, "k=%d must be a multiple of %d", k, chunk_elems);
   if (cfg.cta_pair < 0 || cfg.cta_pair > 3)
     return fail(MSC_ERR_BAD_ARG, "cta_pair must be 0 (auto), 1 (pair), 2 (single CTA) or 3 (pair, tokens on N)");
-  if (cfg.cta_pair == 3 && (kind != KIND_NVFP4 || !group_offsets || !group_rows))
-    return fail(MSC_ERR_UNSUPPORTED, "cta_pair=3 (tokens on N) is built for NVFP4 over row-concatenated groups");
+  if (cfg.cta_pair == 3 && (!group_offsets || !group_rows))
+    return fail(MSC_ERR_UNSUPPORTED, "cta_pair=3 (tokens on N) is built for row-concatenated groups");
   if (cfg.epilogue != MSC_EPI_PLAIN && cfg.epilogue != MSC_EPI_ROW_SCALE)
     return fail(MSC_ERR_UNSUPPORTED, "unknown epilogue %d", cfg.epilogue);
   if (cfg.epilogue == MSC_EPI_ROW_SCALE && !row_scale)
@@ -524,8 +524,14 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
   p.debug_flags = g_debug_flags;
 #endif
 
-  if (cfg.cta_pair == 3)
-    return launch_swap_gemm(a_q, b_q, rows_total, k_bytes, p, cfg.max_ctas, static_cast<cudaStream_t>(stream_v));
+  // 0 = choose.  Row-concatenated groups of a few hundred rows with a long contraction go to the
+  // tokens-on-N kernel: a group's tail costs it a slightly wider tile instead of a second one,
+  // and a K loop of 4 KB or more hides its transposing epilogue (measured: -3 % on the Zipf
+  // MXFP8 benchmark, -4 % on a routed layer's first GEMM; at k_bytes = 1 KB it loses).
+  const bool swap_auto = cfg.cta_pair == 0 && cfg.tile_n == 0 && group_offsets && group_rows && n % 256 == 0 &&
+                         k_bytes >= 4096 && rows_total / l <= 640;
+  if (cfg.cta_pair == 3 || swap_auto)
+    return launch_swap_gemm(kind, a_q, b_q, rows_total, k_bytes, p, cfg.max_ctas, static_cast<cudaStream_t>(stream_v));
   // 0 = choose: pairs pay off when whole 256-row tiles are common and n allows 256-wide tiles
   bool pair = cfg.cta_pair == 1;
   if (cfg.cta_pair == 0 && cfg.tile_n == 0)
@@ -625,7 +631,7 @@ int msc_grouped_gemm_nvfp4_swiglu_ragged(const void* a_q, const void* a_sf, cons
   p.debug_flags = g_debug_flags;
 #endif
   if (cfg && cfg->cta_pair == 3)   // tokens on N: w1 comes interleaved (msc_swiglu_interleave_w1)
-    return launch_swap_gemm(a_q, w1_q, rows_total, k / 2, p, cfg->max_ctas, static_cast<cudaStream_t>(stream));
+    return launch_swap_gemm(KIND_NVFP4, a_q, w1_q, rows_total, k / 2, p, cfg->max_ctas, static_cast<cudaStream_t>(stream));
   return launch_pair_gemm(KIND_NVFP4, a_q, w1_q, rows_total, k / 2, p, cfg ? cfg->stages : 0,
                           cfg ? cfg->max_ctas : 0, static_cast<cudaStream_t>(stream), false);
 }

@@ -1,4 +1,5 @@
-// NVFP4 grouped GEMM on CTA pairs with the operands' roles exchanged: the WEIGHTS are the MMA's
+// Block-scaled grouped GEMM (NVFP4, and MXFP8 with the plain epilogue) on CTA pairs with the
+// operands' roles exchanged: the WEIGHTS are the MMA's
 // M side (256 rows of B per pair tile, 128 per CTA) and the TOKENS its N side.  N has a
 // granularity of 16, so one tile takes up to 320 rows of a group: up to 256 as one MMA, more as
 // two MMAs (the first 128 tokens, then the rest) that share the weight stage.  A group of 272
@@ -28,13 +29,14 @@
 
 namespace msc {
 
-template <int STAGES, bool SWIGLU>
+template <int KIND, int STAGES, bool SWIGLU>
 struct SwapSmem {
+  static constexpr int kChunks = (KIND == KIND_NVFP4) ? 4 : 1;   // 512-byte scale chunks per 128-row block and stage
   static constexpr int kHeader = 1024;
   static constexpr int kW = 128 * 128;        // this CTA's 128 weight rows
   static constexpr int kT = 160 * 128;        // this CTA's half of the tile's (up to) 320 tokens
-  static constexpr int kSfw = 4 * 512;
-  static constexpr int kSft = 3 * 4 * 512;    // scales of all (up to) 384 token rows
+  static constexpr int kSfw = kChunks * 512;
+  static constexpr int kSft = 3 * kChunks * 512;    // scales of all (up to) 384 token rows
   static constexpr int kOffW = kHeader;
   static constexpr int kOffT = kOffW + STAGES * kW;
   static constexpr int kOffSfw = kOffT + STAGES * kT;
@@ -102,21 +104,25 @@ struct SwapCursor {
   }
 };
 
-template <int STAGES, bool SWIGLU>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SwapSmem<STAGES, SWIGLU>::kThreads, 1)
+template <int KIND, int STAGES, bool SWIGLU>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SwapSmem<KIND, STAGES, SWIGLU>::kThreads, 1)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
                  const __grid_constant__ CUtensorMap tmap_t,
                  const __grid_constant__ CUtensorMap tmap_t32,
                  const __grid_constant__ CUtensorMap tmap_sfw,
                  const __grid_constant__ CUtensorMap tmap_sft, const GemmParams p) {
-  using L = SwapSmem<STAGES, SWIGLU>;
+  using L = SwapSmem<KIND, STAGES, SWIGLU>;
+  static_assert(KIND == KIND_NVFP4 || !SWIGLU, "the fused epilogue quantises to NVFP4");
+  constexpr int kChunks = L::kChunks;
   constexpr int kMmaWarp = L::kEpiWarps;
   constexpr int kProducerWarp = L::kEpiWarps + 1;
   constexpr int kAcc1Col = 128;                 // second accumulator: tokens 128 .. 319
-  constexpr int kSfCol0 = 320, kSlotCols = 80, kSlots = 2;
-  constexpr int kSfwCols = 0, kSft0Cols = 16, kSft1Cols = 48;   // offsets inside a slot
-  constexpr uint32_t kSfBoxBytes = 4 * 512;
-  constexpr uint32_t kIdescBase = (1u << 7) | (1u << 10) | (16u << 24);
+  // a slot: weights 4 columns per chunk, tokens of the first MMA 8, of the second 8
+  constexpr int kSfCol0 = 320, kSlotCols = 20 * kChunks, kSlots = 2;
+  constexpr int kSfwCols = 0, kSft0Cols = 4 * kChunks, kSft1Cols = 12 * kChunks;   // offsets inside a slot
+  constexpr uint32_t kSfBoxBytes = kChunks * 512;
+  constexpr uint32_t kIdescBase = (KIND == KIND_NVFP4) ? ((1u << 7) | (1u << 10) | (16u << 24))
+                                                       : ((1u << 23) | (16u << 24));
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -198,7 +204,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (!ok) break;
         bits ^= 1u << s;
         const uint32_t full = bar_full + 8 * s;
-        const int c4 = kb * 16;
+        const int c4 = kb * kChunks * 4;
         if (elect_one()) {
           if (leader) mbar_arrive_expect_tx(full, 2 * bytes);
           tma_load_2d_pair(sbase + L::kOffW + s * L::kW, &tmap_w, full, kb * 128, wrow0);
@@ -214,7 +220,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
           tma_load_2d_pair(sbase + L::kOffSfw + s * L::kSfw, &tmap_sfw, full, 0, sfw_row + c4);
           const uint32_t sft_dst = sbase + L::kOffSft + s * L::kSft;
           for (int bl = 0; bl < blocks; ++bl)
-            tma_load_2d_pair(sft_dst + bl * 2048, &tmap_sft, full, 0, sft_row + bl * p.sf_chunks * 4 + c4);
+            tma_load_2d_pair(sft_dst + bl * kSfBoxBytes, &tmap_sft, full, 0, sft_row + bl * p.sf_chunks * 4 + c4);
         }
         __syncwarp();
         s = (s + 1 == STAGES) ? 0u : s + 1;
@@ -248,45 +254,57 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
           if (!ok) break;
           bits ^= 1u << s;
           tc_fence_after_sync();
-          const int nch = min(4, p.sf_chunks - kb * 4);
+          const int nch = min(kChunks, p.sf_chunks - kb * kChunks);
+          const int nmma = (KIND == KIND_NVFP4) ? nch : 4;
           const uint32_t slot_t = tmem_base + kSfCol0 + slot * kSlotCols;
           const uint32_t sfw_t = slot_t + kSfwCols, sft0_t = slot_t + kSft0Cols, sft1_t = slot_t + kSft1Cols;
-          // descriptor low words count 16-byte units: +32 per 512-byte scale chunk, +128 per
-          // 2048-byte block of 128 rows, +2 per 32 bytes of K in the operand tile, +512 per 64
-          // operand rows
+          // descriptor low words count 16-byte units: +32 per 512-byte scale chunk, +kBlk per
+          // block of 128 rows, +2 per 32 bytes of K in the operand tile, +512 per 64 operand rows
+          constexpr int kBlk = kChunks * 32;
           const uint64_t sfw_d = sfw_d0 + s * (L::kSfw >> 4);
           const uint64_t sft_d = sft_d0 + s * (L::kSft >> 4);
           const uint64_t wdesc = wdesc0 + s * (L::kW >> 4);
           const uint64_t tdesc = tdesc0 + s * (L::kT >> 4);
           if (elect_one()) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < kChunks; ++c) {
               if (c < nch) {
                 tc_cp_32x128b_warpx4_pair(sfw_t + 4 * c, sfw_d + 32 * c);
                 tc_cp_32x128b_warpx4_pair(sft0_t + 8 * c, sft_d + 32 * c);
                 if (n1) {   // second MMA: tokens from 128 on, i.e. scale blocks 1 (and 2)
-                  tc_cp_32x128b_warpx4_pair(sft1_t + 8 * c, sft_d + 128 + 32 * c);
-                  if (n1 > 128) tc_cp_32x128b_warpx4_pair(sft1_t + 8 * c + 4, sft_d + 256 + 32 * c);
+                  tc_cp_32x128b_warpx4_pair(sft1_t + 8 * c, sft_d + kBlk + 32 * c);
+                  if (n1 > 128) tc_cp_32x128b_warpx4_pair(sft1_t + 8 * c + 4, sft_d + 2 * kBlk + 32 * c);
                 } else if (n0 > 128) {
-                  tc_cp_32x128b_warpx4_pair(sft0_t + 8 * c + 4, sft_d + 128 + 32 * c);
+                  tc_cp_32x128b_warpx4_pair(sft0_t + 8 * c + 4, sft_d + kBlk + 32 * c);
                 }
               }
             }
+            // NVFP4: one MMA per 64-element chunk, each with its own scale columns; MXFP8: four
+            // MMAs of 32 elements share the chunk's columns and pick their byte through the
+            // descriptor's scale ids
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              if (j < nch) {
+              if (j < nmma) {
                 const uint32_t accumulate = (j > 0 || kb > 0) ? 1u : 0u;
-                tc_mma_nvfp4_pair(tmem_base, wdesc + 2 * j, tdesc + 2 * j, idesc0, sfw_t + 4 * j,
-                                  sft0_t + 8 * j, accumulate);
+                if (KIND == KIND_NVFP4)
+                  tc_mma_nvfp4_pair(tmem_base, wdesc + 2 * j, tdesc + 2 * j, idesc0, sfw_t + 4 * j,
+                                    sft0_t + 8 * j, accumulate);
+                else
+                  tc_mma_mxf8_pair(tmem_base, wdesc + 2 * j, tdesc + 2 * j,
+                                   idesc0 | (uint32_t(j) << 29) | (uint32_t(j) << 4), sfw_t, sft0_t, accumulate);
               }
             }
             if (n1 && !MSC_FLAG(8)) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                if (j < nch) {
+                if (j < nmma) {
                   const uint32_t accumulate = (j > 0 || kb > 0) ? 1u : 0u;
-                  tc_mma_nvfp4_pair(tmem_base + kAcc1Col, wdesc + 2 * j, tdesc + 512 + 2 * j, idesc1,
-                                    sfw_t + 4 * j, sft1_t + 8 * j, accumulate);
+                  if (KIND == KIND_NVFP4)
+                    tc_mma_nvfp4_pair(tmem_base + kAcc1Col, wdesc + 2 * j, tdesc + 512 + 2 * j, idesc1,
+                                      sfw_t + 4 * j, sft1_t + 8 * j, accumulate);
+                  else
+                    tc_mma_mxf8_pair(tmem_base + kAcc1Col, wdesc + 2 * j, tdesc + 512 + 2 * j,
+                                     idesc1 | (uint32_t(j) << 29) | (uint32_t(j) << 4), sfw_t, sft1_t, accumulate);
                 }
               }
             }
@@ -526,10 +544,10 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
-template <int STAGES, bool SWIGLU>
+template <int KIND, int STAGES, bool SWIGLU>
 static int launch_swap(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStream_t stream) {
-  using L = SwapSmem<STAGES, SWIGLU>;
-  auto kern = gemm_swap_kernel<STAGES, SWIGLU>;
+  using L = SwapSmem<KIND, STAGES, SWIGLU>;
+  auto kern = gemm_swap_kernel<KIND, STAGES, SWIGLU>;
   if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kern), L::kAlloc)) return rc;
   cudaLaunchAttribute attr[1];
   cudaLaunchConfig_t lc = pdl_launch_config(grid, L::kThreads, L::kAlloc, stream, attr);
@@ -537,8 +555,11 @@ static int launch_swap(const CUtensorMap* maps, const GemmParams& p, int grid, c
   return MSC_OK;
 }
 
-int launch_swap_gemm(const void* a_q, const void* b_q, long long rows_total, long long k_bytes,
+int launch_swap_gemm(int kind, const void* a_q, const void* b_q, long long rows_total, long long k_bytes,
                      const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  const int chunk_rows = (kind == KIND_NVFP4) ? 16 : 4;   // 128-byte rows of a stage's scale chunks
+  if (kind != KIND_NVFP4 && p.out_q)
+    return fail(MSC_ERR_UNSUPPORTED, "the fused SwiGLU epilogue is built for NVFP4");
   if (p.n % 256) return fail(MSC_ERR_BAD_ARG, "the tokens-on-N kernel needs n %% 256 == 0, got n=%d", p.n);
   if (!p.group_rows || !p.group_offsets)
     return fail(MSC_ERR_BAD_ARG, "the tokens-on-N kernel takes row-concatenated groups");
@@ -550,18 +571,19 @@ int launch_swap_gemm(const void* a_q, const void* b_q, long long rows_total, lon
   if (rc) return rc;
   rc = make_tmap_bytes_2d(&maps[2], a_q, (uint64_t)rows_total, (uint64_t)k_bytes, 32);
   if (rc) return rc;
-  rc = make_tmap_sf_2d(&maps[3], p.sfb, (uint64_t)p.l * (p.n / 128) * p.sf_chunks * 4, 16);
+  rc = make_tmap_sf_2d(&maps[3], p.sfb, (uint64_t)p.l * (p.n / 128) * p.sf_chunks * 4, chunk_rows);
   if (rc) return rc;
   const uint64_t row_tiles = (uint64_t)(rows_total + 127) / 128;
-  rc = make_tmap_sf_2d(&maps[4], p.sfa, row_tiles * p.sf_chunks * 4, 16);
+  rc = make_tmap_sf_2d(&maps[4], p.sfa, row_tiles * p.sf_chunks * 4, chunk_rows);
   if (rc) return rc;
   const long long max_tiles = ((rows_total + 255) / 256 + p.l) * (long long)(p.n / 256);
   int pairs = (max_ctas > 0 ? max_ctas : num_sms()) / 2;
   if (pairs <= 0) return fail(MSC_ERR_CUDA, "could not query the SM count");
   if (pairs > max_tiles) pairs = (int)max_tiles;
   const int grid = 2 * pairs;
-  if (p.out_q) return launch_swap<4, true>(maps, p, grid, stream);
-  return launch_swap<4, false>(maps, p, grid, stream);
+  if (p.out_q) return launch_swap<KIND_NVFP4, 4, true>(maps, p, grid, stream);
+  if (kind == KIND_NVFP4) return launch_swap<KIND_NVFP4, 4, false>(maps, p, grid, stream);
+  return launch_swap<KIND_MXFP8, 4, false>(maps, p, grid, stream);
 }
 
 // ---- w1 with gate and up rows interleaved in blocks of 64 ------------------------------------

@@ -107,8 +107,8 @@ int launch_pair_gemm(int kind, const void* a_q, const void* b_q, long long rows_
                      const GemmParams& p, int stages, int max_ctas, cudaStream_t stream,
                      bool sf_by_warps);
 
-// Launcher of the tokens-on-N kernel (gemm_blockscaled_swap.cu): NVFP4, row-concatenated groups.
-int launch_swap_gemm(const void* a_q, const void* b_q, long long rows_total, long long k_bytes,
+// Launcher of the tokens-on-N kernel (gemm_blockscaled_swap.cu): row-concatenated groups.
+int launch_swap_gemm(int kind, const void* a_q, const void* b_q, long long rows_total, long long k_bytes,
                      const GemmParams& p, int max_ctas, cudaStream_t stream);
 
 }  // namespace msc

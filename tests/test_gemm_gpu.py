@@ -154,6 +154,9 @@ RAGGED = [
     # short tiles of the pair kernel: every count of 32-row A boxes in either CTA, next to full tiles
     ([32, 33, 64, 96, 97, 128, 160, 161, 224, 255, 256, 288, 289, 400, 512, 31], 256, 896, {"cta_pair": 1}),
     ([289, 161, 33, 544], 512, 384, {"cta_pair": 1, "max_ctas": 2, "stages": 3}),
+    # tokens on the MMA's N side: one- and two-MMA tiles, several token tiles, tiny groups
+    ([272, 1, 16, 17, 320, 321, 576, 640, 129, 255, 256, 0, 82], 512, 640, {"cta_pair": 3}),
+    ([305, 240, 1000], 256, 896, {"cta_pair": 3, "max_ctas": 4}),
 ]
 
 
@@ -193,7 +196,7 @@ def test_mxfp8_ragged_bit_exact(rows_list, n, k, cfg):
     assert np.isnan(got[~mask[:, 0]]).all()
 
 
-RAGGED_NVFP4 = RAGGED[1:] + [
+RAGGED_NVFP4 = RAGGED[1:-2] + [
     # tokens on the MMA's N side (cta_pair=3): tiles of one MMA (<= 256 rows), of two (257 - 320), several
     # token tiles per group (the last one taking a remainder of up to 64), empty and one-row groups
     ([200, 0, 50, 384, 257], 256, 1024, {"cta_pair": 3}),
