@@ -51,7 +51,7 @@ typedef struct msc_gemm_cfg {
                     pairs with the weights on the MMA's M side and the tokens on N, so that one
                     tile takes up to 320 rows of a group - the form for groups of a few hundred
                     rows (a routed MoE layer); 0: the library chooses (3 for row-concatenated
-                    groups averaging <= 640 rows with n % 256 == 0 and >= 4 KB of K per row, else
+                    groups averaging <= 640 rows with n % 256 == 0 and >= 1 KB of K per row, else
                     pairs when n % 256 == 0 and groups have >= 256 rows).  The counterpart
                     of the reference's `collective` knob (cand_pallas_gemm.py:31)          */
   int sf_warps;  /* CTA-pair kernel only. 1: four extra warps write the scale factors into tensor

@@ -526,10 +526,11 @@ static int grouped_gemm(int kind, const void* a_q, const void* a_sf, const void*
 
   // 0 = choose.  Row-concatenated groups of a few hundred rows with a long contraction go to the
   // tokens-on-N kernel: a group's tail costs it a slightly wider tile instead of a second one,
-  // and a K loop of 4 KB or more hides its transposing epilogue (measured: -3 % on the Zipf
-  // MXFP8 benchmark, -4 % on a routed layer's first GEMM; at k_bytes = 1 KB it loses).
+  // and from 1 KB of K per row on its transposing epilogue fits under the K loop (measured on
+  // 256 groups of 256 +- 16 rows: -10 % at k_bytes = 1 KB, -7 % at 3.5 KB; -3 % on the Zipf
+  // MXFP8 benchmark; groups of exactly 256 rows pay 4 - 6 %).
   const bool swap_auto = cfg.cta_pair == 0 && cfg.tile_n == 0 && group_offsets && group_rows && n % 256 == 0 &&
-                         k_bytes >= 4096 && rows_total / l <= 640;
+                         k_bytes >= 1024 && rows_total / l <= 640;
   if (cfg.cta_pair == 3 || swap_auto)
     return launch_swap_gemm(kind, a_q, b_q, rows_total, k_bytes, p, cfg.max_ctas, static_cast<cudaStream_t>(stream_v));
   // 0 = choose: pairs pay off when whole 256-row tiles are common and n allows 256-wide tiles

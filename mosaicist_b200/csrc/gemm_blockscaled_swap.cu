@@ -45,10 +45,12 @@ struct SwapSmem {
   static constexpr int kEpiWarps = 8;
   static constexpr int kThreads = (kEpiWarps + 2) * 32;
   // SwiGLU: two buffers of 64 tokens x 128 bf16 at a 272-byte pitch (16-byte reads of
-  // consecutive tokens then fall in different banks).  Plain: one [32 tokens][32 columns] box
-  // per epilogue warp.
+  // consecutive tokens then fall in different banks).  Plain: one [32 tokens][32 columns] fp32
+  // box per epilogue warp.
   static constexpr int kPitch = 272;
-  static constexpr int kC = SWIGLU ? 2 * 64 * kPitch : kEpiWarps * 2048;
+  static constexpr int kBoxPitch = 36 * 4;            // plain: a token's 32 fp32 columns, padded
+  static constexpr int kBoxBytes = 32 * kBoxPitch;    // one box of 32 tokens per epilogue warp
+  static constexpr int kC = SWIGLU ? 2 * 64 * kPitch : kEpiWarps * kBoxBytes;
   static constexpr int kTotal = kOffC + kC;
   static constexpr int kAlloc = kTotal + 1024;
   static_assert(kAlloc <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
@@ -334,6 +336,14 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
       if (!cur.seek(p, ntiles, t, tt, nt)) break;
       int tn, n0, n1;
       cur.widths(tt, tn, n0, n1);
+      // the row scales of this warp's tokens, one token per lane and chunk, while the K loop
+      // still runs: every later use takes them from here with a shuffle
+      float rsv[5];
+#pragma unroll
+      for (int i = 0; i < 5; ++i) {
+        const int tok = (2 * i + half) * 32 + lane;
+        rsv[i] = (p.row_scale && tok < tn) ? __ldg(p.row_scale + (size_t)cur.off + (size_t)tt * 256 + tok) : 1.0f;
+      }
       bool ok = true;
       if (lane == 0) ok = mbar_wait_bounded(bar_acc_full, tl & 1, abort_flag, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
@@ -358,14 +368,13 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const size_t row0 = (size_t)cur.off + (size_t)tt * 256;   // first token row of the tile
       // 32 tokens of this lane's row, as read from TMEM -> alpha (and the tokens' row scales)
       // applied, rounded to bf16, two tokens per register
-      auto pack = [&](const uint32_t* raw, int tok_first, uint32_t* pk) {
+      auto pack = [&](const uint32_t* raw, float rs_lane, uint32_t* pk) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float s0 = alpha, s1 = alpha;
           if (p.row_scale) {
-            const int tok = tok_first + 2 * i;
-            if (tok < tn) s0 *= __ldg(p.row_scale + row0 + tok);
-            if (tok + 1 < tn) s1 *= __ldg(p.row_scale + row0 + tok + 1);
+            s0 *= __shfl_sync(0xffffffffu, rs_lane, 2 * i);
+            s1 *= __shfl_sync(0xffffffffu, rs_lane, 2 * i + 1);
           }
           const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(raw[2 * i]) * s0,
                                                          __uint_as_float(raw[2 * i + 1]) * s1);
@@ -386,7 +395,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
         uint32_t tmp[32];
         tmem_ld_32x32b_x32(tmem_base + lane_base + (8 + half) * 32, tmp);
         tmem_ld_wait();
-        pack(tmp, (8 + half) * 32, pk4);
+        pack(tmp, rsv[4], pk4);
       }
       uint32_t raw[4][32];
 #pragma unroll
@@ -401,45 +410,67 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
       if (!SWIGLU) {
         if (MSC_FLAG(1)) continue;
         const int colw = nt * 256 + (int)rank * 128 + quad * 32;   // first output column of this warp
-        const uint32_t box0 = sbase + L::kOffC + warp * 2048;
+        const uint32_t box0 = sbase + L::kOffC + warp * L::kBoxBytes;
         // A chunk (32 tokens x this warp's 32 columns) is turned around in the warp's shared box
-        // ([token][column], 64-byte rows); then four lanes write a token's 64 bytes - two full
-        // sectors - with 16-byte stores, eight tokens per instruction.  Tiled bulk stores were
-        // slower here: they queue behind the ring's loads in the copy engine, and with a tile
-        // only eight stages long the epilogue then outlasts the K loop.
-        auto store_chunk = [&](const uint32_t* pk, int tok_first) {
+        // as raw fp32 ([token][column], rows 36 words apart so that neither phase has a bank
+        // conflict); then four lanes take a token's 32 columns, eight each: they apply alpha and
+        // the token's row scale, round to bf16 and write 16 bytes - a token's 64 bytes are two
+        // full sectors, eight tokens go out per instruction.  Tiled bulk stores were slower here:
+        // they queue behind the ring's loads in the copy engine, and with a tile only eight stages
+        // long the epilogue then outlasts the K loop.
+        const int piece = lane & 3;
+        auto store_chunk = [&](const uint32_t* vals, int tok_first, float rs_lane, bool scaled) {
+          float sc[4];   // alpha x the row scale of each of this lane's four tokens
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const float rs = __shfl_sync(0xffffffffu, rs_lane, r * 8 + (lane >> 2));
+            sc[r] = scaled ? 1.0f : alpha * rs;
+          }
           __syncwarp();   // the previous chunk has been read out of the box
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            asm volatile("st.shared.b16 [%0], %1;" ::"r"(box0 + (2 * e) * 64 + lane * 2),
-                         "h"((uint16_t)(pk[e] & 0xffffu)) : "memory");
-            asm volatile("st.shared.b16 [%0], %1;" ::"r"(box0 + (2 * e + 1) * 64 + lane * 2),
-                         "h"((uint16_t)(pk[e] >> 16)) : "memory");
-          }
+          for (int e = 0; e < 32; ++e)
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(box0 + e * L::kBoxPitch + lane * 4), "r"(vals[e]) : "memory");
           __syncwarp();
-          const int piece = lane & 3;
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
             const int tl_ = r * 8 + (lane >> 2);
             const int tok = tok_first + tl_;
-            uint4 v;
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                         : "r"(box0 + tl_ * 64 + piece * 16) : "memory");
-            if (tok < tn)
+            float f[8];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(f[4 * h]), "=f"(f[4 * h + 1]), "=f"(f[4 * h + 2]), "=f"(f[4 * h + 3])
+                           : "r"(box0 + tl_ * L::kBoxPitch + piece * 32 + h * 16) : "memory");
+            if (tok < tn) {
+              uint32_t w[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                const __nv_bfloat162 pr = __floats2bfloat162_rn(f[2 * h] * sc[r], f[2 * h + 1] * sc[r]);
+                w[h] = *reinterpret_cast<const uint32_t*>(&pr);
+              }
               *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.out) +
-                                        ((row0 + tok) * (size_t)p.n + colw) * 2 + piece * 16) = v;
+                                        ((row0 + tok) * (size_t)p.n + colw) * 2 + piece * 16) =
+                  make_uint4(w[0], w[1], w[2], w[3]);
+            }
           }
         };
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int ci = 2 * i + half;
           if (ci >= nchunks) break;
-          uint32_t pk[16];
-          pack(raw[i], ci * 32, pk);
-          store_chunk(pk, ci * 32);
+          store_chunk(raw[i], ci * 32, rsv[i], false);
         }
-        if (have4) store_chunk(pk4, (8 + half) * 32);
+        if (have4) {
+          // the fifth chunk was scaled and rounded when it was packed: bf16 -> fp32 is exact, and
+          // so is rounding it back
+          uint32_t vals[32];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            vals[2 * e] = pk4[e] << 16;
+            vals[2 * e + 1] = pk4[e] & 0xffff0000u;
+          }
+          store_chunk(vals, (8 + half) * 32, 1.0f, true);
+        }
         if (warp == 0) MSC_STAMP(0, tl, 1);   // debug builds: end of this tile's epilogue
         continue;
       }
@@ -470,7 +501,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (2 * ps + half < nchunks) {                  // tokens beyond the tile are never read back
           uint32_t pk[16];
           if (ps < 4) {
-            pack(raw[ps < 4 ? ps : 0], (2 * ps + half) * 32, pk);
+            pack(raw[ps < 4 ? ps : 0], rsv[ps < 4 ? ps : 0], pk);
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) pk[i] = pk4[i];
