@@ -309,7 +309,8 @@ def test_torch_custom_op_matches_direct_call():
     assert torch.equal(y_op, y_d) and int((y_op[200:256] != 0).sum()) == 0 and int((y_op[:200] != 0).sum()) > 0
 
 
-@pytest.mark.parametrize("rows_list,n,k", [([256], 256, 256), ([300, 0, 77, 512, 129], 512, 640)])
+@pytest.mark.parametrize("rows_list,n,k", [([256], 256, 256), ([300, 0, 77, 512, 129], 512, 640),
+                                           ([1, 320, 257, 0, 33], 256, 2048)])
 def test_scatter_epilogue_equals_store_then_permute(rows_list, n, k):
     """msc_grouped_gemm_nvfp4_scatter_ragged: every valid row lands, bit for bit, where its code
     says - across two destination buffers, in a random order - rows coded negative are dropped,
