@@ -1,8 +1,8 @@
 // Block-scaled grouped GEMM (NVFP4, and MXFP8 with the plain epilogue) on CTA pairs with the
-// operands' roles exchanged: the WEIGHTS are the MMA's
-// M side (256 rows of B per pair tile, 128 per CTA) and the TOKENS its N side.  N has a
-// granularity of 16, so one tile takes up to 320 rows of a group: up to 256 as one MMA, more as
-// two MMAs (the first 128 tokens, then the rest) that share the weight stage.  A group of 272
+// operands' roles exchanged: the WEIGHTS are the MMA's M side (256 rows of B per pair tile, 128
+// per CTA) and the TOKENS its N side.  N has a granularity of 16, so one tile takes up to 320
+// rows of a group: up to 256 as one MMA, more as two MMAs (the first 128 tokens, then the
+// rest) that share the weight stage.  A group of 272
 // rows - the routed MoE layer under uniform routing gives every expert 256 +- 16 - then costs
 // 1.06 tiles of tensor time and one pass over the weights, instead of the two 256-row tiles
 // (the second one almost empty but as expensive in the tensor pipe as a full one) of the
