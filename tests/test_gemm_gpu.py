@@ -82,6 +82,25 @@ def test_exact_operands_bit_exact(l, m, n, k, cfg, seed):
     assert np.isnan(got[~np.broadcast_to(rows, got.shape)]).all()
 
 
+@pytest.mark.parametrize("cfg", [{}, {"cta_pair": 2}])
+def test_headline_shape_ragged_rows_bit_exact(cfg):
+    """The headline shape (l=8, m=512, n=2048, k=2048) with ragged row counts - a full group, an
+    odd count, a single row, an empty group, one and three whole 128-row blocks, one row short of
+    full - on exact operands: bit-exact below masked_m, nothing written at or beyond it."""
+    l, m, n, k = 8, 512, 2048, 2048
+    rng = np.random.default_rng([3, l, m, n, k])
+    a_q, a_sf = O.exact_operands(rng, l, m, k)
+    b_q, b_sf = O.exact_operands(rng, l, n, k)
+    alpha = np.exp2(rng.integers(-1, 2, l)).astype(np.float32)
+    masked_m = np.array([512, 253, 1, 0, 128, 384, 511, 512], np.int32)
+    got = run_masked(a_q, a_sf, b_q, b_sf, alpha, masked_m, _cfg(**cfg))
+    want = O.bf16_round(O.grouped_gemm_f64(a_q, a_sf, b_q, b_sf, alpha, masked_m))
+    rows = np.arange(m)[None, :, None] < masked_m[:, None, None]
+    _nontrivial(want[0])
+    assert np.array_equal(np.where(rows, got, 0), want)
+    assert np.isnan(got[~np.broadcast_to(rows, got.shape)]).all()
+
+
 def test_edge_groups_empty_and_single_row():
     l, m, n, k = 4, 256, 128, 256
     rng = np.random.default_rng(7)
