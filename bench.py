@@ -40,6 +40,7 @@ BYTES_OUT = L * M * N * 2
 ALGO_BYTES = BYTES_IN + BYTES_OUT                                     # 40.37 MB
 L2_BYTES = 126e6
 WORKLOAD = f"nvfp4_grouped_gemm l={L} m={M} n={N} k={K}"
+PUBLISHED_TFLOPS = FLOP / 13.4e-6 / 1e12                              # 2564: the reference's kernel, 13.4 us
 
 
 def peaks():
@@ -573,7 +574,9 @@ def main():
             "metric": "nvfp4_grouped_gemm_tflops", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "e2m1 x e2m1 -> f32 -> bf16", "data": "synthetic",
+            # the published figure for this metric and configuration: FlashInfer's CuTeDSL kernel on
+            # a B200, 13.4 us per launch = 2564 TFLOP/s per GPU, timed with the operands in L2
+            "vs_baseline": per_gpu / PUBLISHED_TFLOPS, "dtype": "e2m1 x e2m1 -> f32 -> bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "groups_per_gpu": L},
             "how": {   "kernel": ("single-CTA tiles 128x%d" % (cfg.tile_n or 128))
                        if (cfg.cta_pair == 2 or cfg.tile_n) else "CTA pairs (cta_group::2), library default",
@@ -588,6 +591,7 @@ def main():
             "pct_fp4_peak_4x_measured_bf16": 100.0 * per_gpu / fp4_derived,
             "warm_l2": {"us_per_launch": warm_us, "tflops": FLOP / (warm_us * 1e-6) / 1e12,
                         "reference_cutedsl_us": 13.4,
+                        "vs_published": FLOP / (warm_us * 1e-6) / 1e12 / PUBLISHED_TFLOPS,
                         "note": "same operand set every launch, the reference's timing convention"},
             "roofline": {"bound": "hbm", "achieved": hbm_achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": hbm_achieved / pk["hbm_gbs"],
