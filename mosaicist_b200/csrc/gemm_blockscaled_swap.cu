@@ -501,6 +501,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (2 * ps + half < nchunks) {                  // tokens beyond the tile are never read back
           uint32_t pk[16];
           if (ps < 4) {
+            // (the index is clamped for the unrolled ps == 4 copy of this branch, which never runs)
             pack(raw[ps < 4 ? ps : 0], rsv[ps < 4 ? ps : 0], pk);
           } else {
 #pragma unroll
